@@ -1,0 +1,34 @@
+// Shared helpers of the attention module: status/error plumbing and small
+// device utilities.  Everything here is internal; the public surface is
+// include/bn_attn.h.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#include "bn_attn.h"
+
+namespace bn {
+
+// Records `code` and a printf-style message for bn_last_error(); returns code.
+int fail(int code, const char* fmt, ...);
+
+// BN_OK when the current device is compute capability 10.x, else BN_ERR_ARCH.
+int require_sm100();
+
+// Converts a pending launch error into BN_ERR_CUDA.
+int launch_status(const char* what);
+
+inline cudaStream_t as_stream(bn_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// The RoPE frequency of pair i, with the reference's exact arithmetic
+// (src/ops/op_rope.cuh:82): fp32 exponent, fp32 pow, reciprocal taken in
+// double, rounded to fp32.
+__device__ __forceinline__ float rope_inv_freq(int pair, int head_dim, float theta) {
+    return (float)(1.0 / powf(theta, (float)(2 * pair) / head_dim));
+}
+
+}  // namespace bn

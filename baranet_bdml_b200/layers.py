@@ -1,0 +1,107 @@
+"""Drop-in mirror of the reference's attention layer.
+
+`GroupedQueryAttention` keeps the constructor, attributes, call signature and
+`parameters()` of mygrad/llama/llama_layers.py:46-191; only the body between
+the projections changes: the steps rope -> repeat_kv -> q k^T -> *scale ->
+softmax -> p v (llama_layers.py:161-183: four host round trips, seven launches
+and an (S,S) matrix in memory) become ONE fused call.
+
+Two semantics are offered (see `heads_mode`):
+  "collapsed"  exactly what the reference computes: its `_split_heads` is a
+               no-op (llama_layers.py:87-103), so there is ONE softmax over the
+               scores summed over all heads.  Default, because it is what makes
+               the layer a numerical drop-in.
+  "per_head"   standard grouped-query attention, one softmax per query head.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import _lib
+from .tensor import AGTensor, TensorF
+
+
+@dataclass
+class LLaMAConfig:
+    """Field-for-field mirror of mygrad/llama/llama_config.py:8-38."""
+    vocab_size: int = 32000
+    hidden_size: int = 2048
+    intermediate_size: int = 5632
+    num_hidden_layers: int = 22
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 4
+    max_position_embeddings: int = 2048
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 10000.0
+    pad_token_id: int = 0
+    bos_token_id: int = 1
+    eos_token_id: int = 2
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden_size // self.num_attention_heads
+
+    @property
+    def num_key_value_groups(self) -> int:
+        return self.num_attention_heads // self.num_key_value_heads
+
+    def __post_init__(self):
+        assert self.hidden_size % self.num_attention_heads == 0
+        assert self.num_attention_heads % self.num_key_value_heads == 0
+
+
+class RotaryEmbedding:
+    """mygrad/llama/llama_layers.py:32-42."""
+
+    def __init__(self, dim: int, max_position_embeddings: int = 2048, base: float = 10000.0):
+        self.dim = dim
+        self.max_position_embeddings = max_position_embeddings
+        self.base = base
+
+    def __call__(self, x: AGTensor, position_offset: int = 0) -> AGTensor:
+        return x.rope(position_offset=position_offset, head_dim=self.dim, theta=self.base)
+
+
+class GroupedQueryAttention:
+    """mygrad/llama/llama_layers.py:46-191 with the attention core fused."""
+
+    def __init__(self, config, is_cuda: bool = True, heads_mode: str = "collapsed"):
+        if heads_mode not in ("collapsed", "per_head"):
+            raise ValueError("heads_mode must be 'collapsed' or 'per_head'")
+        self.config = config
+        self.is_cuda = is_cuda
+        self.heads_mode = heads_mode
+        self.num_heads = config.num_attention_heads
+        self.num_kv_heads = config.num_key_value_heads
+        self.head_dim = config.head_dim
+        self.hidden_size = config.hidden_size
+        self.q_proj = self._init_linear(self.hidden_size, self.hidden_size)
+        self.k_proj = self._init_linear(self.hidden_size, self.num_kv_heads * self.head_dim)
+        self.v_proj = self._init_linear(self.hidden_size, self.num_kv_heads * self.head_dim)
+        self.o_proj = self._init_linear(self.hidden_size, self.hidden_size)
+        self.rotary_emb = RotaryEmbedding(self.head_dim, max_position_embeddings=config.max_position_embeddings,
+                                          base=config.rope_theta)
+        self.scale = 1.0 / np.sqrt(self.head_dim)
+
+    def _init_linear(self, in_features: int, out_features: int) -> AGTensor:
+        # Xavier/Glorot, as llama_layers.py:80-85
+        std = np.sqrt(2.0 / (in_features + out_features))
+        w = np.random.randn(in_features, out_features).astype(np.float32) * std
+        return AGTensor(w, requires_grad=True, is_cuda=self.is_cuda)
+
+    def __call__(self, hidden_states: AGTensor, position_offset: int = 0, use_causal_mask: bool = True) -> AGTensor:
+        query = hidden_states @ self.q_proj
+        key = hidden_states @ self.k_proj
+        value = hidden_states @ self.v_proj
+        mode = _lib.BN_HEADS_COLLAPSED if self.heads_mode == "collapsed" else _lib.BN_HEADS_PER_HEAD
+        attn = query.data.attention_fused(
+            key.data, value.data, float(self.scale), causal=use_causal_mask, seq_offset=position_offset,
+            num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
+            theta=self.rotary_emb.base, heads_mode=mode)
+        attn_output = AGTensor(attn, (query, key, value), "attention_fused", requires_grad=False)
+        return attn_output @ self.o_proj
+
+    def parameters(self):
+        return [self.q_proj, self.k_proj, self.v_proj, self.o_proj]

@@ -1,0 +1,82 @@
+"""Functional front-end of the bf16 kernels on torch CUDA tensors (torch is
+used for device memory and streams only; all arithmetic is in libbn_attn.so).
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need(t: torch.Tensor, dtype, what: str):
+    if not t.is_cuda:
+        raise RuntimeError(f"{what}: only GPU implementation available")
+    if t.dtype != dtype or not t.is_contiguous():
+        raise RuntimeError(f"{what}: expected a contiguous {dtype} tensor")
+
+
+class Workspace:
+    """A caller-owned scratch buffer (256-byte aligned, zero-filled once)."""
+
+    def __init__(self, nbytes: int, device=None):
+        self.buf = torch.zeros(max(int(nbytes), 256) + 256, dtype=torch.uint8, device=device or "cuda")
+        self.ptr = (self.buf.data_ptr() + 255) // 256 * 256
+        self.nbytes = self.buf.numel() - (self.ptr - self.buf.data_ptr())
+
+    def status(self) -> None:
+        """Raises if a kernel that used this buffer gave up on a bounded wait."""
+        _lib.check(_lib.load().bn_workspace_status(self.ptr, _stream()))
+
+
+def prefill_workspace(B: int, S: int, Hq: int, Hkv: int, D: int = 64, device=None) -> Workspace:
+    n = _lib.load().bn_attn_prefill_bf16_workspace_bytes(B, S, Hq, Hkv, D)
+    if n == 0:
+        raise RuntimeError(f"bn_attn_prefill_bf16: unsupported shape B={B} S={S} Hq={Hq} Hkv={Hkv} D={D}")
+    return Workspace(n, device)
+
+
+def attn_prefill_bf16(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: Optional[float] = None,
+                      theta: float = 10000.0, position_offset: int = 0, causal: bool = True,
+                      out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None,
+                      workspace: Optional[Workspace] = None, reuse_rotated_k: bool = False) -> torch.Tensor:
+    """q (B,S,Hq,D), k,v (B,S,Hkv,D) bf16, q/k pre-RoPE -> out (B,S,Hq,D) bf16.
+    `reuse_rotated_k`: the workspace still holds the rotated K of an earlier
+    call on the same k and position_offset (skips the rotation launch)."""
+    for t, n in ((q, "q"), (k, "k"), (v, "v")):
+        _need(t, torch.bfloat16, f"attn_prefill_bf16({n})")
+    B, S, Hq, D = q.shape
+    Hkv = k.shape[2]
+    if k.shape != (B, S, Hkv, D) or v.shape != k.shape:
+        raise RuntimeError("Attention: hidden size mismatch")
+    if out is None:
+        out = torch.empty_like(q)
+    if workspace is None:
+        workspace = prefill_workspace(B, S, Hq, Hkv, D, q.device)
+    if scale is None:
+        scale = 1.0 / (D ** 0.5)
+    _lib.check(_lib.load().bn_attn_prefill_bf16(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr() if lse is not None else None,
+        B, S, Hq, Hkv, D, float(scale), float(theta), int(position_offset), int(bool(causal)),
+        0x100 if reuse_rotated_k else 0,
+        workspace.ptr, workspace.nbytes, _stream()))
+    return out
+
+
+def lse_combine(outs: torch.Tensor, lses: torch.Tensor, *, out_dtype=torch.float32) -> Tuple[torch.Tensor, torch.Tensor]:
+    """outs (P, n, D) fp32, lses (P, n) fp32 -> merged (n, D), lse (n)."""
+    _need(outs, torch.float32, "lse_combine(outs)")
+    _need(lses, torch.float32, "lse_combine(lses)")
+    P, n, D = outs.shape
+    o32 = torch.empty((n, D), dtype=torch.float32, device=outs.device) if out_dtype == torch.float32 else None
+    o16 = torch.empty((n, D), dtype=torch.bfloat16, device=outs.device) if out_dtype == torch.bfloat16 else None
+    lse = torch.empty((n,), dtype=torch.float32, device=outs.device)
+    _lib.check(_lib.load().bn_attn_lse_combine(outs.data_ptr(), lses.data_ptr(), P, n, D,
+                                               o32.data_ptr() if o32 is not None else None,
+                                               o16.data_ptr() if o16 is not None else None, lse.data_ptr(), _stream()))
+    return (o32 if o32 is not None else o16), lse

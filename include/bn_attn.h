@@ -1,0 +1,177 @@
+/*
+ * bn_attn.h — C ABI of the B200 (sm_100a) fused grouped-query-attention module.
+ *
+ * Drop-in boundary for BareNet's attention hot path.  Every entry point takes
+ * plain device pointers, element strides and sizes, launches on the given CUDA
+ * stream (pass 0 for the legacy default stream that all of the reference's
+ * operators use) and returns a status code; nothing here allocates device
+ * memory, synchronises the device or owns a buffer.  There is no CPU fallback:
+ * on a device that is not compute capability 10.x every call returns
+ * BN_ERR_ARCH.
+ *
+ * Reference interfaces replaced (paths relative to the reference project):
+ *   op_mm              src/ops/op_mm.cuh:39-57, op_mm_optimized.cuh:73-87
+ *   op_rope            src/ops/op_rope.cuh:101-126
+ *   op_multiply(t, c)  src/ops/op_elemwise.cuh:436-451
+ *   op_softmax         src/ops/op_softmax.cuh:153-180
+ *   op_attention_fused src/ops/op_attention_fused.cuh:109-138  (the operator
+ *                      slot: same argument meaning, never bound upstream)
+ *   the op sequence of GroupedQueryAttention.__call__
+ *                      mygrad/llama/llama_layers.py:161-183
+ *   decode semantics   mygrad/llama/llama_model.py:136-144
+ *
+ * Conventions: bf16 buffers are passed as `const void*` / `void*` holding
+ * IEEE bfloat16 bit patterns; "elements" in a stride means elements of the
+ * buffer's own type.
+ */
+#ifndef BN_ATTN_H_
+#define BN_ATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes (0 = success).  A binding converts non-zero into the
+ * reference's error convention, std::runtime_error(bn_last_error())
+ * (src/utils/check_error.cuh:8-14). */
+#define BN_OK 0
+#define BN_ERR_INVALID_ARG 1   /* null pointer, negative size, misaligned buffer */
+#define BN_ERR_UNSUPPORTED 2   /* shape outside what the kernels are built for */
+#define BN_ERR_CUDA 3          /* a CUDA runtime/driver call failed */
+#define BN_ERR_ARCH 4          /* current device is not sm_100 */
+#define BN_ERR_TIMEOUT 5       /* a bounded device-side wait ran out */
+#define BN_ERR_WORKSPACE 6     /* workspace missing or too small */
+
+/* head modes of the fp32 prefill path */
+#define BN_HEADS_COLLAPSED 0   /* the reference's semantics: ONE softmax over scores summed over all heads */
+#define BN_HEADS_PER_HEAD 1    /* standard GQA: one softmax per query head, KV head = q_head / (Hq/Hkv) */
+
+/* tokens per KV-cache page */
+#define BN_PAGE_TOKENS 16
+
+typedef void* bn_stream_t; /* a cudaStream_t */
+
+/* exported symbol (the library is built with hidden default visibility) */
+#if defined(__GNUC__)
+#define BN_API __attribute__((visibility("default")))
+#else
+#define BN_API
+#endif
+
+/* Message of the last non-zero status returned on the calling thread. */
+BN_API const char* bn_last_error(void);
+
+/* Library version (major*100 + minor). */
+BN_API int bn_version(void);
+
+/* Every device-side wait in these kernels is bounded; a kernel that gave up
+ * raises an error word at the head of the scratch buffer it was given.  This
+ * call waits for `stream`, reads that word and returns BN_OK or
+ * BN_ERR_TIMEOUT.  (It synchronises; use it in tests and after a suspected
+ * hang, not on the hot path.)  After BN_ERR_TIMEOUT the scratch buffer must be
+ * zero-filled again before reuse. */
+BN_API int bn_workspace_status(const void* workspace, bn_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * fp32 path (bit-faithful to the reference's operator arithmetic)
+ * ------------------------------------------------------------------------ */
+
+/* C(M,N) = A(M,K) @ B(K,N), fp32, arbitrary element strides (so transposed and
+ * sliced views work).  Each output is one fused-multiply-add chain with k
+ * ascending, the order of the reference's kernels.
+ * Replaces op_mm (src/ops/op_mm.cuh:39-57). */
+BN_API int bn_mm_f32(const float* A, int64_t a_rs, int64_t a_cs, const float* B, int64_t b_rs, int64_t b_cs,
+              float* C, int64_t c_rs, int64_t c_cs, int M, int K, int N, bn_stream_t stream);
+
+/* y = RoPE(x): adjacent pairs (2i, 2i+1) inside every head_dim-wide column
+ * block, row r at position r + position_offset, fp32 angles.
+ * Replaces op_rope (src/ops/op_rope.cuh:101-126). */
+BN_API int bn_rope_f32(const float* x, int64_t x_rs, int64_t x_cs, float* y, int64_t y_rs, int64_t y_cs, int rows,
+                int cols, int head_dim, float theta, int position_offset, bn_stream_t stream);
+
+/* Fused attention core, fp32:
+ *   out = softmax_causal((rope(q) @ repeat(rope(k))^T) * scale) @ repeat(v)
+ * q, out: (S, Hq*D); k, v: (S, Hkv*D); all with element strides.
+ * heads_mode BN_HEADS_COLLAPSED reproduces the reference layer exactly (one
+ * (S,S) score matrix over the full Hq*D width, one softmax); BN_HEADS_PER_HEAD
+ * applies the same operators per D-wide head.  causal: key j valid iff
+ * j <= row + position_offset (src/ops/op_softmax.cuh:88-101).  apply_rope = 0
+ * skips the rotation (inputs already rotated).  No workspace is needed.
+ * Takes the slot of op_attention_fused (src/ops/op_attention_fused.cuh:109-118)
+ * and replaces llama_layers.py:161-183. */
+BN_API int bn_attn_prefill_f32(const float* q, int64_t q_rs, int64_t q_cs, const float* k, int64_t k_rs, int64_t k_cs,
+                        const float* v, int64_t v_rs, int64_t v_cs, float* out, int64_t o_rs, int64_t o_cs,
+                        int S, int Hq, int Hkv, int D, float scale, float theta, int position_offset, int causal,
+                        int heads_mode, int apply_rope, bn_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * bf16 path (fp32 accumulation), per-head GQA
+ * ------------------------------------------------------------------------ */
+
+/* Bytes of scratch bn_attn_prefill_bf16 needs for this shape. */
+BN_API size_t bn_attn_prefill_bf16_workspace_bytes(int B, int S, int Hq, int Hkv, int D);
+
+/* Causal (or full) prefill attention with RoPE fused.
+ *   q   (B, S, Hq,  D) bf16, pre-RoPE       out (B, S, Hq, D) bf16
+ *   k,v (B, S, Hkv, D) bf16, k pre-RoPE     lse (B, Hq, S) fp32 natural log, may be NULL
+ * Row s sits at position s + position_offset; key j is valid iff
+ * j <= s + position_offset when causal.  D must be 64.  The same math as
+ * bn_attn_prefill_f32 in BN_HEADS_PER_HEAD mode on bf16 operands.
+ * Two launches: K is rotated once into the scratch buffer (it is read by every
+ * query head of its group and every query tile), then the attention kernel
+ * (tcgen05 tensor cores, TMEM accumulators, TMA-staged K/V) runs.
+ * flags: 0, or BN_PREFILL_REUSE_ROTATED_K when the scratch buffer still holds
+ * the rotated K of an earlier call on the same k / position_offset (skips the
+ * first launch). */
+#define BN_PREFILL_REUSE_ROTATED_K 0x100
+BN_API int bn_attn_prefill_bf16(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S, int Hq,
+                         int Hkv, int D, float scale, float theta, int position_offset, int causal, int flags,
+                                void* workspace, size_t workspace_bytes, bn_stream_t stream);
+
+/* Paged KV cache.  One pool per layer:
+ *   pool[page][kv_head][0=K,1=V][BN_PAGE_TOKENS][D]  bf16
+ * K is stored rotated (RoPE at the token's position), V as is.
+ * page_table (n_seqs, max_pages) int32 maps a sequence's logical page to a
+ * pool page.
+ *
+ * bn_kv_append: for t in [0,T): token of sequence seq_ids[t] at position
+ * positions[t]; k_new, v_new (T, Hkv*D) with row stride in elements; dtype 0 =
+ * fp32, 1 = bf16.  Fuses RoPE(K) (src/ops/op_rope.cuh:55-99), the bf16
+ * conversion and the page write. */
+BN_API int bn_kv_append(void* pool, int64_t pool_pages, const int32_t* page_table, int max_pages, const int32_t* seq_ids,
+                 const int32_t* positions, int T, const void* k_new, const void* v_new, int64_t kv_row_stride,
+                 int dtype, int Hkv, int D, float theta, bn_stream_t stream);
+
+/* Bytes of scratch bn_attn_decode_paged needs (split-KV partials + tickets).
+ * The scratch must be zero-filled once before its first use; the kernel leaves
+ * it clean for the next call. */
+BN_API size_t bn_attn_decode_workspace_bytes(int B, int Hq, int Hkv, int D, int max_seq_len, int chunk_tokens);
+
+/* Single-token decode over the paged cache: for every sequence b the last row
+ * of a per-head prefill over its seq_lens[b] cached tokens.
+ *   q (B, Hq, D) bf16; rope_q != 0 rotates it in-kernel at position
+ *   q_positions[b] (NULL: seq_lens[b]-1).
+ *   out (B, Hq, D) bf16 (may be NULL); out_f32 (B, Hq, D) fp32 (may be NULL);
+ *   lse (B, Hq) fp32 natural log (may be NULL; -inf for an empty sequence).
+ * The sequence is cut into chunks of chunk_tokens (0 = pick; else a multiple
+ * of 128) that run in parallel; partials are merged by a log-sum-exp combine
+ * inside the same launch.  max_seq_len bounds seq_lens (sizes the chunk grid). */
+BN_API int bn_attn_decode_paged(const void* q, const void* pool, int64_t pool_pages, const int32_t* page_table,
+                         int max_pages, const int32_t* seq_lens, const int32_t* q_positions, void* out,
+                         float* out_f32, float* lse, int B, int Hq, int Hkv, int D, float scale, float theta,
+                         int rope_q, int max_seq_len, int chunk_tokens, void* workspace, size_t workspace_bytes,
+                         bn_stream_t stream);
+
+/* Log-sum-exp merge of P partial attention results (split-KV across GPUs):
+ *   outs (P, n, D) fp32 normalised partial outputs, lses (P, n) natural log
+ *   (-inf = empty part)  ->  out_f32 (n, D) and/or out_bf16 (n, D), lse (n). */
+BN_API int bn_attn_lse_combine(const float* outs, const float* lses, int P, int64_t n, int D, float* out_f32,
+                        void* out_bf16, float* lse, bn_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BN_ATTN_H_ */
