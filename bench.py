@@ -339,5 +339,3 @@ def main():
 
 if __name__ == "__main__":
     main()
-EOF
-python bench.py --impl reference --steps 1 --warmup 1 | cut -c1-400; git add -A; git commit -qm "Oracle (numpy + C), C-ABI attention library (fp32, bf16 tcgen05 prefill, paged decode), host mirror, tests, bench" && echo committed

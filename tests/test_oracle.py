@@ -123,6 +123,18 @@ def test_oracle_matches_reference_cuda_golden(path, cref):
         got = cref.gqa_layer(g["x"], g["wq"], g["wk"], g["wv"], g["wo"], **kw)
     elif kind == "core":
         got = cref.attention_collapsed(g["q"], g["k"], g["v"], **kw)
+    elif kind == "layer_seeded":
+        import importlib.util
+        spec = importlib.util.spec_from_file_location("make_golden", os.path.join(GOLDEN, "make_golden.py"))
+        mg = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mg)
+        x, wq, wk, wv, wo = mg.layer_inputs_from_seed(int(g["seed"]), int(g["S"]), int(g["hidden"]), int(g["Hq"]),
+                                                      int(g["Hkv"]), int(g["D"]))
+        full = cref.gqa_layer(x, wq, wk, wv, wo, **kw)
+        got = full[::int(g["sub_rows"]), ::int(g["sub_cols"])]
+        err = float(np.abs(got.astype(np.float64) - g["out_sub"]).max() / float(g["out_absmax"]))
+        assert err <= 1e-5, (path, err)
+        return
     elif kind == "rope":
         got = cref.rope(g["x"], int(g["D"]), 10000.0, int(g["offset"]), inv_freq=g["inv_freq"])
     else:
