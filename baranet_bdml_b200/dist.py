@@ -1,0 +1,76 @@
+"""Multi-GPU partitioning of the attention path (one process per GPU,
+torch.distributed for the plumbing).
+
+The reference is single-GPU (no NCCL, MPI, streams or device selection anywhere
+in its tree), so everything here is new.  The path shards without any
+data-path collective except in one place:
+
+  * prefill:     (batch, KV-head group) units are independent   -> `shard_range`
+  * decode:      sequences are independent; balance by length   -> `shard_sequences_by_length`
+  * long context decode: ONE sequence is cut into contiguous token ranges, one
+    per GPU; each GPU produces normalised partial outputs and log-sum-exps for
+    its range, and the only exchange is one all-gather of (D + 1) floats per
+    (sequence, query head) followed by a local log-sum-exp merge
+                                                                 -> `sequence_split_ranges`, `combine_partials`
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import torch
+
+
+def shard_range(n_units: int, world: int, rank: int) -> Tuple[int, int]:
+    """Contiguous, balanced [lo, hi) of n_units for this rank (sizes differ by at most 1)."""
+    base, rem = divmod(int(n_units), int(world))
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)
+
+
+def shard_sequences_by_length(seq_lens: Sequence[int], world: int) -> List[List[int]]:
+    """Longest-processing-time greedy: sequences sorted by length, each given to the
+    least-loaded rank.  Returns the sequence indices of every rank (ascending)."""
+    order = sorted(range(len(seq_lens)), key=lambda i: (-int(seq_lens[i]), i))
+    load = [0] * world
+    out: List[List[int]] = [[] for _ in range(world)]
+    for i in order:
+        r = min(range(world), key=lambda j: (load[j], j))
+        out[r].append(i)
+        load[r] += int(seq_lens[i])
+    return [sorted(x) for x in out]
+
+
+def sequence_split_ranges(length: int, world: int, page_tokens: int = 16) -> List[Tuple[int, int]]:
+    """Contiguous page-aligned token ranges [t0, t1), one per rank, covering [0, length)."""
+    pages = (int(length) + page_tokens - 1) // page_tokens
+    out = []
+    for r in range(world):
+        lo, hi = shard_range(pages, world, r)
+        out.append((min(lo * page_tokens, length), min(hi * page_tokens, length)))
+    return out
+
+
+def combine_partials(out_partial: torch.Tensor, lse_partial: torch.Tensor, group=None,
+                     merge: Optional[Callable] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """out_partial (n, D) fp32 normalised over this rank's tokens, lse_partial (n,) fp32
+    natural log (-inf when the rank holds no token of the row).  One all-gather, then every
+    rank merges locally, so all ranks end with identical results.
+
+    `merge(outs[P,n,D], lses[P,n]) -> (out, lse)` defaults to the CUDA kernel
+    (bn_attn_lse_combine); CPU-only tests of the exchange pass their own."""
+    import torch.distributed as dist
+    n, D = out_partial.shape
+    packed = torch.cat([out_partial, lse_partial.reshape(n, 1)], dim=1).contiguous()
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world > 1:
+        gathered = [torch.empty_like(packed) for _ in range(world)]
+        dist.all_gather(gathered, packed, group=group)
+        allp = torch.stack(gathered)
+    else:
+        allp = packed[None]
+    outs = allp[:, :, :D].contiguous()
+    lses = allp[:, :, D].contiguous()
+    if merge is None:
+        from . import ops
+        merge = ops.lse_combine
+    return merge(outs, lses)

@@ -189,34 +189,10 @@ def time_loop(torch, fn, steps, warmup, dist=None):
     return e0.elapsed_time(e1) / steps   # ms per step
 
 
-def run_ours(args):
-    import torch
-    from baranet_bdml_b200 import ops, _lib
-    _lib.load()   # fails loudly if the CUDA library is missing
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist_mod
-        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
-        dist = dist_mod
-    pk = peaks()
+def measure_prefill(torch, ops, args, rank, world, dist, reduce_max, pk):
     c = PREFILL
     B, S, Hq, Hkv, D = c["B"], c["S"], c["Hq"], c["Hkv"], c["D"]
-
-    def reduce_max(x):
-        if dist is None:
-            return x
-        t = torch.tensor([x], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    sampler = ClockSampler(local)
-    result = {}
-
-    # ---------------- prefill: rotate over 3 input sets (3 x 151 MB > 126 MB L2)
+    # rotate over 3 input sets (3 x 151 MB > 126 MB L2)
     n_sets = 3
     g = torch.Generator(device="cuda").manual_seed(1234 + rank)
     sets = []
@@ -235,34 +211,34 @@ def run_ours(args):
         q, k, v, o, ws = sets[i % n_sets]
         ops.attn_prefill_bf16(q, k, v, out=o, workspace=ws, reuse_rotated_k=True)
 
-    if rank == 0:
-        sampler.start()
     ms_step = reduce_max(time_loop(torch, step, args.steps, args.warmup, dist))
     ms_kernel = time_loop(torch, kernel_only, args.steps, max(3, args.warmup))   # attention kernel alone
     for s in sets:
         s[4].status()
 
-    # ---------------- end to end: pinned host buffers, H2D + kernel + D2H inside the timed region
-    hq = torch.randn((B, S, Hq, D)).to(torch.bfloat16).pin_memory()
-    hk = torch.randn((B, S, Hkv, D)).to(torch.bfloat16).pin_memory()
-    hv = torch.randn((B, S, Hkv, D)).to(torch.bfloat16).pin_memory()
-    ho = torch.empty((B, S, Hq, D), dtype=torch.bfloat16).pin_memory()
-    dq, dk, dv, do, dws = sets[0]
+    # end to end: pinned host buffers, H2D + kernels + D2H inside the timed region
+    ms_e2e, h2d, d2h = None, 0, 0
+    if not args.no_e2e:
+        hq = torch.randn((B, S, Hq, D)).to(torch.bfloat16).pin_memory()
+        hk = torch.randn((B, S, Hkv, D)).to(torch.bfloat16).pin_memory()
+        hv = torch.randn((B, S, Hkv, D)).to(torch.bfloat16).pin_memory()
+        ho = torch.empty((B, S, Hq, D), dtype=torch.bfloat16).pin_memory()
+        dq, dk, dv, do, dws = sets[0]
 
-    def e2e_step(i):
-        dq.copy_(hq, non_blocking=True)
-        dk.copy_(hk, non_blocking=True)
-        dv.copy_(hv, non_blocking=True)
-        ops.attn_prefill_bf16(dq, dk, dv, out=do, workspace=dws)
-        ho.copy_(do, non_blocking=True)
+        def e2e_step(i):
+            dq.copy_(hq, non_blocking=True)
+            dk.copy_(hk, non_blocking=True)
+            dv.copy_(hv, non_blocking=True)
+            ops.attn_prefill_bf16(dq, dk, dv, out=do, workspace=dws)
+            ho.copy_(do, non_blocking=True)
 
-    ms_e2e = reduce_max(time_loop(torch, e2e_step, args.steps, args.warmup, dist))
-    clocks = sampler.stop() if rank == 0 else None
+        ms_e2e = reduce_max(time_loop(torch, e2e_step, args.steps, args.warmup, dist))
+        h2d = (hq.numel() + hk.numel() + hv.numel()) * 2
+        d2h = ho.numel() * 2
 
     flops = prefill_flops()
-    h2d = (hq.numel() + hk.numel() + hv.numel()) * 2
-    d2h = ho.numel() * 2
-    result = {
+    ach = flops / (ms_kernel * 1e-3) / 1e12
+    return {
         "metric": "prefill_attention_tflops", "value": flops * world / (ms_step * 1e-3) / 1e12, "unit": "TFLOP/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
@@ -272,47 +248,79 @@ def run_ours(args):
                    "global_batch": B * world, "seq_len": S, "parallelism": f"batch-sharded x{world}, no collective",
                    "l2": f"inputs rotate over {n_sets} buffer sets of 151 MB each (> 126 MB L2)",
                    "flops_per_step_per_gpu": flops, "launches_per_step": 2},
-        "roofline": {"bound": "tensor", "achieved": flops / (ms_kernel * 1e-3) / 1e12, "peak": pk["tensor"],
-                     "unit": "TFLOP/s", "frac": flops / (ms_kernel * 1e-3) / 1e12 / pk["tensor"], "traffic": None,
-                     "peak_source": pk["source"] + " (bf16 burst)", "kernel": "prefill_kernel",
-                     "kernel_ms": ms_kernel},
-        "e2e": {"value": flops * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
+        "roofline": {"bound": "tensor", "achieved": ach, "peak": pk["tensor"], "unit": "TFLOP/s",
+                     "frac": ach / pk["tensor"], "traffic": None, "peak_source": pk["source"] + " (bf16 burst)",
+                     "kernel": "prefill_kernel", "kernel_ms": ms_kernel},
+        "e2e": None if ms_e2e is None else {
+            "value": flops * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
         "gpu_launches": 2 * args.steps,
-        "clocks": clocks,
     }
 
-    # ---------------- decode (config 3) as a second measurement on the same line
-    try:
-        dsets = 8   # 8 x ~168 MB of cache: every launch reads HBM-cold data
-        caches, q, bytes_alg, tokens = make_decode_case(torch, 77 + rank, dsets)
-        outs = torch.empty((DECODE["B"], DECODE["Hq"], DECODE["D"]), dtype=torch.bfloat16, device="cuda")
 
-        def dstep(i):
-            caches[i % dsets].decode(q, num_heads=DECODE["Hq"], out=outs, max_seq_len=DECODE["Lmax"], rope_q=True)
+def measure_decode(torch, args, rank, world, dist, reduce_max, pk):
+    dsets = 8   # 8 x ~168 MB of cache: every launch reads HBM-cold data
+    caches, q, bytes_alg, tokens = make_decode_case(torch, 77 + rank, dsets)
+    outs = torch.empty((DECODE["B"], DECODE["Hq"], DECODE["D"]), dtype=torch.bfloat16, device="cuda")
 
-        dsteps = max(args.steps, 16)
-        ms_dec = reduce_max(time_loop(torch, dstep, dsteps, max(3, args.warmup), dist))
-        for cch in caches:
-            cch._ws.status()
-        gbs = bytes_alg / (ms_dec * 1e-3) / 1e9
-        result["decode"] = {
-            "metric": "decode_attention_hbm_gbs", "value": gbs * world, "unit": "GB/s", "ms_per_step": ms_dec,
-            "steps": dsteps,
-            "config": {"workload": "paged decode, BASELINE config 3: per GPU batch 64, one token per sequence, bf16 "
-                                   "KV cache in 16-token pages (permuted page table), lengths uniform in [1024,4096]",
-                       "tokens_in_cache": tokens, "algorithmic_bytes_per_step": bytes_alg,
-                       "l2": f"{dsets} distinct caches rotate"},
-            "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s", "frac": gbs / pk["hbm"],
-                         "traffic": None, "peak_source": pk["source"], "kernel": "decode_paged_kernel"},
-            "gpu_launches": dsteps,
-        }
-        del caches
-    except Exception as e:  # the headline must still print
-        result["decode"] = {"error": repr(e)}
+    def dstep(i):
+        caches[i % dsets].decode(q, num_heads=DECODE["Hq"], out=outs, max_seq_len=DECODE["Lmax"], rope_q=True)
 
+    dsteps = max(args.steps, 16)
+    ms_dec = reduce_max(time_loop(torch, dstep, dsteps, max(3, args.warmup), dist))
+    for cch in caches:
+        cch._ws.status()
+    gbs = bytes_alg / (ms_dec * 1e-3) / 1e9
+    return {
+        "metric": "decode_attention_hbm_gbs", "value": gbs * world, "unit": "GB/s", "ms_per_step": ms_dec,
+        "steps": dsteps, "n_gpus": world,
+        "config": {"workload": "paged decode, BASELINE config 3: per GPU batch 64, one token per sequence, bf16 "
+                               "KV cache in 16-token pages (permuted page table), lengths uniform in [1024,4096]",
+                   "tokens_in_cache": tokens, "algorithmic_bytes_per_step": bytes_alg,
+                   "l2": f"{dsets} distinct caches rotate"},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s", "frac": gbs / pk["hbm"],
+                     "traffic": None, "peak_source": pk["source"], "kernel": "decode_paged_kernel"},
+        "gpu_launches": dsteps,
+    }
+
+
+def run_ours(args):
+    import torch
+    from baranet_bdml_b200 import ops, _lib
+    _lib.load()   # fails loudly if the CUDA library is missing
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist = dist_mod
+    pk = peaks()
+
+    def reduce_max(x):
+        if dist is None:
+            return x
+        t = torch.tensor([x], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    sampler = ClockSampler(local)
     if rank == 0:
-        if world == 1 and not args.no_cpu_baseline:
+        sampler.start()
+    if args.decode_only:
+        result = measure_decode(torch, args, rank, world, dist, reduce_max, pk)
+    else:
+        result = measure_prefill(torch, ops, args, rank, world, dist, reduce_max, pk)
+        if not args.no_decode:
+            try:
+                result["decode"] = measure_decode(torch, args, rank, world, dist, reduce_max, pk)
+            except Exception as e:  # the headline must still print
+                result["decode"] = {"error": repr(e)}
+    if rank == 0:
+        result["clocks"] = sampler.stop()
+        if world == 1 and not args.no_cpu_baseline and not args.decode_only:
             r = cpu_prefill_sample(n_batches=2)
             result["cpu_baseline"] = {"value": r["value"], "unit": "TFLOP/s", "cores": r["cores"], "kind": "port",
                                       "sample": r["sample"], "seconds": r["seconds"]}
@@ -328,6 +336,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end measurement")
+    ap.add_argument("--no-decode", action="store_true", help="skip the config-3 decode measurement")
+    ap.add_argument("--decode-only", action="store_true",
+                    help="run only the decode measurement (for profiling); prints its object alone")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
