@@ -266,7 +266,7 @@ def measure_decode(torch, args, rank, world, dist, reduce_max, pk):
     def dstep(i):
         caches[i % dsets].decode(q, num_heads=DECODE["Hq"], out=outs, max_seq_len=DECODE["Lmax"], rope_q=True)
 
-    dsteps = max(args.steps, 16)
+    dsteps = args.steps if args.decode_only else max(args.steps, 16)
     ms_dec = reduce_max(time_loop(torch, dstep, dsteps, max(3, args.warmup), dist))
     for cch in caches:
         cch._ws.status()
@@ -332,8 +332,8 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end measurement")
