@@ -11,7 +11,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libbn_attn.so")
+# BN_ATTN_LIB names another build of the same library (e.g. an instrumented one)
+LIB_PATH = os.environ.get("BN_ATTN_LIB") or os.path.join(_HERE, "libbn_attn.so")
 
 BN_OK, BN_ERR_INVALID_ARG, BN_ERR_UNSUPPORTED, BN_ERR_CUDA, BN_ERR_ARCH, BN_ERR_TIMEOUT, BN_ERR_WORKSPACE = range(7)
 BN_HEADS_COLLAPSED, BN_HEADS_PER_HEAD = 0, 1

@@ -24,12 +24,12 @@ def _stale() -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    if not force and not _stale():
+def build(force: bool = False, verbose: bool = False, extra_flags=(), out: str = LIB) -> str:
+    if out == LIB and not force and not _stale():
         return LIB
     nvcc = os.environ.get("NVCC", "nvcc")
     cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + \
-          [os.path.join(CSRC, s) for s in SOURCES] + ["-o", LIB]
+          list(extra_flags) + [os.path.join(CSRC, s) for s in SOURCES] + ["-o", out]
     env = dict(os.environ)
     # the image exports CC/CXX wrappers that lack some spec files; nvcc should use the system g++
     env.pop("CC", None)
@@ -39,7 +39,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         sys.stderr.write(res.stdout + res.stderr)
     if res.returncode != 0:
         raise RuntimeError("nvcc failed building libbn_attn.so")
-    return LIB
+    return out
 
 
 if __name__ == "__main__":

@@ -23,6 +23,7 @@
 //   * Every wait is bounded; on expiry the kernel raises the error word in the
 //     scratch header and returns.
 #include <math.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -32,6 +33,9 @@ namespace bn {
 
 using namespace ptx;
 
+#ifndef BN_DDBG
+#define BN_DDBG 0
+#endif
 constexpr int DEC_D = 64;
 constexpr int DEC_G = 8;                    // query heads per KV head served by one MMA (n = 8)
 constexpr int DEC_STAGE_TOKENS = 128;
@@ -91,7 +95,7 @@ struct DecodeParams {
     DecodeHeader* hdr;
     int* tickets;
     float *part_m, *part_l, *part_o;
-    int B, Hq, Hkv, n_rep, max_pages, max_seq_len, chunk, max_chunks, total_items, rope_q;
+    int B, Hq, Hkv, n_rep, max_pages, max_seq_len, chunk, max_chunks, total_items, rope_q, debug;
     float scale_log2, theta;
 };
 
@@ -162,7 +166,11 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
                 }
                 __syncwarp();
                 if (lane < npages) {
+#if (BN_DDBG & 2)
+                    const int page = (b * 61 + ts / BN_PAGE_TOKENS + lane) & 8191;
+#else
                     const int page = p.page_table[(size_t)b * p.max_pages + ts / BN_PAGE_TOKENS + lane];
+#endif
                     tma_load_2d(ring + stage * DEC_STAGE_BYTES + lane * DEC_BOX_BYTES, &tmap, 0,
                                 (page * p.Hkv + g) * DEC_BOX_ROWS, fb);
                 }
@@ -249,6 +257,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
         for (int pi = 0; pi < 2; ++pi) {
             const int pg = warp * 2 + pi;
             nv[pi] = max(0, min(BN_PAGE_TOKENS, mt.ntok - pg * BN_PAGE_TOKENS));
+            if (p.debug & 1) nv[pi] = 0;
             const uint32_t box = sbase + pg * DEC_BOX_BYTES;
 #pragma unroll
             for (int j = 0; j < 4; ++j) s[pi][j] = 0.f;
@@ -322,6 +331,9 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
         if (++stage == DEC_NSTAGES) { stage = 0; phase ^= 1u; }
 
         if (!mt.last) continue;
+#if (BN_DDBG & 4)
+        continue;
+#endif
 
         // ------------------------------------------------ merge the 4 warps
 #pragma unroll
@@ -504,6 +516,7 @@ extern "C" int bn_attn_decode_paged(const void* q, const void* pool, int64_t poo
     p.chunk = chunk; p.max_chunks = L.max_chunks;
     p.total_items = B * Hkv * L.max_chunks;
     p.rope_q = rope_q;
+    { const char* e = getenv("BN_DECODE_DEBUG"); p.debug = e ? atoi(e) : 0; }
     p.scale_log2 = scale * LOG2E;
     p.theta = theta;
 

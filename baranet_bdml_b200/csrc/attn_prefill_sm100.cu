@@ -37,6 +37,9 @@ namespace bn {
 
 using namespace ptx;
 
+#ifndef BN_DBG
+#define BN_DBG 0
+#endif
 constexpr int PF_D = 64;
 constexpr int PF_BM = 128;           // query rows per CTA
 constexpr int PF_BN = 128;           // keys per tile
@@ -66,23 +69,33 @@ static PrefillWsLayout prefill_layout(int B, int S, int Hkv) {
 // ---------------------------------------------------------------------------
 // launch 1: K rotation + cos/sin table
 // ---------------------------------------------------------------------------
-__global__ void rope_k_kernel(const __nv_bfloat16* __restrict__ k, __nv_bfloat16* __restrict__ krot,
-                              float2* __restrict__ table, int B, int S, int Hkv, float theta, int position_offset,
-                              int* __restrict__ error_word) {
-    const int s = blockIdx.x, b = blockIdx.y;
-    if (s == 0 && b == 0 && threadIdx.x == 0) *error_word = 0;
-    const int pairs = Hkv * (PF_D / 2);
-    for (int e = threadIdx.x; e < pairs; e += blockDim.x) {
-        const int i = e % (PF_D / 2);
+constexpr int RK_POS = 8;   // positions per block
+
+__global__ void __launch_bounds__(256)
+rope_k_kernel(const __nv_bfloat16* __restrict__ k, __nv_bfloat16* __restrict__ krot, float2* __restrict__ table, int B,
+              int S, int Hkv, float theta, int position_offset, int* __restrict__ error_word) {
+    __shared__ float2 cs[RK_POS][PF_D / 2];
+    const int s0 = blockIdx.x * RK_POS, b = blockIdx.y;
+    if (blockIdx.x == 0 && b == 0 && threadIdx.x == 0) *error_word = 0;
+    {
+        const int ds = threadIdx.x / (PF_D / 2), i = threadIdx.x % (PF_D / 2);
         const float freq = rope_inv_freq(i, PF_D, theta);
-        const float angle = (s + position_offset) * freq;
-        const float cos_angle = cosf(angle), sin_angle = sinf(angle);
-        if (b == 0 && e < PF_D / 2) table[(size_t)s * (PF_D / 2) + i] = make_float2(cos_angle, sin_angle);
-        const size_t idx = ((size_t)b * S + s) * Hkv * PF_D + 2 * e;
+        const float angle = (s0 + ds + position_offset) * freq;
+        const float2 v = make_float2(cosf(angle), sinf(angle));
+        cs[ds][i] = v;
+        if (b == 0 && s0 + ds < S) table[(size_t)(s0 + ds) * (PF_D / 2) + i] = v;
+    }
+    __syncthreads();
+    const int pairs = Hkv * (PF_D / 2);
+    for (int e = threadIdx.x; e < RK_POS * pairs; e += blockDim.x) {
+        const int ds = e / pairs, r = e % pairs, i = r % (PF_D / 2);
+        if (s0 + ds >= S) break;
+        const float2 v = cs[ds][i];
+        const size_t idx = ((size_t)b * S + s0 + ds) * Hkv * PF_D + 2 * r;
         const uint32_t raw = *reinterpret_cast<const uint32_t*>(k + idx);
         const float x0 = bf16_lo(raw), x1 = bf16_hi(raw);
-        const float y0 = x0 * cos_angle - x1 * sin_angle;
-        const float y1 = x0 * sin_angle + x1 * cos_angle;
+        const float y0 = x0 * v.x - x1 * v.y;
+        const float y1 = x0 * v.y + x1 * v.x;
         *reinterpret_cast<uint32_t*>(krot + idx) = pack_bf16(y0, y1);
     }
 }
@@ -101,7 +114,7 @@ struct PrefillParams {
 };
 
 __global__ void __launch_bounds__(PF_THREADS, 2)
-prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+prefill_kernel_v1(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                const PrefillParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_q, bar_s, bar_p, bar_o;
@@ -266,7 +279,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant
             for (int c = 0; c < 4; ++c) {
                 uint32_t r[32];
                 tc::ld32(tmem + lane_base + PF_COL_S + c * 32, r);
-                tc::wait_ld();
+                tc::wait_ld(r);
                 if (need_mask) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
@@ -289,7 +302,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant
                     for (int c = 0; c < 2; ++c) {
                         uint32_t r[32];
                         tc::ld32(tmem + lane_base + PF_COL_O + c * 32, r);
-                        tc::wait_ld();
+                        tc::wait_ld(r);
 #pragma unroll
                         for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
                         tc::st32(tmem + lane_base + PF_COL_O + c * 32, r);
@@ -304,7 +317,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant
             for (int c = 0; c < 4; ++c) {
                 uint32_t r[32];
                 tc::ld32(tmem + lane_base + PF_COL_S + c * 32, r);
-                tc::wait_ld();
+                tc::wait_ld(r);
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
@@ -335,7 +348,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant
                 uint32_t r[32];
                 if (n_tiles > 0) {
                     tc::ld32(tmem + lane_base + PF_COL_O + c * 32, r);
-                    tc::wait_ld();
+                    tc::wait_ld(r);
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) r[i] = 0;
@@ -368,6 +381,401 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant
     }
 }
 
+
+// ---------------------------------------------------------------------------
+// launch 2, main kernel: one CTA per SM-slot, TWO query tiles in flight
+// ---------------------------------------------------------------------------
+// CTA = (batch, query head, pair of 128-row query tiles).  Ten warps:
+//   warps 0-3  softmax group 0 (query tile 2t)      warp 8  MMA issuer
+//   warps 4-7  softmax group 1 (query tile 2t+1)    warp 9  TMA producer
+// Both tiles read the same K/V stages, so each K/V tile is fetched once per
+// 256 query rows, and the tensor pipe works on one tile (P V, then the next
+// Q K^T) while the other tile's softmax runs.
+// TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,320) O1 [320,384)
+//                     P0 [384,448) P1 [448,512)
+// Softmax is ONE pass per tile: the exponent reference is the running maximum
+// of the earlier tiles; if a tile turns out to exceed it by more than 2^8 (or it
+// is the first tile) the warp rescales O, moves the reference and redoes the
+// tile.  A quarter of the exponentials is evaluated on the FMA pipe (Cody-Waite
+// split + degree-3 polynomial) because at head_dim 64 the MUFU unit, not the
+// tensor pipe, is the first limit.
+constexpr int P2_THREADS = 320;
+constexpr int P2_NSTAGE = 4;
+constexpr int P2_SMEM_BYTES = 1024 + PF_TILE_BYTES * (2 + 2 * P2_NSTAGE);
+constexpr uint32_t P2_TMEM_COLS = 512;
+
+__device__ __forceinline__ float ex2_fma_pipe(float x) {
+    // 2^x for x <= ~8: n = round(x) via the 1.5*2^23 trick, 2^(x-n) by a cubic (rel. err 7.5e-5),
+    // then n is added to the exponent field
+    x = fmaxf(x, -125.0f);
+    const float t = x + 12582912.0f;
+    const float f = x - (t - 12582912.0f);
+    float p = fmaf(f, 0.0551716499f, 0.2426111251f);
+    p = fmaf(p, f, 0.6932609677f);
+    p = fmaf(p, f, 0.9999280572f);
+    return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
+// exp2 of 32 scores -> 16 packed bf16x2; returns the row-sum contribution.  `pmax` tracks the largest p (packed).
+template <bool MASK>
+__device__ __forceinline__ float softmax_chunk(const uint32_t (&r)[32], uint32_t (&pk)[16], float scale_log2,
+                                               float mneg, int first_key, int row_last, uint32_t& pmax) {
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+        const float x0 = fmaf(__uint_as_float(r[i]), scale_log2, mneg);
+        const float x1 = fmaf(__uint_as_float(r[i + 1]), scale_log2, mneg);
+#if (BN_DBG & 4)
+        float p0 = x0, p1 = x1;
+#elif (BN_DBG & 1)
+        float p0 = ex2(x0), p1 = ex2(x1);
+#else
+        float p0 = ((i & 7) == 6) ? ex2_fma_pipe(x0) : ex2(x0);
+        float p1 = ((i & 7) == 6) ? ex2_fma_pipe(x1) : ex2(x1);
+#endif
+        if (MASK) {
+            if (first_key + i > row_last) p0 = 0.f;
+            if (first_key + i + 1 > row_last) p1 = 0.f;
+        }
+        sum += p0 + p1;
+        pk[i / 2] = pack_bf16(p0, p1);
+#if !(BN_DBG & 8)
+        asm("max.bf16x2 %0, %0, %1;" : "+r"(pmax) : "r"(pk[i / 2]));
+#endif
+    }
+    return sum;
+}
+
+__global__ void __launch_bounds__(P2_THREADS, 1)
+prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+               const PrefillParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar_q[2], bar_s[2], bar_p[2], bar_o[2];
+    __shared__ __align__(8) uint64_t bar_kfull[P2_NSTAGE], bar_vfull[P2_NSTAGE], bar_empty[P2_NSTAGE];
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort;
+
+    const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sQ = smem0;                                        // 2 tiles
+    const uint32_t sK = smem0 + PF_TILE_BYTES * 2;                    // P2_NSTAGE tiles
+    const uint32_t sV = smem0 + PF_TILE_BYTES * (2 + P2_NSTAGE);      // P2_NSTAGE tiles
+
+    // work unit: heaviest (latest) pair of query tiles first; the heads of a KV group are neighbours
+    const int BH = p.B * p.Hq;
+    const int n_pairs = (p.n_qtiles + 1) / 2;
+    const int qp = n_pairs - 1 - (int)(blockIdx.x / BH);
+    const int bh = blockIdx.x % BH;
+    const int b = bh / p.Hq, h = bh % p.Hq, g = h / p.n_rep;
+    const int n_ktiles_all = (p.S + PF_BN - 1) / PF_BN;
+    int n_t[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int i0 = (2 * qp + u) * PF_BM;
+        if (i0 >= p.S) { n_t[u] = 0; continue; }
+        n_t[u] = p.causal ? min(n_ktiles_all, (i0 + PF_BM - 1 + p.position_offset) / PF_BN + 1) : n_ktiles_all;
+    }
+    const int n_max = max(n_t[0], n_t[1]);
+
+    if (tid == 0) {
+        for (int u = 0; u < 2; ++u) {
+            mbar_init(smem_u32(&bar_q[u]), 128);
+            mbar_init(smem_u32(&bar_s[u]), 1);
+            mbar_init(smem_u32(&bar_p[u]), (BN_DBG & 2) ? 4 : 128);
+            mbar_init(smem_u32(&bar_o[u]), 1);
+        }
+        for (int s = 0; s < P2_NSTAGE; ++s) {
+            mbar_init(smem_u32(&bar_kfull[s]), 1);
+            mbar_init(smem_u32(&bar_vfull[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        s_abort = 0;
+        fence_mbar_init();
+    }
+    if (warp == 8) {
+        tc::tmem_alloc(smem_u32(&s_tmem_base), P2_TMEM_COLS);
+        tc::tmem_relinquish();
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem = s_tmem_base;
+
+    if (warp == 9) {
+        // ---------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            prefetch_tensormap(&tmap_k);
+            prefetch_tensormap(&tmap_v);
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int j = 0; j < n_max; ++j) {
+                if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &s_abort)) break;
+                mbar_arrive_expect_tx(smem_u32(&bar_kfull[stage]), PF_TILE_BYTES);
+                tma_load_4d(sK + stage * PF_TILE_BYTES, &tmap_k, 0, g, j * PF_BN, b, smem_u32(&bar_kfull[stage]));
+                mbar_arrive_expect_tx(smem_u32(&bar_vfull[stage]), PF_TILE_BYTES);
+                tma_load_4d(sV + stage * PF_TILE_BYTES, &tmap_v, 0, g, j * PF_BN, b, smem_u32(&bar_vfull[stage]));
+                if (++stage == P2_NSTAGE) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 8) {
+        // ------------------------------------------------------------ MMA issuer
+        constexpr uint32_t IDESC_QK = tc::idesc_bf16(PF_BM, PF_BN, 0);
+        constexpr uint32_t IDESC_PV = tc::idesc_bf16(PF_BM, PF_D, 1);
+        auto issue_qk = [&](int u, int stage) {
+            if (lane == 0) {
+                tc::fence_after_sync();
+#if !(BN_DBG & 64)
+#pragma unroll
+                for (int kk = 0; kk < PF_D / 16; ++kk)
+                    tc::mma_ss(tmem + u * 128, tc::smem_desc_sw128(sQ + u * PF_TILE_BYTES + kk * 32),
+                               tc::smem_desc_sw128(sK + stage * PF_TILE_BYTES + kk * 32), IDESC_QK, kk > 0);
+#endif
+                tc::commit(smem_u32(&bar_s[u]));
+            }
+            __syncwarp();
+        };
+        bool ok = true;
+        for (int u = 0; u < 2 && ok; ++u)
+            if (n_t[u] > 0) ok = mbar_wait(smem_u32(&bar_q[u]), 0, &s_abort);
+        if (ok && n_max > 0) ok = mbar_wait(smem_u32(&bar_kfull[0]), 0, &s_abort);
+        if (ok) {
+            if (n_t[0] > 0) issue_qk(0, 0);
+            if (n_t[1] > 0) issue_qk(1, 0);
+        }
+        int stage = 0;
+        uint32_t phase = 0;
+        for (int j = 0; ok && j < n_max; ++j) {
+            const int nstage = (stage + 1 == P2_NSTAGE) ? 0 : stage + 1;
+            const uint32_t nphase = (stage + 1 == P2_NSTAGE) ? phase ^ 1u : phase;
+            bool next_k_ready = false;
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                if (j >= n_t[u]) continue;
+                // O_u += P_u(j) V(j)
+                ok = mbar_wait(smem_u32(&bar_p[u]), j & 1, &s_abort) &&
+                     mbar_wait(smem_u32(&bar_vfull[stage]), phase, &s_abort);
+                if (!ok) break;
+                if (lane == 0) {
+                    tc::fence_after_sync();
+#if !(BN_DBG & 64)
+#pragma unroll
+                    for (int kk = 0; kk < PF_BN / 16; ++kk)
+                        tc::mma_ts(tmem + 256 + u * 64, tmem + 384 + u * 64 + kk * 8,
+                                   tc::smem_desc_sw128(sV + stage * PF_TILE_BYTES + kk * 2048), IDESC_PV,
+                                   (j > 0) || (kk > 0));
+#endif
+                    if (j == n_t[u] - 1) tc::commit(smem_u32(&bar_o[u]));
+                    const bool last_user = (u == 1) || (j >= n_t[1]);
+                    if (last_user) tc::commit(smem_u32(&bar_empty[stage]));   // K(j)/V(j) may be overwritten
+                }
+                __syncwarp();
+                // S_u(j+1) = Q_u K(j+1)^T: its S columns are free because P_u(j) has been written
+                if (j + 1 < n_t[u]) {
+                    if (!next_k_ready) {
+                        ok = mbar_wait(smem_u32(&bar_kfull[nstage]), nphase, &s_abort);
+                        if (!ok) break;
+                        next_k_ready = true;
+                    }
+                    issue_qk(u, nstage);
+                }
+            }
+            stage = nstage;
+            phase = nphase;
+        }
+    } else {
+        // ------------------------------------------- softmax groups (warps 0..7)
+        const int u = warp / 4;                     // which query tile
+        const int row = tid % 128;                  // TMEM lane = query row inside the tile
+        const int i0 = (2 * qp + u) * PF_BM;
+        const int gi = i0 + row;
+        const int nt = n_t[u];
+        const uint32_t lane_base = ((uint32_t)((warp % 4) * 32)) << 16;
+        const uint32_t tS = tmem + lane_base + u * 128;
+        const uint32_t tO = tmem + lane_base + 256 + u * 64;
+        const uint32_t tP = tmem + lane_base + 384 + u * 64;
+
+        if (nt > 0) {
+            // prologue: rotate the Q row and store it, 128-byte-swizzled, K-major
+            uint4 qv[8];
+            const bool valid = gi < p.S;
+            const uint4* src = reinterpret_cast<const uint4*>(p.q + (((size_t)b * p.S + (valid ? gi : 0)) * p.Hq + h) * PF_D);
+            const float4* tab = reinterpret_cast<const float4*>(p.table + (size_t)(valid ? gi : 0) * (PF_D / 2));
+#pragma unroll
+            for (int c = 0; c < 8; ++c) qv[c] = valid ? __ldg(src + c) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                uint32_t w[4] = {qv[c].x, qv[c].y, qv[c].z, qv[c].w};
+#pragma unroll
+                for (int e = 0; e < 4; e += 2) {
+                    const float4 cs = __ldg(tab + c * 2 + e / 2);
+                    float x0 = bf16_lo(w[e]), x1 = bf16_hi(w[e]);
+                    w[e] = pack_bf16(x0 * cs.x - x1 * cs.y, x0 * cs.y + x1 * cs.x);
+                    x0 = bf16_lo(w[e + 1]); x1 = bf16_hi(w[e + 1]);
+                    w[e + 1] = pack_bf16(x0 * cs.z - x1 * cs.w, x0 * cs.w + x1 * cs.z);
+                }
+                const uint32_t dst = sQ + u * PF_TILE_BYTES + row * 128 + ((c ^ (row & 7)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                             : "memory");
+            }
+            fence_proxy_async_smem();
+            mbar_arrive(smem_u32(&bar_q[u]));
+        }
+
+        float m_ref = -INFINITY;   // exponent reference, raw score units
+        float l_run = 0.f;
+        bool ok = true;
+        const int row_last = p.causal ? min(p.S - 1, gi + p.position_offset) : p.S - 1;
+        const int tile_free_last = p.causal ? min(p.S - 1, i0 + p.position_offset) : p.S - 1;   // no mask needed up to here
+
+        for (int j = 0; j < nt; ++j) {
+            ok = mbar_wait(smem_u32(&bar_s[u]), j & 1, &s_abort);
+            if (!ok) break;
+            tc::fence_after_sync();
+            const int j0 = j * PF_BN;
+            const bool need_mask = (j0 + PF_BN - 1) > tile_free_last;
+
+            // row maximum of this tile (raw score units), by re-reading S: first tile and the rare redo only
+            auto tile_max = [&]() {
+                float tmax = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t r[32];
+                    tc::ld32(tS + c * 32, r);
+                    tc::wait_ld(r);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (!need_mask || j0 + c * 32 + i <= row_last) tmax = fmaxf(tmax, __uint_as_float(r[i]));
+                }
+                return tmax;
+            };
+            // one pass over the tile: P = exp2(S * scale_log2 - m_ref * scale_log2) -> TMEM, with the load of the
+            // next 32 columns in flight while the current 32 are processed
+            auto tile_pass = [&](float mneg, uint32_t& pmax) {
+                float lsum = 0.f;
+                uint32_t r0[32], r1[32], pk[16];
+                tc::ld32(tS + 0, r0);
+                tc::wait_ld(r0);
+                tc::ld32(tS + 32, r1);
+                lsum += need_mask ? softmax_chunk<true>(r0, pk, p.scale_log2, mneg, j0, row_last, pmax)
+                                  : softmax_chunk<false>(r0, pk, p.scale_log2, mneg, j0, row_last, pmax);
+#if !(BN_DBG & 16)
+                tc::st16(tP + 0, pk);
+#endif
+                tc::wait_ld(r1);
+                tc::ld32(tS + 64, r0);
+                lsum += need_mask ? softmax_chunk<true>(r1, pk, p.scale_log2, mneg, j0 + 32, row_last, pmax)
+                                  : softmax_chunk<false>(r1, pk, p.scale_log2, mneg, j0 + 32, row_last, pmax);
+#if !(BN_DBG & 16)
+                tc::st16(tP + 16, pk);
+#endif
+                tc::wait_ld(r0);
+                tc::ld32(tS + 96, r1);
+                lsum += need_mask ? softmax_chunk<true>(r0, pk, p.scale_log2, mneg, j0 + 64, row_last, pmax)
+                                  : softmax_chunk<false>(r0, pk, p.scale_log2, mneg, j0 + 64, row_last, pmax);
+#if !(BN_DBG & 16)
+                tc::st16(tP + 32, pk);
+#endif
+                tc::wait_ld(r1);
+                lsum += need_mask ? softmax_chunk<true>(r1, pk, p.scale_log2, mneg, j0 + 96, row_last, pmax)
+                                  : softmax_chunk<false>(r1, pk, p.scale_log2, mneg, j0 + 96, row_last, pmax);
+#if !(BN_DBG & 16)
+                tc::st16(tP + 48, pk);
+#endif
+                return lsum;
+            };
+
+#if (BN_DBG & 32)
+            uint32_t pmax = 0;
+            float lsum = 1.f;
+#else
+            if (j == 0) {
+                const float tmax = tile_max();
+                if (tmax > -INFINITY) m_ref = tmax;
+            }
+            uint32_t pmax = 0;           // bf16x2 (+0, +0)
+            float lsum = tile_pass(m_ref == -INFINITY ? 0.f : -m_ref * p.scale_log2, pmax);
+#endif
+            // did any p leave the safe range (> 2^8, incl. inf/NaN)?  bf16 bit patterns are monotone for p >= 0
+            const bool over = max(pmax & 0xffffu, pmax >> 16) > 0x4380u;   // bf16(256.0)
+            if (__any_sync(0xffffffffu, over)) {
+                // rare: the tile exceeds the reference by more than 2^8.  Move the reference to the true row
+                // maximum, rescale O and l, redo the tile.
+                const float m_new = fmaxf(m_ref, tile_max());
+                const float m_upd = m_new == -INFINITY ? m_ref : m_new;
+                if (j > 0) {
+                    const float alpha = m_ref == -INFINITY ? 0.f : ex2((m_ref - m_upd) * p.scale_log2);
+                    l_run *= alpha;
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        uint32_t ro[32];
+                        tc::ld32(tO + c * 32, ro);
+                        tc::wait_ld(ro);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) ro[i] = __float_as_uint(__uint_as_float(ro[i]) * alpha);
+                        tc::st32(tO + c * 32, ro);
+                    }
+                }
+                m_ref = m_upd;
+                pmax = 0;
+                lsum = tile_pass(m_ref == -INFINITY ? 0.f : -m_ref * p.scale_log2, pmax);
+            }
+            l_run += lsum;
+            tc::wait_st();
+            tc::fence_before_sync();
+#if (BN_DBG & 2)
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_p[u]));
+#else
+            mbar_arrive(smem_u32(&bar_p[u]));
+#endif
+        }
+
+        // epilogue: O / l -> bf16 -> global
+        if (ok && nt > 0) ok = mbar_wait(smem_u32(&bar_o[u]), 0, &s_abort);
+        if (ok && nt > 0) {
+            tc::fence_after_sync();
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            __nv_bfloat16* dst = p.out + (((size_t)b * p.S + gi) * p.Hq + h) * PF_D;
+            uint32_t r0[32], r1[32];
+            tc::ld32(tO, r0);
+            tc::ld32(tO + 32, r1);
+            tc::wait_ld(r1);
+            if (gi < p.S) {
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    uint4 o4;
+                    o4.x = pack_bf16(__uint_as_float(r0[v * 8 + 0]) * inv, __uint_as_float(r0[v * 8 + 1]) * inv);
+                    o4.y = pack_bf16(__uint_as_float(r0[v * 8 + 2]) * inv, __uint_as_float(r0[v * 8 + 3]) * inv);
+                    o4.z = pack_bf16(__uint_as_float(r0[v * 8 + 4]) * inv, __uint_as_float(r0[v * 8 + 5]) * inv);
+                    o4.w = pack_bf16(__uint_as_float(r0[v * 8 + 6]) * inv, __uint_as_float(r0[v * 8 + 7]) * inv);
+                    *reinterpret_cast<uint4*>(dst + v * 8) = o4;
+                }
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    uint4 o4;
+                    o4.x = pack_bf16(__uint_as_float(r1[v * 8 + 0]) * inv, __uint_as_float(r1[v * 8 + 1]) * inv);
+                    o4.y = pack_bf16(__uint_as_float(r1[v * 8 + 2]) * inv, __uint_as_float(r1[v * 8 + 3]) * inv);
+                    o4.z = pack_bf16(__uint_as_float(r1[v * 8 + 4]) * inv, __uint_as_float(r1[v * 8 + 5]) * inv);
+                    o4.w = pack_bf16(__uint_as_float(r1[v * 8 + 6]) * inv, __uint_as_float(r1[v * 8 + 7]) * inv);
+                    *reinterpret_cast<uint4*>(dst + 32 + v * 8) = o4;
+                }
+                if (p.lse)
+                    p.lse[((size_t)b * p.Hq + h) * p.S + gi] =
+                        l_run > 0.f ? (m_ref * p.scale_log2 + log2f(l_run)) * PF_LN2 : -INFINITY;
+            }
+        }
+    }
+
+    // common exit: everybody arrives here (all waits are bounded), then TMEM is freed
+    tc::fence_before_sync();
+    __syncthreads();
+    if (tid == 0 && s_abort) atomicExch(p.error_word, BN_ERR_TIMEOUT);
+    if (warp == 8) {
+        tc::fence_after_sync();
+        tc::tmem_dealloc(tmem, P2_TMEM_COLS);
+    }
+}
+
 }  // namespace bn
 
 using namespace bn;
@@ -388,7 +796,7 @@ extern "C" int bn_attn_prefill_bf16(const void* q, const void* k, const void* v,
     if (Hq % Hkv != 0) return fail(BN_ERR_INVALID_ARG, "bn_attn_prefill_bf16: Hq=%d not a multiple of Hkv=%d", Hq, Hkv);
     if (D != PF_D) return fail(BN_ERR_UNSUPPORTED, "bn_attn_prefill_bf16: head_dim=%d (64 supported)", D);
     if (position_offset < 0) return fail(BN_ERR_INVALID_ARG, "bn_attn_prefill_bf16: position_offset=%d < 0", position_offset);
-    if (flags & ~BN_PREFILL_REUSE_ROTATED_K)
+    if (flags & ~(BN_PREFILL_REUSE_ROTATED_K | BN_PREFILL_SINGLE_TILE_KERNEL))
         return fail(BN_ERR_UNSUPPORTED, "bn_attn_prefill_bf16: flags=0x%x not understood", flags);
     if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
          reinterpret_cast<uintptr_t>(out)) & 15)
@@ -412,7 +820,7 @@ extern "C" int bn_attn_prefill_bf16(const void* q, const void* k, const void* v,
     cudaStream_t st = as_stream(stream);
 
     if (!(flags & BN_PREFILL_REUSE_ROTATED_K)) {
-        rope_k_kernel<<<dim3(S, B), 128, 0, st>>>(static_cast<const __nv_bfloat16*>(k), krot, table, B, S, Hkv, theta,
+        rope_k_kernel<<<dim3((S + RK_POS - 1) / RK_POS, B), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(k), krot, table, B, S, Hkv, theta,
                                                   position_offset, error_word);
         if (int rc = launch_status("bn_attn_prefill_bf16 (rope_k)")) return rc;
     }
@@ -445,10 +853,17 @@ extern "C" int bn_attn_prefill_bf16(const void* q, const void* k, const void* v,
     int dev = 0;
     cudaGetDevice(&dev);
     if (configured_dev != dev) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P2_SMEM_BYTES);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(prefill_kernel_v1, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM_BYTES);
         if (e != cudaSuccess) return fail(BN_ERR_CUDA, "cudaFuncSetAttribute(prefill): %s", cudaGetErrorString(e));
         configured_dev = dev;
     }
-    prefill_kernel<<<(unsigned)(n_qtiles * B * Hq), PF_THREADS, PF_SMEM_BYTES, st>>>(tmap_k, tmap_v, p);
+    if (flags & BN_PREFILL_SINGLE_TILE_KERNEL) {
+        prefill_kernel_v1<<<(unsigned)(n_qtiles * B * Hq), PF_THREADS, PF_SMEM_BYTES, st>>>(tmap_k, tmap_v, p);
+    } else {
+        const long long n_pairs = (n_qtiles + 1) / 2;
+        prefill_kernel<<<(unsigned)(n_pairs * B * Hq), P2_THREADS, P2_SMEM_BYTES, st>>>(tmap_k, tmap_v, p);
+    }
     return launch_status("bn_attn_prefill_bf16");
 }

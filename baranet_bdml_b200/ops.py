@@ -44,10 +44,12 @@ def prefill_workspace(B: int, S: int, Hq: int, Hkv: int, D: int = 64, device=Non
 def attn_prefill_bf16(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: Optional[float] = None,
                       theta: float = 10000.0, position_offset: int = 0, causal: bool = True,
                       out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None,
-                      workspace: Optional[Workspace] = None, reuse_rotated_k: bool = False) -> torch.Tensor:
+                      workspace: Optional[Workspace] = None, reuse_rotated_k: bool = False,
+                      single_tile_kernel: bool = False) -> torch.Tensor:
     """q (B,S,Hq,D), k,v (B,S,Hkv,D) bf16, q/k pre-RoPE -> out (B,S,Hq,D) bf16.
     `reuse_rotated_k`: the workspace still holds the rotated K of an earlier
-    call on the same k and position_offset (skips the rotation launch)."""
+    call on the same k and position_offset (skips the rotation launch).
+    `single_tile_kernel` selects the simpler kernel variant kept for comparison."""
     for t, n in ((q, "q"), (k, "k"), (v, "v")):
         _need(t, torch.bfloat16, f"attn_prefill_bf16({n})")
     B, S, Hq, D = q.shape
@@ -63,7 +65,7 @@ def attn_prefill_bf16(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scal
     _lib.check(_lib.load().bn_attn_prefill_bf16(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr() if lse is not None else None,
         B, S, Hq, Hkv, D, float(scale), float(theta), int(position_offset), int(bool(causal)),
-        0x100 if reuse_rotated_k else 0,
+        (0x100 if reuse_rotated_k else 0) | (0x200 if single_tile_kernel else 0),
         workspace.ptr, workspace.nbytes, _stream()))
     return out
 

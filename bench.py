@@ -269,7 +269,8 @@ def measure_decode(torch, args, rank, world, dist, reduce_max, pk):
     dsteps = args.steps if args.decode_only else max(args.steps, 16)
     ms_dec = reduce_max(time_loop(torch, dstep, dsteps, max(3, args.warmup), dist))
     for cch in caches:
-        cch._ws.status()
+        if cch._ws is not None:
+            cch._ws.status()
     gbs = bytes_alg / (ms_dec * 1e-3) / 1e9
     return {
         "metric": "decode_attention_hbm_gbs", "value": gbs * world, "unit": "GB/s", "ms_per_step": ms_dec,

@@ -125,8 +125,11 @@ BN_API size_t bn_attn_prefill_bf16_workspace_bytes(int B, int S, int Hq, int Hkv
  * (tcgen05 tensor cores, TMEM accumulators, TMA-staged K/V) runs.
  * flags: 0, or BN_PREFILL_REUSE_ROTATED_K when the scratch buffer still holds
  * the rotated K of an earlier call on the same k / position_offset (skips the
- * first launch). */
+ * first launch).
+ * BN_PREFILL_SINGLE_TILE_KERNEL selects the simpler kernel variant (one query
+ * tile per CTA, two CTAs per SM) kept for comparison. */
 #define BN_PREFILL_REUSE_ROTATED_K 0x100
+#define BN_PREFILL_SINGLE_TILE_KERNEL 0x200
 BN_API int bn_attn_prefill_bf16(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S, int Hq,
                          int Hkv, int D, float scale, float theta, int position_offset, int causal, int flags,
                                 void* workspace, size_t workspace_bytes, bn_stream_t stream);

@@ -19,13 +19,14 @@ def make_inputs(B, S, Hq, Hkv, D, seed):
     return q, k, v
 
 
-def run(q, k, v, off, causal, want_lse=False):
+def run(q, k, v, off, causal, want_lse=False, single=False):
     from baranet_bdml_b200 import ops
     tq, tk, tv = (torch.from_numpy(a).cuda().to(torch.bfloat16) for a in (q, k, v))
     B, S, Hq, D = q.shape
     ws = ops.prefill_workspace(B, S, Hq, k.shape[2], D)
     lse = torch.empty((B, Hq, S), dtype=torch.float32, device="cuda") if want_lse else None
-    out = ops.attn_prefill_bf16(tq, tk, tv, position_offset=off, causal=causal, lse=lse, workspace=ws)
+    out = ops.attn_prefill_bf16(tq, tk, tv, position_offset=off, causal=causal, lse=lse, workspace=ws,
+                                single_tile_kernel=single)
     torch.cuda.synchronize()
     ws.status()
     return out.float().cpu().numpy(), (lse.cpu().numpy() if want_lse else None)
@@ -39,12 +40,13 @@ def oracle(q, k, v, off, causal, b):
                                 dtype=np.float64, round_rope_bf16=True, return_lse=True)
 
 
-@pytest.mark.parametrize("S", [1, 15, 16, 17, 127, 128, 129, 256, 300])
+@pytest.mark.parametrize("S", [1, 15, 16, 17, 127, 128, 129, 255, 256, 257, 300, 400, 513])
 @pytest.mark.parametrize("off", [0, 5])
-def test_prefill_small(lib, S, off):
+@pytest.mark.parametrize("single", [False, True])
+def test_prefill_small(lib, S, off, single):
     B, Hq, Hkv, D = 2, 8, 2, 64
     q, k, v = make_inputs(B, S, Hq, Hkv, D, S * 7 + off)
-    got, lse = run(q, k, v, off, True, want_lse=True)
+    got, lse = run(q, k, v, off, True, want_lse=True, single=single)
     for b in range(B):
         ref, ref_lse = oracle(q, k, v, off, True, b)
         err = np.abs(got[b].reshape(S, Hq * D) - ref).max()
@@ -52,13 +54,29 @@ def test_prefill_small(lib, S, off):
         assert np.abs(lse[b].T - ref_lse).max() <= 2e-2
 
 
-@pytest.mark.parametrize("S", [64, 200])
-def test_prefill_non_causal(lib, S):
+@pytest.mark.parametrize("S", [64, 200, 384])
+@pytest.mark.parametrize("single", [False, True])
+def test_prefill_non_causal(lib, S, single):
     B, Hq, Hkv, D = 1, 8, 1, 64
     q, k, v = make_inputs(B, S, Hq, Hkv, D, 99 + S)
-    got, _ = run(q, k, v, 0, False)
+    got, _ = run(q, k, v, 0, False, single=single)
     ref, _ = oracle(q, k, v, 0, False, 0)
     assert np.abs(got[0].reshape(S, Hq * D) - ref).max() <= GATE
+
+
+def test_prefill_growing_scores_take_the_rescale_path(lib):
+    """Keys whose scores grow along the sequence force the running reference to move by more than 2^8
+    several times (the rescale-and-redo path of the single-pass softmax)."""
+    B, S, Hq, Hkv, D = 1, 640, 8, 1, 64
+    q, k, v = make_inputs(B, S, Hq, Hkv, D, 4242)
+    ramp = (1.0 + 7.0 * np.arange(S) / S).astype(np.float32)            # later keys are up to 8x larger
+    k = R.round_bf16(k * ramp[None, :, None, None])
+    q = R.round_bf16(q * 3.0)
+    for single in (False, True):
+        got, lse = run(q, k, v, 0, True, want_lse=True, single=single)
+        ref, ref_lse = oracle(q, k, v, 0, True, 0)
+        assert np.abs(got[0].reshape(S, Hq * D) - ref).max() <= GATE
+        assert np.abs(lse[0].T - ref_lse).max() <= 5e-2
 
 
 def test_prefill_tinyllama_shape_one_batch(lib):
