@@ -5,25 +5,28 @@
 // (mygrad/llama/llama_model.py:136-144); here the earlier keys/values come from
 // the cache instead of being recomputed.
 //
-// Design (one persistent CTA per SM):
-//   * Work item = (sequence, KV head, chunk of `chunk` tokens), claimed from an
-//     atomic counter so that SMs stay balanced over ragged lengths.
-//   * A producer warp streams the item's pages through a ring of shared-memory
-//     stages with TMA tensor loads (one 4 KB box = K and V of one (page, head),
-//     128-byte swizzle), completion counted on mbarriers.
+// Design (one persistent CTA per SM, no scheduling atomics):
+//   * The work of the launch is the sequence of all 128-token stages, ordered by
+//     (sequence, KV head, position).  It is cut into equal contiguous ranges,
+//     one per CTA, so every SM streams the same number of bytes whatever the
+//     sequence lengths are.  A range is a list of segments = (sequence, KV head,
+//     run of stages); every warp derives the list from seq_lens by itself.
+//   * A producer warp streams the pages of its range through a ring of
+//     shared-memory stages with TMA tensor loads (one 4 KB box = K and V of one
+//     (page, head), 128-byte swizzle), completion counted on mbarriers; page
+//     numbers are fetched one stage ahead.
 //   * Four consumer warps each take two pages (32 tokens) of a stage.  All 8
 //     query heads of the GQA group are served from the one K/V read:
 //       S^T (16 tokens x 8 heads) = K_page (16 x 64) . Q^T (64 x 8)
 //       O^T (64 dims  x 8 heads) += V_page^T (64 x 16) . P^T (16 x 8)
 //     as m16n8k16 bf16 MMAs with fp32 accumulation; softmax is online, base 2.
-//   * Per item the four warps merge (m, l, O) in shared memory.  A sequence cut
-//     into several chunks leaves fp32 partials in scratch memory; the CTA that
-//     finishes the last chunk of a (sequence, head) performs the log-sum-exp
-//     combine (atomic ticket, nobody spins on another CTA).
+//   * At the end of a segment the four warps merge (m, l, O) in shared memory.
+//     A (sequence, head) that spans several CTAs leaves fp32 partials in scratch
+//     memory; the CTA that delivers the last partial performs the log-sum-exp
+//     combine (atomic ticket, nobody spins on another CTA) and re-arms the ticket.
 //   * Every wait is bounded; on expiry the kernel raises the error word in the
 //     scratch header and returns.
 #include <math.h>
-#include <stdlib.h>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -33,9 +36,6 @@ namespace bn {
 
 using namespace ptx;
 
-#ifndef BN_DDBG
-#define BN_DDBG 0
-#endif
 constexpr int DEC_D = 64;
 constexpr int DEC_G = 8;                    // query heads per KV head served by one MMA (n = 8)
 constexpr int DEC_STAGE_TOKENS = 128;
@@ -47,42 +47,35 @@ constexpr int DEC_NSTAGES = 6;
 constexpr int DEC_CWARPS = 4;
 constexpr int DEC_THREADS = (DEC_CWARPS + 1) * 32;
 constexpr int DEC_SMEM_BYTES = DEC_NSTAGES * DEC_STAGE_BYTES + 1024;
+constexpr int DEC_MAX_SEQS = 2048;          // sequences per launch (prefix table in shared memory)
+constexpr int DEC_DEFAULT_MIN_TOKENS = 1024;   // a CTA's range is never shorter than this
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 
 struct DecodeHeader {   // first 256 bytes of the scratch buffer
     int error;          // BN_ERR_TIMEOUT once a bounded wait ran out
-    int work_counter;   // next work item to claim
-    int done_counter;   // CTAs that ran out of work
 };
 
 struct DecodeLayout {
     size_t tickets, part_m, part_l, part_o, total;
-    int max_chunks;
+    int max_parts;      // partial slots per (sequence, KV head)
 };
 
-static DecodeLayout decode_layout(int B, int Hkv, int max_seq_len, int chunk) {
+static DecodeLayout decode_layout(int B, int Hkv, int max_seq_len, int min_tokens) {
     DecodeLayout L;
     auto up = [](size_t x) { return (x + 255) / 256 * 256; };
-    L.max_chunks = max_seq_len > 0 ? (max_seq_len + chunk - 1) / chunk : 1;
+    // a (sequence, head) of n stages overlaps at most n / (min stages per CTA) + 2 CTA ranges
+    L.max_parts = (max_seq_len + min_tokens - 1) / min_tokens + 2;
     size_t bg = (size_t)B * Hkv;
     L.tickets = 256;
     L.part_m = L.tickets + up(bg * sizeof(int));
-    L.part_l = L.part_m + up(bg * L.max_chunks * DEC_G * sizeof(float));
-    L.part_o = L.part_l + up(bg * L.max_chunks * DEC_G * sizeof(float));
-    L.total = L.part_o + up(bg * L.max_chunks * DEC_G * DEC_D * sizeof(float));
+    L.part_l = L.part_m + up(bg * L.max_parts * DEC_G * sizeof(float));
+    L.part_o = L.part_l + up(bg * L.max_parts * DEC_G * sizeof(float));
+    L.total = L.part_o + up(bg * L.max_parts * DEC_G * DEC_D * sizeof(float));
     return L;
 }
 
-static int pick_chunk(int B, int Hkv, int max_seq_len, int chunk_tokens) {
-    if (chunk_tokens > 0) return chunk_tokens;
-    // aim at ~8 items per SM when every sequence is at its maximum length
-    long long tokens = (long long)B * Hkv * (long long)max_seq_len;
-    long long c = tokens / (8 * 148) / DEC_STAGE_TOKENS * DEC_STAGE_TOKENS;
-    if (c < 256) c = 256;
-    if (c > 8192) c = 8192;
-    return (int)c;
-}
+static int pick_min_tokens(int chunk_tokens) { return chunk_tokens > 0 ? chunk_tokens : DEC_DEFAULT_MIN_TOKENS; }
 
 struct DecodeParams {
     const __nv_bfloat16* q;
@@ -95,13 +88,57 @@ struct DecodeParams {
     DecodeHeader* hdr;
     int* tickets;
     float *part_m, *part_l, *part_o;
-    int B, Hq, Hkv, n_rep, max_pages, max_seq_len, chunk, max_chunks, total_items, rope_q, debug;
+    int B, Hq, Hkv, n_rep, max_pages, max_seq_len, min_stages, max_parts, rope_q;
     float scale_log2, theta;
 };
 
-struct StageMeta {
-    int item, b, g, chunk, ntok, first, last, n_chunks, qpos;
+// The launch-wide schedule, derived from seq_lens by every thread of every CTA.
+struct Schedule {
+    const int* prefix;     // shared memory: prefix[b] = sum of stages of sequences < b (one KV head)
+    int Hkv, B;
+    long long T;           // all stages of the launch
+    int G;                 // CTAs that take part
+    __device__ __forceinline__ int nst(int b) const { return prefix[b + 1] - prefix[b]; }
+    __device__ __forceinline__ long long seg_begin(int b, int g) const {
+        return (long long)Hkv * prefix[b] + (long long)g * nst(b);
+    }
+    __device__ __forceinline__ long long range_begin(int cta) const { return (long long)cta * T / G; }
+    // the CTA whose range holds global stage x
+    __device__ __forceinline__ int cta_of(long long x) const { return (int)(((x + 1) * G - 1) / T); }
+    // first sequence b with Hkv * prefix[b + 1] > x
+    __device__ __forceinline__ int seq_of(long long x) const {
+        int lo = 0, hi = B - 1;
+        while (lo < hi) {
+            int mid = (lo + hi) >> 1;
+            if ((long long)Hkv * prefix[mid + 1] > x) hi = mid; else lo = mid + 1;
+        }
+        return lo;
+    }
 };
+
+// One segment of a CTA's range: stages [s0, s1) of (b, g).
+struct Segment {
+    int b, g, s0, s1, L;
+    int c_first, n_parts;   // CTAs that hold a piece of this (b, g)
+};
+
+__device__ __forceinline__ bool next_segment(const Schedule& sc, const int32_t* seq_lens, int max_seq_len,
+                                             long long& pos, long long end, Segment& sg) {
+    if (pos >= end) return false;
+    const int b = sc.seq_of(pos);
+    const int n = sc.nst(b);
+    const long long base = (long long)sc.Hkv * sc.prefix[b];
+    const int g = (int)((pos - base) / n);
+    const long long sb = base + (long long)g * n;
+    sg.b = b; sg.g = g;
+    sg.s0 = (int)(pos - sb);
+    sg.s1 = (int)min((long long)n, end - sb);
+    sg.L = max(0, min(seq_lens[b], max_seq_len));
+    sg.c_first = sc.cta_of(sb);
+    sg.n_parts = sc.cta_of(sb + n - 1) - sg.c_first + 1;
+    pos = sb + sg.s1;
+    return true;
+}
 
 __global__ void __launch_bounds__(DEC_THREADS, 1)
 decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams p) {
@@ -109,11 +146,12 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
     __shared__ __align__(8) uint64_t full_bar[DEC_NSTAGES];
     __shared__ __align__(8) uint64_t empty_bar[DEC_NSTAGES];
     __shared__ __align__(8) uint64_t merge_bar;
-    __shared__ StageMeta meta[DEC_NSTAGES];
+    __shared__ int s_prefix[DEC_MAX_SEQS + 1];
     __shared__ float mrg_m[DEC_CWARPS][DEC_G], mrg_l[DEC_CWARPS][DEC_G];
-    __shared__ float mrg_o[DEC_CWARPS][DEC_G][DEC_D + 1];
+    __shared__ float mrg_o[DEC_CWARPS][DEC_G][DEC_D + 4];
+    __shared__ __align__(16) __nv_bfloat16 s_q[DEC_G][DEC_D];   // rotated query heads of the current segment
     __shared__ float s_inv_freq[DEC_D / 2];
-    __shared__ int s_abort, s_ticket;
+    __shared__ int s_abort;
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -125,215 +163,236 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
         }
         mbar_init(smem_u32(&merge_bar), DEC_CWARPS);
         s_abort = 0;
-        s_ticket = 0;
         fence_mbar_init();
         prefetch_tensormap(&tmap);
     }
     if (tid < DEC_D / 2) s_inv_freq[tid] = rope_inv_freq(tid, DEC_D, p.theta);
+    // stages per sequence, then an exclusive prefix sum (warp 0)
+    for (int b = tid; b < p.B; b += DEC_THREADS) {
+        const int L = max(0, min(p.seq_lens[b], p.max_seq_len));
+        s_prefix[b + 1] = (L + DEC_STAGE_TOKENS - 1) / DEC_STAGE_TOKENS;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        int carry = 0;
+        for (int b0 = 0; b0 < p.B; b0 += 32) {
+            const int b = b0 + lane;
+            int v = b < p.B ? s_prefix[b + 1] : 0;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, v, o);
+                if (lane >= o) v += t;
+            }
+            if (b < p.B) s_prefix[b + 1] = carry + v;
+            carry += __shfl_sync(0xffffffffu, v, 31);
+        }
+        if (lane == 0) s_prefix[0] = 0;
+    }
     __syncthreads();
 
-    const int BG = p.B * p.Hkv;
+    Schedule sc;
+    sc.prefix = s_prefix;
+    sc.Hkv = p.Hkv;
+    sc.B = p.B;
+    sc.T = (long long)p.Hkv * s_prefix[p.B];
+    sc.G = (int)max(1LL, min((long long)gridDim.x, sc.T / p.min_stages));
+    const bool active = sc.T > 0 && (int)blockIdx.x < sc.G;
+    const long long range_lo = active ? sc.range_begin(blockIdx.x) : 0;
+    const long long range_hi = active ? sc.range_begin(blockIdx.x + 1) : 0;
 
     if (warp == DEC_CWARPS) {
         // ------------------------------------------------------------ producer
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        while (ok) {
-            int id = 0;
-            if (lane == 0) id = atomicAdd(&p.hdr->work_counter, 1);
-            id = __shfl_sync(0xffffffffu, id, 0);
-            if (id >= p.total_items) break;
-            const int c = id / BG, bg = id % BG, b = bg / p.Hkv, g = bg % p.Hkv;
-            int L = p.seq_lens[b];
-            L = max(0, min(L, p.max_seq_len));
-            const int n_chunks = max(1, (L + p.chunk - 1) / p.chunk);
-            if (c >= n_chunks) continue;
-            const int t0 = c * p.chunk, t1 = min(L, t0 + p.chunk);
-            const int nst = max(1, (t1 - t0 + DEC_STAGE_TOKENS - 1) / DEC_STAGE_TOKENS);
-            const int qpos = p.q_positions ? p.q_positions[b] : L - 1;
-            for (int s = 0; s < nst; ++s) {
+        long long pos = range_lo;
+        Segment sg;
+        while (ok && next_segment(sc, p.seq_lens, p.max_seq_len, pos, range_hi, sg)) {
+            const int32_t* pt = p.page_table + (size_t)sg.b * p.max_pages;
+            const int n_pages_seq = (sg.L + BN_PAGE_TOKENS - 1) / BN_PAGE_TOKENS;
+            // page number of this lane's box, fetched one stage ahead of its use
+            auto load_page = [&](int s) {
+                const int pg = s * DEC_PAGES_PER_STAGE + lane;
+                return (lane < DEC_PAGES_PER_STAGE && pg < n_pages_seq) ? pt[pg] : -1;
+            };
+            int page_next = load_page(sg.s0);
+            for (int s = sg.s0; s < sg.s1; ++s) {
+                const int page = page_next;
+                if (s + 1 < sg.s1) page_next = load_page(s + 1);
                 if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, &s_abort)) { ok = false; break; }
-                const int ts = t0 + s * DEC_STAGE_TOKENS;
-                const int ntok = max(0, min(DEC_STAGE_TOKENS, t1 - ts));
-                const int npages = (ntok + BN_PAGE_TOKENS - 1) / BN_PAGE_TOKENS;
+                const int npages = min(DEC_PAGES_PER_STAGE, n_pages_seq - s * DEC_PAGES_PER_STAGE);
                 const uint32_t fb = smem_u32(&full_bar[stage]);
-                if (lane == 0) {
-                    StageMeta mt{id, b, g, c, ntok, s == 0, s == nst - 1, n_chunks, qpos};
-                    meta[stage] = mt;
-                    if (npages > 0) mbar_arrive_expect_tx(fb, (uint32_t)npages * DEC_BOX_BYTES);
-                    else mbar_arrive(fb);
-                }
+                if (lane == 0) mbar_arrive_expect_tx(fb, (uint32_t)npages * DEC_BOX_BYTES);
                 __syncwarp();
-                if (lane < npages) {
-#if (BN_DDBG & 2)
-                    const int page = (b * 61 + ts / BN_PAGE_TOKENS + lane) & 8191;
-#else
-                    const int page = p.page_table[(size_t)b * p.max_pages + ts / BN_PAGE_TOKENS + lane];
-#endif
+                if (page >= 0)
                     tma_load_2d(ring + stage * DEC_STAGE_BYTES + lane * DEC_BOX_BYTES, &tmap, 0,
-                                (page * p.Hkv + g) * DEC_BOX_ROWS, fb);
-                }
+                                (page * p.Hkv + sg.g) * DEC_BOX_ROWS, fb);
                 if (++stage == DEC_NSTAGES) { stage = 0; phase ^= 1u; }
             }
         }
-        if (ok && mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, &s_abort)) {
-            if (lane == 0) {
-                meta[stage].item = -1;   // end marker
-                mbar_arrive(smem_u32(&full_bar[stage]));
-            }
-        }
-        if (lane == 0) {
-            if (s_abort) {
-                atomicExch(&p.hdr->error, BN_ERR_TIMEOUT);
-            } else {
-                // the last CTA to run out of work re-arms the counters for the next launch
-                int old = atomicAdd(&p.hdr->done_counter, 1);
-                if (old == (int)gridDim.x - 1) {
-                    p.hdr->work_counter = 0;
-                    p.hdr->done_counter = 0;
-                }
-            }
-        }
+        if (lane == 0 && s_abort) atomicExch(&p.hdr->error, BN_ERR_TIMEOUT);
         return;
     }
 
     // --------------------------------------------------------------- consumers
+    // sequences without tokens get a zero output from whoever passes by
+    for (int bgi = blockIdx.x; bgi < p.B * p.Hkv; bgi += gridDim.x) {
+        const int b = bgi / p.Hkv, g = bgi % p.Hkv;
+        if (sc.nst(b) > 0) continue;
+        const int th = tid / 16, td = (tid % 16) * 4;
+        if (th >= p.n_rep) continue;
+        const size_t row = (size_t)b * p.Hq + (size_t)g * p.n_rep + th;
+        if (p.out) *reinterpret_cast<uint2*>(p.out + row * DEC_D + td) = make_uint2(0u, 0u);
+        if (p.out_f32) *reinterpret_cast<float4*>(p.out_f32 + row * DEC_D + td) = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (p.lse && tid % 16 == 0) p.lse[row] = -INFINITY;
+    }
+
     int stage = 0;
     uint32_t phase = 0, mphase = 0;
-    const int hl = lane / 4;             // head (B-fragment column / S^T column pair owner)
     const int hA = 2 * (lane % 4);       // the two heads whose softmax state this thread carries
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-    float o[4][4];
-    uint32_t qb[4][2] = {};
     const uint32_t mb = smem_u32(&merge_bar);
-
     auto group_sync = [&]() -> bool {
         __syncwarp();
         if (lane == 0) mbar_arrive(mb);
-        bool ok = mbar_wait(mb, mphase, &s_abort);
+        const bool ok = mbar_wait(mb, mphase, &s_abort);
         mphase ^= 1u;
         return ok;
     };
+    // raw query pair of thread (head tid / 16, dims 4 * (tid % 16) .. + 3) for a segment
+    auto load_q_raw = [&](const Segment& sg) -> uint2 {
+        const int th = tid / 16, td = (tid % 16) * 4;
+        if (th >= p.n_rep) return make_uint2(0u, 0u);
+        return *reinterpret_cast<const uint2*>(p.q + ((size_t)sg.b * p.Hq + (size_t)sg.g * p.n_rep + th) * DEC_D + td);
+    };
 
-    while (true) {
-        if (!mbar_wait(smem_u32(&full_bar[stage]), phase, &s_abort)) break;
-        const StageMeta mt = meta[stage];
-        if (mt.item < 0) break;
-        const int b = mt.b, g = mt.g;
+    long long pos = range_lo;
+    Segment sg, sg_next;
+    bool have = next_segment(sc, p.seq_lens, p.max_seq_len, pos, range_hi, sg);
+    uint2 q_raw = have ? load_q_raw(sg) : make_uint2(0u, 0u);
+    bool ok = true;
+    while (ok && have) {
+        // look one segment ahead so that its query is already on the way
+        const bool have_next = next_segment(sc, p.seq_lens, p.max_seq_len, pos, range_hi, sg_next);
+        const uint2 q_raw_next = have_next ? load_q_raw(sg_next) : make_uint2(0u, 0u);
 
-        if (mt.first) {
-            // Q^T fragments (k = dims, n = heads), rotated at the query position
-            const bool hv = hl < p.n_rep;
-            const __nv_bfloat16* qrow = p.q + ((size_t)b * p.Hq + (size_t)g * p.n_rep + hl) * DEC_D;
+        // rotate the 8 query heads of this segment (two pairs per thread) into shared memory
+        {
+            const int th = tid / 16, td = (tid % 16) * 4;
+            const int qpos = p.q_positions ? p.q_positions[sg.b] : sg.L - 1;
+            uint32_t w[2] = {q_raw.x, q_raw.y};
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
+            for (int e = 0; e < 2; ++e) {
+                float x0 = bf16_lo(w[e]), x1 = bf16_hi(w[e]);
+                if (p.rope_q) {
+                    const float angle = qpos * s_inv_freq[td / 2 + e];
+                    const float cos_angle = cosf(angle), sin_angle = sinf(angle);
+                    const float y0 = x0 * cos_angle - x1 * sin_angle;
+                    const float y1 = x0 * sin_angle + x1 * cos_angle;
+                    x0 = y0; x1 = y1;
+                }
+                w[e] = pack_bf16(x0, x1);
+            }
+            *reinterpret_cast<uint2*>(&s_q[th][td]) = make_uint2(w[0], w[1]);
+        }
+        if (!group_sync()) break;
+        // Q^T fragments (k = dims, n = heads)
+        uint32_t qb[4][2];
 #pragma unroll
-                for (int h8 = 0; h8 < 2; ++h8) {
-                    const int d = kk * 16 + h8 * 8 + 2 * (lane % 4);
-                    uint32_t raw = hv ? *reinterpret_cast<const uint32_t*>(qrow + d) : 0u;
-                    float x0 = bf16_lo(raw), x1 = bf16_hi(raw);
-                    if (p.rope_q) {
-                        float angle = mt.qpos * s_inv_freq[d / 2];
-                        float cos_angle = cosf(angle), sin_angle = sinf(angle);
-                        float y0 = x0 * cos_angle - x1 * sin_angle;
-                        float y1 = x0 * sin_angle + x1 * cos_angle;
-                        x0 = y0; x1 = y1;
+        for (int kk = 0; kk < 4; ++kk)
+#pragma unroll
+            for (int h8 = 0; h8 < 2; ++h8)
+                qb[kk][h8] = *reinterpret_cast<const uint32_t*>(&s_q[lane / 4][kk * 16 + h8 * 8 + 2 * (lane % 4)]);
+
+        float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+        float o[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
+
+        for (int s = sg.s0; s < sg.s1; ++s) {
+            if (!mbar_wait(smem_u32(&full_bar[stage]), phase, &s_abort)) { ok = false; break; }
+            const int ntok = min(DEC_STAGE_TOKENS, sg.L - s * DEC_STAGE_TOKENS);
+            const uint32_t sbase = ring + stage * DEC_STAGE_BYTES;
+            float sv[2][4];
+            int nv[2];
+#pragma unroll
+            for (int pi = 0; pi < 2; ++pi) {
+                const int pg = warp * 2 + pi;
+                nv[pi] = max(0, min(BN_PAGE_TOKENS, ntok - pg * BN_PAGE_TOKENS));
+                const uint32_t box = sbase + pg * DEC_BOX_BYTES;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) sv[pi][j] = 0.f;
+                if (nv[pi] == 0) continue;
+                if (nv[pi] < BN_PAGE_TOKENS) {
+                    // ragged last page: the unwritten V rows may hold anything; 0 * NaN must not reach O
+                    for (int e = lane; e < (BN_PAGE_TOKENS - nv[pi]) * 8; e += 32) {
+                        const int row = BN_PAGE_TOKENS + nv[pi] + e / 8;
+                        asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(box + row * 128 + (e % 8) * 16), "r"(0)
+                                     : "memory");
                     }
-                    qb[kk][h8] = pack_bf16(x0, x1);
+                    __syncwarp();
                 }
-            m_run[0] = m_run[1] = -INFINITY;
-            l_run[0] = l_run[1] = 0.f;
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
-        }
-
-        const uint32_t sbase = ring + stage * DEC_STAGE_BYTES;
-        float s[2][4];
-        int nv[2];
-#pragma unroll
-        for (int pi = 0; pi < 2; ++pi) {
-            const int pg = warp * 2 + pi;
-            nv[pi] = max(0, min(BN_PAGE_TOKENS, mt.ntok - pg * BN_PAGE_TOKENS));
-            if (p.debug & 1) nv[pi] = 0;
-            const uint32_t box = sbase + pg * DEC_BOX_BYTES;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) s[pi][j] = 0.f;
-            if (nv[pi] == 0) continue;
-            if (nv[pi] < BN_PAGE_TOKENS) {
-                // ragged last page: the unwritten V rows may hold anything; 0 * NaN must not reach O
-                for (int e = lane; e < (BN_PAGE_TOKENS - nv[pi]) * 8; e += 32) {
-                    int row = BN_PAGE_TOKENS + nv[pi] + e / 8;
-                    asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(box + row * 128 + (e % 8) * 16), "r"(0)
-                                 : "memory");
+                for (int kk = 0; kk < 4; ++kk) {
+                    const int mat = lane / 8, tok = (lane % 8) + (mat & 1) * 8, chunk16 = kk * 2 + (mat >> 1);
+                    uint32_t a0, a1, a2, a3;
+                    ldmatrix_x4(box + tok * 128 + ((chunk16 ^ (tok & 7)) << 4), a0, a1, a2, a3);
+                    mma_bf16_16816(sv[pi], a0, a1, a2, a3, qb[kk][0], qb[kk][1]);
                 }
-                __syncwarp();
+            }
+            // online softmax, base 2; thread owns heads hA, hA+1 and tokens lane/4 (+8) of each page
+            float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int pi = 0; pi < 2; ++pi)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int tok = lane / 4 + (j >> 1) * 8;
+                    sv[pi][j] = tok < nv[pi] ? sv[pi][j] * p.scale_log2 : -INFINITY;
+                    tmax[j & 1] = fmaxf(tmax[j & 1], sv[pi][j]);
+                }
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                tmax[hh] = fmaxf(tmax[hh], __shfl_xor_sync(0xffffffffu, tmax[hh], 4));
+                tmax[hh] = fmaxf(tmax[hh], __shfl_xor_sync(0xffffffffu, tmax[hh], 8));
+                tmax[hh] = fmaxf(tmax[hh], __shfl_xor_sync(0xffffffffu, tmax[hh], 16));
+            }
+            float msafe[2];
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const float m_new = fmaxf(m_run[hh], tmax[hh]);
+                msafe[hh] = m_new == -INFINITY ? 0.f : m_new;
+                const float alpha = ex2(m_run[hh] - msafe[hh]);
+                m_run[hh] = m_new;
+                l_run[hh] *= alpha;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { o[i][hh] *= alpha; o[i][hh + 2] *= alpha; }
             }
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-                const int mat = lane / 8, tok = (lane % 8) + (mat & 1) * 8, chunk16 = kk * 2 + (mat >> 1);
-                uint32_t a0, a1, a2, a3;
-                ldmatrix_x4(box + tok * 128 + ((chunk16 ^ (tok & 7)) << 4), a0, a1, a2, a3);
-                mma_bf16_16816(s[pi], a0, a1, a2, a3, qb[kk][0], qb[kk][1]);
+            for (int pi = 0; pi < 2; ++pi) {
+                if (nv[pi] == 0) continue;
+                float pr[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    pr[j] = ex2(sv[pi][j] - msafe[j & 1]);
+                    l_run[j & 1] += pr[j];
+                }
+                const uint32_t b0 = movmatrix_trans(pack_bf16(pr[0], pr[1]));
+                const uint32_t b1 = movmatrix_trans(pack_bf16(pr[2], pr[3]));
+                const uint32_t vbox = sbase + (warp * 2 + pi) * DEC_BOX_BYTES + BN_PAGE_TOKENS * 128;
+#pragma unroll
+                for (int mtile = 0; mtile < 4; ++mtile) {
+                    const int mat = lane / 8, tok = (lane % 8) + (mat >> 1) * 8, chunk16 = mtile * 2 + (mat & 1);
+                    uint32_t a0, a1, a2, a3;
+                    ldmatrix_x4_trans(vbox + tok * 128 + ((chunk16 ^ (tok & 7)) << 4), a0, a1, a2, a3);
+                    mma_bf16_16816(o[mtile], a0, a1, a2, a3, b0, b1);
+                }
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&empty_bar[stage]));
+            if (++stage == DEC_NSTAGES) { stage = 0; phase ^= 1u; }
         }
-        // online softmax, base 2; thread owns heads hA, hA+1 and tokens lane/4 (+8) of each page
-        float tmax[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-        for (int pi = 0; pi < 2; ++pi)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int tok = lane / 4 + (j >> 1) * 8;
-                s[pi][j] = tok < nv[pi] ? s[pi][j] * p.scale_log2 : -INFINITY;
-                tmax[j & 1] = fmaxf(tmax[j & 1], s[pi][j]);
-            }
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-            tmax[hh] = fmaxf(tmax[hh], __shfl_xor_sync(0xffffffffu, tmax[hh], 4));
-            tmax[hh] = fmaxf(tmax[hh], __shfl_xor_sync(0xffffffffu, tmax[hh], 8));
-            tmax[hh] = fmaxf(tmax[hh], __shfl_xor_sync(0xffffffffu, tmax[hh], 16));
-        }
-        float msafe[2];
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-            const float m_new = fmaxf(m_run[hh], tmax[hh]);
-            msafe[hh] = m_new == -INFINITY ? 0.f : m_new;
-            const float alpha = ex2(m_run[hh] - msafe[hh]);
-            m_run[hh] = m_new;
-            l_run[hh] *= alpha;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) { o[i][hh] *= alpha; o[i][hh + 2] *= alpha; }
-        }
-#pragma unroll
-        for (int pi = 0; pi < 2; ++pi) {
-            if (nv[pi] == 0) continue;
-            float pr[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                pr[j] = ex2(s[pi][j] - msafe[j & 1]);
-                l_run[j & 1] += pr[j];
-            }
-            const uint32_t b0 = movmatrix_trans(pack_bf16(pr[0], pr[1]));
-            const uint32_t b1 = movmatrix_trans(pack_bf16(pr[2], pr[3]));
-            const uint32_t vbox = sbase + (warp * 2 + pi) * DEC_BOX_BYTES + BN_PAGE_TOKENS * 128;
-#pragma unroll
-            for (int mtile = 0; mtile < 4; ++mtile) {
-                const int mat = lane / 8, tok = (lane % 8) + (mat >> 1) * 8, chunk16 = mtile * 2 + (mat & 1);
-                uint32_t a0, a1, a2, a3;
-                ldmatrix_x4_trans(vbox + tok * 128 + ((chunk16 ^ (tok & 7)) << 4), a0, a1, a2, a3);
-                mma_bf16_16816(o[mtile], a0, a1, a2, a3, b0, b1);
-            }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&empty_bar[stage]));
-        if (++stage == DEC_NSTAGES) { stage = 0; phase ^= 1u; }
-
-        if (!mt.last) continue;
-#if (BN_DDBG & 4)
-        continue;
-#endif
+        if (!ok) break;
 
         // ------------------------------------------------ merge the 4 warps
 #pragma unroll
@@ -364,15 +423,26 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
         float lsum = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int w = 0; w < DEC_CWARPS; ++w) {
-            const float sc = ex2(mrg_m[w][th] - ms);
-            lsum += mrg_l[w][th] * sc;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) acc[j] += mrg_o[w][th][td + j] * sc;
+            const float scl = ex2(mrg_m[w][th] - ms);
+            lsum += mrg_l[w][th] * scl;
+            const float4 po = *reinterpret_cast<const float4*>(&mrg_o[w][th][td]);
+            acc[0] += po.x * scl; acc[1] += po.y * scl; acc[2] += po.z * scl; acc[3] += po.w * scl;
         }
-        const int bgi = b * p.Hkv + g;
-        bool write_final = mt.n_chunks == 1;
-        if (!write_final) {
-            const size_t slot = (size_t)bgi * p.max_chunks + mt.chunk;
+        const int bgi = sg.b * p.Hkv + sg.g;
+        const size_t row = (size_t)sg.b * p.Hq + (size_t)sg.g * p.n_rep + th;
+        auto write_final = [&](float m_, float l_, const float (&a)[4]) {
+            if (th >= p.n_rep) return;
+            const float inv = l_ > 0.f ? 1.f / l_ : 0.f;
+            const float r0 = a[0] * inv, r1 = a[1] * inv, r2 = a[2] * inv, r3 = a[3] * inv;
+            if (p.out) *reinterpret_cast<uint2*>(p.out + row * DEC_D + td) = make_uint2(pack_bf16(r0, r1), pack_bf16(r2, r3));
+            if (p.out_f32) *reinterpret_cast<float4*>(p.out_f32 + row * DEC_D + td) = make_float4(r0, r1, r2, r3);
+            if (p.lse && tid % 16 == 0) p.lse[row] = l_ > 0.f ? (m_ + log2f(l_)) * LN2 : -INFINITY;
+        };
+        if (sg.n_parts == 1) {
+            write_final(mstar, lsum, acc);
+            if (!group_sync()) break;          // mrg_* and s_q are reused by the next segment
+        } else {
+            const size_t slot = (size_t)bgi * p.max_parts + ((int)blockIdx.x - sg.c_first);
             if (tid % 16 == 0) {
                 p.part_m[slot * DEC_G + th] = mstar;
                 p.part_l[slot * DEC_G + th] = lsum;
@@ -381,39 +451,55 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
                 make_float4(acc[0], acc[1], acc[2], acc[3]);
             __threadfence();
             if (!group_sync()) break;
-            if (tid == 0) s_ticket = atomicAdd(&p.tickets[bgi], 1);
-            if (!group_sync()) break;
-            if (s_ticket == mt.n_chunks - 1) {
-                // this CTA finished the last chunk of (b, g): log-sum-exp combine of all partials
-                __threadfence();
-                const size_t base = (size_t)bgi * p.max_chunks;
-                mstar = -INFINITY;
-                for (int c = 0; c < mt.n_chunks; ++c) mstar = fmaxf(mstar, __ldcg(p.part_m + (base + c) * DEC_G + th));
-                const float ms2 = mstar == -INFINITY ? 0.f : mstar;
-                lsum = 0.f;
-                acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-                for (int c = 0; c < mt.n_chunks; ++c) {
-                    const float sc = ex2(__ldcg(p.part_m + (base + c) * DEC_G + th) - ms2);
-                    lsum += __ldcg(p.part_l + (base + c) * DEC_G + th) * sc;
-                    const float4 po = __ldcg(reinterpret_cast<const float4*>(p.part_o + ((base + c) * DEC_G + th) * DEC_D + td));
-                    acc[0] += po.x * sc; acc[1] += po.y * sc; acc[2] += po.z * sc; acc[3] += po.w * sc;
+            // warp 0 alone takes the ticket and, if it holds the last one, combines; the others go on
+            if (warp == 0) {
+                int ticket = 0;
+                if (lane == 0) ticket = atomicAdd(&p.tickets[bgi], 1);
+                ticket = __shfl_sync(0xffffffffu, ticket, 0);
+                if (ticket == sg.n_parts - 1) {
+                    __threadfence();
+                    const size_t base = (size_t)bgi * p.max_parts;
+                    // lane -> head lane / 4, dims 16 * (lane % 4) .. + 15
+                    const int ch = lane / 4, cd = (lane % 4) * 16;
+                    float m2 = -INFINITY;
+                    for (int c = 0; c < sg.n_parts; ++c) m2 = fmaxf(m2, __ldcg(p.part_m + (base + c) * DEC_G + ch));
+                    const float ms2 = m2 == -INFINITY ? 0.f : m2;
+                    float l2 = 0.f, a2[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) a2[i] = 0.f;
+                    for (int c = 0; c < sg.n_parts; ++c) {
+                        const float scl = ex2(__ldcg(p.part_m + (base + c) * DEC_G + ch) - ms2);
+                        l2 += __ldcg(p.part_l + (base + c) * DEC_G + ch) * scl;
+                        const float4* po = reinterpret_cast<const float4*>(p.part_o + ((base + c) * DEC_G + ch) * DEC_D + cd);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float4 v4 = __ldcg(po + i);
+                            a2[4 * i] += v4.x * scl; a2[4 * i + 1] += v4.y * scl;
+                            a2[4 * i + 2] += v4.z * scl; a2[4 * i + 3] += v4.w * scl;
+                        }
+                    }
+                    if (lane == 0) p.tickets[bgi] = 0;   // leave the scratch clean for the next launch
+                    if (ch < p.n_rep) {
+                        const float inv = l2 > 0.f ? 1.f / l2 : 0.f;
+                        const size_t crow = (size_t)sg.b * p.Hq + (size_t)sg.g * p.n_rep + ch;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float r0 = a2[4 * i] * inv, r1 = a2[4 * i + 1] * inv, r2 = a2[4 * i + 2] * inv,
+                                        r3 = a2[4 * i + 3] * inv;
+                            if (p.out)
+                                *reinterpret_cast<uint2*>(p.out + crow * DEC_D + cd + 4 * i) =
+                                    make_uint2(pack_bf16(r0, r1), pack_bf16(r2, r3));
+                            if (p.out_f32)
+                                *reinterpret_cast<float4*>(p.out_f32 + crow * DEC_D + cd + 4 * i) = make_float4(r0, r1, r2, r3);
+                        }
+                        if (p.lse && lane % 4 == 0) p.lse[crow] = l2 > 0.f ? (m2 + log2f(l2)) * LN2 : -INFINITY;
+                    }
                 }
-                if (tid == 0) p.tickets[bgi] = 0;   // leave the scratch clean for the next launch
-                write_final = true;
             }
         }
-        if (write_final && th < p.n_rep) {
-            const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-            const size_t row = (size_t)b * p.Hq + (size_t)g * p.n_rep + th;
-            const float r0 = acc[0] * inv, r1 = acc[1] * inv, r2 = acc[2] * inv, r3 = acc[3] * inv;
-            if (p.out) {
-                uint2 v = make_uint2(pack_bf16(r0, r1), pack_bf16(r2, r3));
-                *reinterpret_cast<uint2*>(p.out + row * DEC_D + td) = v;
-            }
-            if (p.out_f32) *reinterpret_cast<float4*>(p.out_f32 + row * DEC_D + td) = make_float4(r0, r1, r2, r3);
-            if (p.lse && tid % 16 == 0) p.lse[row] = lsum > 0.f ? (mstar + log2f(lsum)) * LN2 : -INFINITY;
-        }
-        if (!group_sync()) break;   // mrg_* may be overwritten by the next item after this point
+        sg = sg_next;
+        q_raw = q_raw_next;
+        have = have_next;
     }
     if (s_abort && lane == 0) atomicExch(&p.hdr->error, BN_ERR_TIMEOUT);
 }
@@ -452,8 +538,7 @@ extern "C" size_t bn_attn_decode_workspace_bytes(int B, int Hq, int Hkv, int D, 
     (void)Hq;
     if (B <= 0 || Hkv <= 0 || D != DEC_D || max_seq_len < 0) return 0;
     if (chunk_tokens < 0 || chunk_tokens % DEC_STAGE_TOKENS) return 0;
-    int chunk = pick_chunk(B, Hkv, max_seq_len, chunk_tokens);
-    return decode_layout(B, Hkv, max_seq_len, chunk).total;
+    return decode_layout(B, Hkv, max_seq_len, pick_min_tokens(chunk_tokens)).total;
 }
 
 extern "C" int bn_attn_decode_paged(const void* q, const void* pool, int64_t pool_pages, const int32_t* page_table,
@@ -469,6 +554,9 @@ extern "C" int bn_attn_decode_paged(const void* q, const void* pool, int64_t poo
     if (D != DEC_D) return fail(BN_ERR_UNSUPPORTED, "bn_attn_decode_paged: head_dim=%d (64 supported)", D);
     if (Hq % Hkv != 0 || Hq / Hkv > DEC_G)
         return fail(BN_ERR_UNSUPPORTED, "bn_attn_decode_paged: Hq/Hkv=%d/%d (group of 1..8 supported)", Hq, Hkv);
+    if (B > DEC_MAX_SEQS)
+        return fail(BN_ERR_UNSUPPORTED, "bn_attn_decode_paged: %d sequences in one launch (<= %d supported)", B,
+                    DEC_MAX_SEQS);
     if (chunk_tokens < 0 || chunk_tokens % DEC_STAGE_TOKENS)
         return fail(BN_ERR_INVALID_ARG, "bn_attn_decode_paged: chunk_tokens=%d must be 0 or a multiple of %d",
                     chunk_tokens, DEC_STAGE_TOKENS);
@@ -477,13 +565,13 @@ extern "C" int bn_attn_decode_paged(const void* q, const void* pool, int64_t poo
                     max_seq_len);
     if (pool_pages * Hkv * DEC_BOX_ROWS > 0x7fffffffLL)
         return fail(BN_ERR_UNSUPPORTED, "bn_attn_decode_paged: pool of %lld pages is too large", (long long)pool_pages);
-    if ((reinterpret_cast<uintptr_t>(q) & 3) || (out && (reinterpret_cast<uintptr_t>(out) & 7)) ||
+    if ((reinterpret_cast<uintptr_t>(q) & 7) || (out && (reinterpret_cast<uintptr_t>(out) & 7)) ||
         (out_f32 && (reinterpret_cast<uintptr_t>(out_f32) & 15)))
-        return fail(BN_ERR_INVALID_ARG, "bn_attn_decode_paged: q/out buffers must be 4/8/16-byte aligned");
+        return fail(BN_ERR_INVALID_ARG, "bn_attn_decode_paged: q/out buffers must be 8/8/16-byte aligned");
     if (int rc = require_sm100()) return rc;
     if (B == 0) return BN_OK;
-    const int chunk = pick_chunk(B, Hkv, max_seq_len, chunk_tokens);
-    const DecodeLayout L = decode_layout(B, Hkv, max_seq_len, chunk);
+    const int min_tokens = pick_min_tokens(chunk_tokens);
+    const DecodeLayout L = decode_layout(B, Hkv, max_seq_len, min_tokens);
     if (!workspace || workspace_bytes < L.total)
         return fail(BN_ERR_WORKSPACE, "bn_attn_decode_paged: workspace of %zu bytes given, %zu needed", workspace_bytes,
                     L.total);
@@ -513,10 +601,9 @@ extern "C" int bn_attn_decode_paged(const void* q, const void* pool, int64_t poo
     p.part_l = reinterpret_cast<float*>(ws + L.part_l);
     p.part_o = reinterpret_cast<float*>(ws + L.part_o);
     p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.n_rep = Hq / Hkv; p.max_pages = max_pages; p.max_seq_len = max_seq_len;
-    p.chunk = chunk; p.max_chunks = L.max_chunks;
-    p.total_items = B * Hkv * L.max_chunks;
+    p.min_stages = min_tokens / DEC_STAGE_TOKENS;
+    p.max_parts = L.max_parts;
     p.rope_q = rope_q;
-    { const char* e = getenv("BN_DECODE_DEBUG"); p.debug = e ? atoi(e) : 0; }
     p.scale_log2 = scale * LOG2E;
     p.theta = theta;
 
@@ -530,7 +617,9 @@ extern "C" int bn_attn_decode_paged(const void* q, const void* pool, int64_t poo
         configured_dev = dev;
     }
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    int grid = p.total_items < sms ? p.total_items : sms;
+    // no more CTAs than ranges of the minimum length can exist
+    const long long max_ranges = (long long)B * Hkv * ((max_seq_len + min_tokens - 1) / min_tokens + 1);
+    const int grid = (int)(max_ranges < sms ? (max_ranges > 0 ? max_ranges : 1) : sms);
     decode_paged_kernel<<<grid, DEC_THREADS, DEC_SMEM_BYTES, as_stream(stream)>>>(tmap, p);
     return launch_status("bn_attn_decode_paged");
 }

@@ -383,25 +383,38 @@ prefill_kernel_v1(const __grid_constant__ CUtensorMap tmap_k, const __grid_const
 
 
 // ---------------------------------------------------------------------------
-// launch 2, main kernel: one CTA per SM-slot, TWO query tiles in flight
+// launch 2, main kernel: persistent, one CTA per SM, TWO query tiles in flight
 // ---------------------------------------------------------------------------
-// CTA = (batch, query head, pair of 128-row query tiles).  Ten warps:
+// Work unit = (batch, query head, pair of 128-row query tiles); units are ordered
+// heaviest first and dealt round-robin to the CTAs (grid = number of SMs), each
+// CTA walking its units in a loop so that the next unit's Q/K/V loads overlap the
+// current unit's tail.  Ten warps:
 //   warps 0-3  softmax group 0 (query tile 2t)      warp 8  MMA issuer
 //   warps 4-7  softmax group 1 (query tile 2t+1)    warp 9  TMA producer
 // Both tiles read the same K/V stages, so each K/V tile is fetched once per
 // 256 query rows, and the tensor pipe works on one tile (P V, then the next
-// Q K^T) while the other tile's softmax runs.
+// Q K^T) while the other tile's softmax runs.  Q tiles arrive by TMA (double
+// buffered across units) and are rotated in place by their softmax group.
 // TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,320) O1 [320,384)
 //                     P0 [384,448) P1 [448,512)
 // Softmax is ONE pass per tile: the exponent reference is the running maximum
-// of the earlier tiles; if a tile turns out to exceed it by more than 2^8 (or it
-// is the first tile) the warp rescales O, moves the reference and redoes the
-// tile.  A quarter of the exponentials is evaluated on the FMA pipe (Cody-Waite
-// split + degree-3 polynomial) because at head_dim 64 the MUFU unit, not the
-// tensor pipe, is the first limit.
+// of the earlier tiles; if a tile turns out to exceed it by more than 2^8 the
+// warp rescales O, moves the reference and redoes the tile (the first tile of a
+// unit takes its true maximum first).  Part of the exponentials can be evaluated
+// on the FMA pipe (Cody-Waite split + cubic): at head_dim 64 the MUFU unit, not
+// the tensor pipe, is the first limit.
+#if (BN_DBG & 128)
+// timeline instrumentation: the lse buffer receives clock64() stamps of CTA 0's first unit
+#define BN_STAMP(ev, u_, j_) do { if (blockIdx.x == 0 && it == 0 && p.lse) reinterpret_cast<long long*>(p.lse)[((ev) * 2 + (u_)) * 32 + (j_)] = clock64(); } while (0)
+#else
+#define BN_STAMP(ev, u_, j_) do {} while (0)
+#endif
+#ifndef BN_EMU
+#define BN_EMU 0    // of every 8 (pairs of) exponentials, how many go to the FMA pipe
+#endif
 constexpr int P2_THREADS = 320;
 constexpr int P2_NSTAGE = 4;
-constexpr int P2_SMEM_BYTES = 1024 + PF_TILE_BYTES * (2 + 2 * P2_NSTAGE);
+constexpr int P2_SMEM_BYTES = 1024 + PF_TILE_BYTES * (4 + 2 * P2_NSTAGE);
 constexpr uint32_t P2_TMEM_COLS = 512;
 
 __device__ __forceinline__ float ex2_fma_pipe(float x) {
@@ -416,73 +429,90 @@ __device__ __forceinline__ float ex2_fma_pipe(float x) {
     return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
 }
 
-// exp2 of 32 scores -> 16 packed bf16x2; returns the row-sum contribution.  `pmax` tracks the largest p (packed).
+// exp2 of 32 scores -> 16 packed bf16x2.  The row sum is accumulated two-wide in `sum2`; `pmax` tracks the
+// largest p (packed bf16x2).  scale2 / mneg2 hold (scale_log2, scale_log2) and (-m*scale_log2, same).
 template <bool MASK>
-__device__ __forceinline__ float softmax_chunk(const uint32_t (&r)[32], uint32_t (&pk)[16], float scale_log2,
-                                               float mneg, int first_key, int row_last, uint32_t& pmax) {
-    float sum = 0.f;
+__device__ __forceinline__ void softmax_chunk(const uint32_t (&r)[32], uint32_t (&pk)[16], uint64_t scale2,
+                                              uint64_t mneg2, int first_key, int row_last, uint32_t& pmax,
+                                              uint64_t& sum2) {
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
-        const float x0 = fmaf(__uint_as_float(r[i]), scale_log2, mneg);
-        const float x1 = fmaf(__uint_as_float(r[i + 1]), scale_log2, mneg);
-#if (BN_DBG & 4)
-        float p0 = x0, p1 = x1;
-#elif (BN_DBG & 1)
-        float p0 = ex2(x0), p1 = ex2(x1);
-#else
-        float p0 = ((i & 7) == 6) ? ex2_fma_pipe(x0) : ex2(x0);
-        float p1 = ((i & 7) == 6) ? ex2_fma_pipe(x1) : ex2(x1);
-#endif
+        float x0, x1;
+        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), scale2, mneg2), x0, x1);
+        const bool emu = ((i >> 1) & 7) < BN_EMU;
+        float p0 = emu ? ex2_fma_pipe(x0) : ex2(x0);
+        float p1 = emu ? ex2_fma_pipe(x1) : ex2(x1);
         if (MASK) {
             if (first_key + i > row_last) p0 = 0.f;
             if (first_key + i + 1 > row_last) p1 = 0.f;
         }
-        sum += p0 + p1;
+        sum2 = add_f32x2(sum2, pack_f32x2(p0, p1));
         pk[i / 2] = pack_bf16(p0, p1);
-#if !(BN_DBG & 8)
         asm("max.bf16x2 %0, %0, %1;" : "+r"(pmax) : "r"(pk[i / 2]));
-#endif
     }
-    return sum;
+}
+
+struct UnitInfo {
+    int b, h, g, qp;
+    int n_t[2], n_max;
+};
+
+__device__ __forceinline__ UnitInfo unit_info(const PrefillParams& p, int k) {
+    UnitInfo w;
+    const int BH = p.B * p.Hq;
+    const int n_pairs = (p.n_qtiles + 1) / 2;
+    w.qp = n_pairs - 1 - k / BH;               // heaviest (latest) pair of query tiles first
+    const int bh = k % BH;                      // the heads of a KV group are neighbours
+    w.b = bh / p.Hq;
+    w.h = bh % p.Hq;
+    w.g = w.h / p.n_rep;
+    const int n_ktiles_all = (p.S + PF_BN - 1) / PF_BN;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int i0 = (2 * w.qp + u) * PF_BM;
+        if (i0 >= p.S) w.n_t[u] = 0;
+        else w.n_t[u] = p.causal ? min(n_ktiles_all, (i0 + PF_BM - 1 + p.position_offset) / PF_BN + 1) : n_ktiles_all;
+    }
+    w.n_max = max(w.n_t[0], w.n_t[1]);
+    return w;
+}
+
+// Units are sorted heaviest first and dealt to the CTAs in snake order (round r runs left to right when r is
+// even, right to left when odd), which keeps the per-CTA sums within one unit of each other.  -1 = no more.
+__device__ __forceinline__ int unit_of(int round, int n_units) {
+    const int G = gridDim.x, c = blockIdx.x;
+    const int k = round * G + ((round & 1) ? G - 1 - c : c);
+    return k < n_units ? k : -1;
 }
 
 __global__ void __launch_bounds__(P2_THREADS, 1)
-prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
-               const PrefillParams p) {
+prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+               const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p, const int n_units) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bar_q[2], bar_s[2], bar_p[2], bar_o[2];
+    // Q tile barriers are indexed [buffer][tile]
+    __shared__ __align__(8) uint64_t bar_qfull[2][2], bar_qrot[2][2], bar_qfree[2][2];
+    __shared__ __align__(8) uint64_t bar_s[2], bar_p[2], bar_o[2], bar_pv[2];
     __shared__ __align__(8) uint64_t bar_kfull[P2_NSTAGE], bar_vfull[P2_NSTAGE], bar_empty[P2_NSTAGE];
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t sQ = smem0;                                        // 2 tiles
-    const uint32_t sK = smem0 + PF_TILE_BYTES * 2;                    // P2_NSTAGE tiles
-    const uint32_t sV = smem0 + PF_TILE_BYTES * (2 + P2_NSTAGE);      // P2_NSTAGE tiles
-
-    // work unit: heaviest (latest) pair of query tiles first; the heads of a KV group are neighbours
-    const int BH = p.B * p.Hq;
-    const int n_pairs = (p.n_qtiles + 1) / 2;
-    const int qp = n_pairs - 1 - (int)(blockIdx.x / BH);
-    const int bh = blockIdx.x % BH;
-    const int b = bh / p.Hq, h = bh % p.Hq, g = h / p.n_rep;
-    const int n_ktiles_all = (p.S + PF_BN - 1) / PF_BN;
-    int n_t[2];
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-        const int i0 = (2 * qp + u) * PF_BM;
-        if (i0 >= p.S) { n_t[u] = 0; continue; }
-        n_t[u] = p.causal ? min(n_ktiles_all, (i0 + PF_BM - 1 + p.position_offset) / PF_BN + 1) : n_ktiles_all;
-    }
-    const int n_max = max(n_t[0], n_t[1]);
+    const uint32_t sQ = smem0;                                        // [buffer][tile] = 4 tiles
+    const uint32_t sK = smem0 + PF_TILE_BYTES * 4;                    // P2_NSTAGE tiles
+    const uint32_t sV = smem0 + PF_TILE_BYTES * (4 + P2_NSTAGE);      // P2_NSTAGE tiles
 
     if (tid == 0) {
-        for (int u = 0; u < 2; ++u) {
-            mbar_init(smem_u32(&bar_q[u]), 128);
-            mbar_init(smem_u32(&bar_s[u]), 1);
-            mbar_init(smem_u32(&bar_p[u]), (BN_DBG & 2) ? 4 : 128);
-            mbar_init(smem_u32(&bar_o[u]), 1);
+        for (int i = 0; i < 2; ++i) {
+            for (int u = 0; u < 2; ++u) {
+                mbar_init(smem_u32(&bar_qfull[i][u]), 1);
+                mbar_init(smem_u32(&bar_qrot[i][u]), 4);
+                mbar_init(smem_u32(&bar_qfree[i][u]), 1);
+            }
+            mbar_init(smem_u32(&bar_s[i]), 1);
+            mbar_init(smem_u32(&bar_p[i]), 4);
+            mbar_init(smem_u32(&bar_o[i]), 1);
+            mbar_init(smem_u32(&bar_pv[i]), 1);
         }
         for (int s = 0; s < P2_NSTAGE; ++s) {
             mbar_init(smem_u32(&bar_kfull[s]), 1);
@@ -504,242 +534,303 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant
     if (warp == 9) {
         // ---------------------------------------------------------- TMA producer
         if (lane == 0) {
+            prefetch_tensormap(&tmap_q);
             prefetch_tensormap(&tmap_k);
             prefetch_tensormap(&tmap_v);
             int stage = 0;
             uint32_t phase = 0;
-            for (int j = 0; j < n_max; ++j) {
-                if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &s_abort)) break;
-                mbar_arrive_expect_tx(smem_u32(&bar_kfull[stage]), PF_TILE_BYTES);
-                tma_load_4d(sK + stage * PF_TILE_BYTES, &tmap_k, 0, g, j * PF_BN, b, smem_u32(&bar_kfull[stage]));
-                mbar_arrive_expect_tx(smem_u32(&bar_vfull[stage]), PF_TILE_BYTES);
-                tma_load_4d(sV + stage * PF_TILE_BYTES, &tmap_v, 0, g, j * PF_BN, b, smem_u32(&bar_vfull[stage]));
-                if (++stage == P2_NSTAGE) { stage = 0; phase ^= 1u; }
+            int q_use[2] = {0, 0};        // how many units have used tile slot u so far
+            bool ok = true;
+            for (int it = 0; ok; ++it) {
+                const int k = unit_of(it, n_units);
+                if (k < 0) break;
+                const UnitInfo w = unit_info(p, k);
+                for (int u = 0; u < 2 && ok; ++u) {
+                    if (w.n_t[u] == 0) continue;
+                    const int buf = q_use[u] & 1;
+                    const uint32_t par = (q_use[u] >> 1) & 1;
+                    ++q_use[u];
+                    ok = mbar_wait(smem_u32(&bar_qfree[buf][u]), par ^ 1u, &s_abort);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(smem_u32(&bar_qfull[buf][u]), PF_TILE_BYTES);
+                    tma_load_4d(sQ + (buf * 2 + u) * PF_TILE_BYTES, &tmap_q, 0, w.h, (2 * w.qp + u) * PF_BM, w.b,
+                                smem_u32(&bar_qfull[buf][u]));
+                }
+                for (int j = 0; ok && j < w.n_max; ++j) {
+                    ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &s_abort);
+                    if (!ok) break;
+                    BN_STAMP(6, 0, j);
+                    mbar_arrive_expect_tx(smem_u32(&bar_kfull[stage]), PF_TILE_BYTES);
+                    tma_load_4d(sK + stage * PF_TILE_BYTES, &tmap_k, 0, w.g, j * PF_BN, w.b, smem_u32(&bar_kfull[stage]));
+                    mbar_arrive_expect_tx(smem_u32(&bar_vfull[stage]), PF_TILE_BYTES);
+                    tma_load_4d(sV + stage * PF_TILE_BYTES, &tmap_v, 0, w.g, j * PF_BN, w.b, smem_u32(&bar_vfull[stage]));
+                    if (++stage == P2_NSTAGE) { stage = 0; phase ^= 1u; }
+                }
             }
         }
     } else if (warp == 8) {
         // ------------------------------------------------------------ MMA issuer
         constexpr uint32_t IDESC_QK = tc::idesc_bf16(PF_BM, PF_BN, 0);
         constexpr uint32_t IDESC_PV = tc::idesc_bf16(PF_BM, PF_D, 1);
-        auto issue_qk = [&](int u, int stage) {
-            if (lane == 0) {
-                tc::fence_after_sync();
-#if !(BN_DBG & 64)
-#pragma unroll
-                for (int kk = 0; kk < PF_D / 16; ++kk)
-                    tc::mma_ss(tmem + u * 128, tc::smem_desc_sw128(sQ + u * PF_TILE_BYTES + kk * 32),
-                               tc::smem_desc_sw128(sK + stage * PF_TILE_BYTES + kk * 32), IDESC_QK, kk > 0);
-#endif
-                tc::commit(smem_u32(&bar_s[u]));
-            }
-            __syncwarp();
-        };
-        bool ok = true;
-        for (int u = 0; u < 2 && ok; ++u)
-            if (n_t[u] > 0) ok = mbar_wait(smem_u32(&bar_q[u]), 0, &s_abort);
-        if (ok && n_max > 0) ok = mbar_wait(smem_u32(&bar_kfull[0]), 0, &s_abort);
-        if (ok) {
-            if (n_t[0] > 0) issue_qk(0, 0);
-            if (n_t[1] > 0) issue_qk(1, 0);
-        }
         int stage = 0;
         uint32_t phase = 0;
-        for (int j = 0; ok && j < n_max; ++j) {
-            const int nstage = (stage + 1 == P2_NSTAGE) ? 0 : stage + 1;
-            const uint32_t nphase = (stage + 1 == P2_NSTAGE) ? phase ^ 1u : phase;
-            bool next_k_ready = false;
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                if (j >= n_t[u]) continue;
-                // O_u += P_u(j) V(j)
-                ok = mbar_wait(smem_u32(&bar_p[u]), j & 1, &s_abort) &&
-                     mbar_wait(smem_u32(&bar_vfull[stage]), phase, &s_abort);
-                if (!ok) break;
-                if (lane == 0) {
+        int q_use[2] = {0, 0};
+        uint32_t tiles_done[2] = {0, 0};    // tiles of slot u completed so far (parity of bar_s / bar_p)
+        uint32_t units_done[2] = {0, 0};
+        bool ok = true;
+        for (int it = 0; ok; ++it) {
+            const int k = unit_of(it, n_units);
+            if (k < 0) break;
+            const UnitInfo w = unit_info(p, k);
+            uint32_t qaddr[2] = {0, 0};
+            for (int u = 0; u < 2 && ok; ++u) {
+                if (w.n_t[u] == 0) continue;
+                const int buf = q_use[u] & 1;
+                const uint32_t par = (q_use[u] >> 1) & 1;
+                ++q_use[u];
+                qaddr[u] = sQ + (buf * 2 + u) * PF_TILE_BYTES;
+                ok = mbar_wait(smem_u32(&bar_qrot[buf][u]), par, &s_abort);
+            }
+            if (!ok) break;
+            // S_u = Q_u K(j)^T; the last one of the unit also frees the Q buffer
+            auto issue_qk = [&](int u, int st, int j) {
+                if (elect_one()) {
                     tc::fence_after_sync();
-#if !(BN_DBG & 64)
 #pragma unroll
-                    for (int kk = 0; kk < PF_BN / 16; ++kk)
-                        tc::mma_ts(tmem + 256 + u * 64, tmem + 384 + u * 64 + kk * 8,
-                                   tc::smem_desc_sw128(sV + stage * PF_TILE_BYTES + kk * 2048), IDESC_PV,
-                                   (j > 0) || (kk > 0));
-#endif
-                    if (j == n_t[u] - 1) tc::commit(smem_u32(&bar_o[u]));
-                    const bool last_user = (u == 1) || (j >= n_t[1]);
-                    if (last_user) tc::commit(smem_u32(&bar_empty[stage]));   // K(j)/V(j) may be overwritten
+                    for (int kk = 0; kk < PF_D / 16; ++kk)
+                        tc::mma_ss(tmem + u * 128, tc::smem_desc_sw128(qaddr[u] + kk * 32),
+                                   tc::smem_desc_sw128(sK + st * PF_TILE_BYTES + kk * 32), IDESC_QK, kk > 0);
+                    tc::commit(smem_u32(&bar_s[u]));
+                    if (j == w.n_t[u] - 1) tc::commit(smem_u32(&bar_qfree[(q_use[u] - 1) & 1][u]));
                 }
                 __syncwarp();
-                // S_u(j+1) = Q_u K(j+1)^T: its S columns are free because P_u(j) has been written
-                if (j + 1 < n_t[u]) {
-                    if (!next_k_ready) {
-                        ok = mbar_wait(smem_u32(&bar_kfull[nstage]), nphase, &s_abort);
-                        if (!ok) break;
-                        next_k_ready = true;
+            };
+            if (w.n_max > 0) ok = mbar_wait(smem_u32(&bar_kfull[stage]), phase, &s_abort);
+            if (!ok) break;
+            if (lane == 0) BN_STAMP(0, 1, 0);
+            if (w.n_t[0] > 0) issue_qk(0, stage, 0);
+            if (w.n_t[1] > 0) issue_qk(1, stage, 0);
+            for (int j = 0; ok && j < w.n_max; ++j) {
+                const int nstage = (stage + 1 == P2_NSTAGE) ? 0 : stage + 1;
+                const uint32_t nphase = (stage + 1 == P2_NSTAGE) ? phase ^ 1u : phase;
+                bool next_k_ready = false;
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    if (j >= w.n_t[u]) continue;
+                    ok = mbar_wait(smem_u32(&bar_p[u]), (tiles_done[u] + j) & 1, &s_abort);
+                    if (!ok) break;
+                    if (lane == 0) BN_STAMP(3, u, j);
+                    // S_u(j+1) = Q_u K(j+1)^T first: its S columns are free because P_u(j) has been written, and
+                    // the softmax of tile j+1 can start while P_u(j) V(j) still runs
+                    if (j + 1 < w.n_t[u]) {
+                        if (!next_k_ready) {
+                            ok = mbar_wait(smem_u32(&bar_kfull[nstage]), nphase, &s_abort);
+                            if (!ok) break;
+                            next_k_ready = true;
+                        }
+                        issue_qk(u, nstage, j + 1);
                     }
-                    issue_qk(u, nstage);
+                    // O_u += P_u(j) V(j)
+                    ok = mbar_wait(smem_u32(&bar_vfull[stage]), phase, &s_abort);
+                    if (!ok) break;
+                    if (elect_one()) {
+                        tc::fence_after_sync();
+#pragma unroll
+                        for (int kk = 0; kk < PF_BN / 16; ++kk)
+                            tc::mma_ts(tmem + 256 + u * 64, tmem + 384 + u * 64 + kk * 8,
+                                       tc::smem_desc_sw128(sV + stage * PF_TILE_BYTES + kk * 2048), IDESC_PV,
+                                       (j > 0) || (kk > 0));
+                        tc::commit(smem_u32(&bar_pv[u]));                          // P_u(j) may be overwritten
+                        if (j == w.n_t[u] - 1) tc::commit(smem_u32(&bar_o[u]));
+                        const bool last_user = (u == 1) || (j >= w.n_t[1]);
+                        if (last_user) tc::commit(smem_u32(&bar_empty[stage]));   // K(j)/V(j) may be overwritten
+                    }
+                    __syncwarp();
+                    if (lane == 0) BN_STAMP(4, u, j);
                 }
+                stage = nstage;
+                phase = nphase;
             }
-            stage = nstage;
-            phase = nphase;
+            tiles_done[0] += w.n_t[0];
+            tiles_done[1] += w.n_t[1];
+            units_done[0] += w.n_t[0] > 0;
+            units_done[1] += w.n_t[1] > 0;
         }
     } else {
         // ------------------------------------------- softmax groups (warps 0..7)
-        const int u = warp / 4;                     // which query tile
+        const int u = warp / 4;                     // which query tile of the pair
         const int row = tid % 128;                  // TMEM lane = query row inside the tile
-        const int i0 = (2 * qp + u) * PF_BM;
-        const int gi = i0 + row;
-        const int nt = n_t[u];
         const uint32_t lane_base = ((uint32_t)((warp % 4) * 32)) << 16;
         const uint32_t tS = tmem + lane_base + u * 128;
         const uint32_t tO = tmem + lane_base + 256 + u * 64;
         const uint32_t tP = tmem + lane_base + 384 + u * 64;
-
-        if (nt > 0) {
-            // prologue: rotate the Q row and store it, 128-byte-swizzled, K-major
-            uint4 qv[8];
-            const bool valid = gi < p.S;
-            const uint4* src = reinterpret_cast<const uint4*>(p.q + (((size_t)b * p.S + (valid ? gi : 0)) * p.Hq + h) * PF_D);
-            const float4* tab = reinterpret_cast<const float4*>(p.table + (size_t)(valid ? gi : 0) * (PF_D / 2));
-#pragma unroll
-            for (int c = 0; c < 8; ++c) qv[c] = valid ? __ldg(src + c) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                uint32_t w[4] = {qv[c].x, qv[c].y, qv[c].z, qv[c].w};
-#pragma unroll
-                for (int e = 0; e < 4; e += 2) {
-                    const float4 cs = __ldg(tab + c * 2 + e / 2);
-                    float x0 = bf16_lo(w[e]), x1 = bf16_hi(w[e]);
-                    w[e] = pack_bf16(x0 * cs.x - x1 * cs.y, x0 * cs.y + x1 * cs.x);
-                    x0 = bf16_lo(w[e + 1]); x1 = bf16_hi(w[e + 1]);
-                    w[e + 1] = pack_bf16(x0 * cs.z - x1 * cs.w, x0 * cs.w + x1 * cs.z);
-                }
-                const uint32_t dst = sQ + u * PF_TILE_BYTES + row * 128 + ((c ^ (row & 7)) << 4);
-                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
-                             : "memory");
-            }
-            fence_proxy_async_smem();
-            mbar_arrive(smem_u32(&bar_q[u]));
-        }
-
-        float m_ref = -INFINITY;   // exponent reference, raw score units
-        float l_run = 0.f;
+        int q_use = 0;
+        uint32_t tiles_done = 0, units_done = 0;
         bool ok = true;
-        const int row_last = p.causal ? min(p.S - 1, gi + p.position_offset) : p.S - 1;
-        const int tile_free_last = p.causal ? min(p.S - 1, i0 + p.position_offset) : p.S - 1;   // no mask needed up to here
+        for (int it = 0; ok; ++it) {
+            const int k = unit_of(it, n_units);
+            if (k < 0) break;
+            const UnitInfo w = unit_info(p, k);
+            const int nt = w.n_t[u];
+            if (nt == 0) continue;
+            const int b = w.b, h = w.h;
+            const int i0 = (2 * w.qp + u) * PF_BM;
+            const int gi = i0 + row;
+            if (tid == 0) BN_STAMP(0, 0, 0);
 
-        for (int j = 0; j < nt; ++j) {
-            ok = mbar_wait(smem_u32(&bar_s[u]), j & 1, &s_abort);
-            if (!ok) break;
-            tc::fence_after_sync();
-            const int j0 = j * PF_BN;
-            const bool need_mask = (j0 + PF_BN - 1) > tile_free_last;
-
-            // row maximum of this tile (raw score units), by re-reading S: first tile and the rare redo only
-            auto tile_max = [&]() {
-                float tmax = -INFINITY;
+            // prologue: rotate the TMA-loaded Q row in place (128-byte-swizzled, K-major)
+            {
+                const int buf = q_use & 1;
+                const uint32_t par = (q_use >> 1) & 1;
+                ++q_use;
+                const float4* tab = reinterpret_cast<const float4*>(p.table + (size_t)min(gi, p.S - 1) * (PF_D / 2));
+                float4 cs[16];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t r[32];
-                    tc::ld32(tS + c * 32, r);
-                    tc::wait_ld(r);
+                for (int c = 0; c < 16; ++c) cs[c] = __ldg(tab + c);
+                ok = mbar_wait(smem_u32(&bar_qfull[buf][u]), par, &s_abort);
+                if (!ok) break;
+                const uint32_t qrow = sQ + (buf * 2 + u) * PF_TILE_BYTES + row * 128;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (!need_mask || j0 + c * 32 + i <= row_last) tmax = fmaxf(tmax, __uint_as_float(r[i]));
-                }
-                return tmax;
-            };
-            // one pass over the tile: P = exp2(S * scale_log2 - m_ref * scale_log2) -> TMEM, with the load of the
-            // next 32 columns in flight while the current 32 are processed
-            auto tile_pass = [&](float mneg, uint32_t& pmax) {
-                float lsum = 0.f;
-                uint32_t r0[32], r1[32], pk[16];
-                tc::ld32(tS + 0, r0);
-                tc::wait_ld(r0);
-                tc::ld32(tS + 32, r1);
-                lsum += need_mask ? softmax_chunk<true>(r0, pk, p.scale_log2, mneg, j0, row_last, pmax)
-                                  : softmax_chunk<false>(r0, pk, p.scale_log2, mneg, j0, row_last, pmax);
-#if !(BN_DBG & 16)
-                tc::st16(tP + 0, pk);
-#endif
-                tc::wait_ld(r1);
-                tc::ld32(tS + 64, r0);
-                lsum += need_mask ? softmax_chunk<true>(r1, pk, p.scale_log2, mneg, j0 + 32, row_last, pmax)
-                                  : softmax_chunk<false>(r1, pk, p.scale_log2, mneg, j0 + 32, row_last, pmax);
-#if !(BN_DBG & 16)
-                tc::st16(tP + 16, pk);
-#endif
-                tc::wait_ld(r0);
-                tc::ld32(tS + 96, r1);
-                lsum += need_mask ? softmax_chunk<true>(r0, pk, p.scale_log2, mneg, j0 + 64, row_last, pmax)
-                                  : softmax_chunk<false>(r0, pk, p.scale_log2, mneg, j0 + 64, row_last, pmax);
-#if !(BN_DBG & 16)
-                tc::st16(tP + 32, pk);
-#endif
-                tc::wait_ld(r1);
-                lsum += need_mask ? softmax_chunk<true>(r1, pk, p.scale_log2, mneg, j0 + 96, row_last, pmax)
-                                  : softmax_chunk<false>(r1, pk, p.scale_log2, mneg, j0 + 96, row_last, pmax);
-#if !(BN_DBG & 16)
-                tc::st16(tP + 48, pk);
-#endif
-                return lsum;
-            };
-
-#if (BN_DBG & 32)
-            uint32_t pmax = 0;
-            float lsum = 1.f;
-#else
-            if (j == 0) {
-                const float tmax = tile_max();
-                if (tmax > -INFINITY) m_ref = tmax;
-            }
-            uint32_t pmax = 0;           // bf16x2 (+0, +0)
-            float lsum = tile_pass(m_ref == -INFINITY ? 0.f : -m_ref * p.scale_log2, pmax);
-#endif
-            // did any p leave the safe range (> 2^8, incl. inf/NaN)?  bf16 bit patterns are monotone for p >= 0
-            const bool over = max(pmax & 0xffffu, pmax >> 16) > 0x4380u;   // bf16(256.0)
-            if (__any_sync(0xffffffffu, over)) {
-                // rare: the tile exceeds the reference by more than 2^8.  Move the reference to the true row
-                // maximum, rescale O and l, redo the tile.
-                const float m_new = fmaxf(m_ref, tile_max());
-                const float m_upd = m_new == -INFINITY ? m_ref : m_new;
-                if (j > 0) {
-                    const float alpha = m_ref == -INFINITY ? 0.f : ex2((m_ref - m_upd) * p.scale_log2);
-                    l_run *= alpha;
+                for (int c = 0; c < 8; ++c) {
+                    const uint32_t addr = qrow + ((c ^ (row & 7)) << 4);
+                    uint32_t w4[4];
+                    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(w4[0]), "=r"(w4[1]), "=r"(w4[2]), "=r"(w4[3]) : "r"(addr));
 #pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        uint32_t ro[32];
-                        tc::ld32(tO + c * 32, ro);
-                        tc::wait_ld(ro);
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) ro[i] = __float_as_uint(__uint_as_float(ro[i]) * alpha);
-                        tc::st32(tO + c * 32, ro);
+                    for (int e = 0; e < 4; e += 2) {
+                        const float4 t4 = cs[c * 2 + e / 2];   // (cos, sin) of pairs 4c+e, 4c+e+1
+                        float x0 = bf16_lo(w4[e]), x1 = bf16_hi(w4[e]);
+                        w4[e] = pack_bf16(x0 * t4.x - x1 * t4.y, x0 * t4.y + x1 * t4.x);
+                        x0 = bf16_lo(w4[e + 1]); x1 = bf16_hi(w4[e + 1]);
+                        w4[e + 1] = pack_bf16(x0 * t4.z - x1 * t4.w, x0 * t4.w + x1 * t4.z);
                     }
+                    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(w4[0]), "r"(w4[1]), "r"(w4[2]),
+                                 "r"(w4[3]) : "memory");
                 }
-                m_ref = m_upd;
-                pmax = 0;
-                lsum = tile_pass(m_ref == -INFINITY ? 0.f : -m_ref * p.scale_log2, pmax);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bar_qrot[buf][u]));
             }
-            l_run += lsum;
-            tc::wait_st();
-            tc::fence_before_sync();
-#if (BN_DBG & 2)
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bar_p[u]));
-#else
-            mbar_arrive(smem_u32(&bar_p[u]));
-#endif
-        }
 
-        // epilogue: O / l -> bf16 -> global
-        if (ok && nt > 0) ok = mbar_wait(smem_u32(&bar_o[u]), 0, &s_abort);
-        if (ok && nt > 0) {
+            float m_ref = -INFINITY;   // exponent reference, raw score units
+            float l_run = 0.f;
+            const int row_last = p.causal ? min(p.S - 1, gi + p.position_offset) : p.S - 1;
+            const int tile_free_last = p.causal ? min(p.S - 1, i0 + p.position_offset) : p.S - 1;   // no mask needed up to here
+
+            for (int j = 0; j < nt; ++j) {
+                ok = mbar_wait(smem_u32(&bar_s[u]), (tiles_done + j) & 1, &s_abort);
+                if (!ok) break;
+                if (row == 0) BN_STAMP(1, u, j);
+                tc::fence_after_sync();
+                const int j0 = j * PF_BN;
+                const bool need_mask = (j0 + PF_BN - 1) > tile_free_last;
+
+                // row maximum of this tile (raw score units), by re-reading S: first tile and the rare redo only
+                auto tile_max = [&]() {
+                    float tmax = -INFINITY;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t r[32];
+                        tc::ld32(tS + c * 32, r);
+                        tc::wait_ld(r);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (!need_mask || j0 + c * 32 + i <= row_last) tmax = fmaxf(tmax, __uint_as_float(r[i]));
+                    }
+                    return tmax;
+                };
+                // one pass over the tile: P = exp2(S * scale_log2 - m_ref * scale_log2) -> TMEM, with the load of the
+                // next 32 columns in flight while the current 32 are processed
+                auto tile_pass = [&](float mneg, uint32_t& pmax, bool first_store_needs_pv) {
+                    uint64_t sum2 = 0;   // (0.f, 0.f)
+                    const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2), mneg2 = pack_f32x2(mneg, mneg);
+                    uint32_t r0[32], r1[32], pk[16];
+                    tc::ld32(tS + 0, r0);
+                    tc::wait_ld(r0);
+                    tc::ld32(tS + 32, r1);
+                    if (need_mask) softmax_chunk<true>(r0, pk, scale2, mneg2, j0, row_last, pmax, sum2);
+                    else softmax_chunk<false>(r0, pk, scale2, mneg2, j0, row_last, pmax, sum2);
+                    // P(j-1) is still being read by its P V until bar_pv says otherwise
+                    bool good = true;
+                    if (first_store_needs_pv) {
+                        good = mbar_wait(smem_u32(&bar_pv[u]), (tiles_done + j - 1) & 1, &s_abort);
+                        tc::fence_after_sync();
+                    }
+                    tc::st16(tP + 0, pk);
+                    tc::wait_ld(r1);
+                    tc::ld32(tS + 64, r0);
+                    if (need_mask) softmax_chunk<true>(r1, pk, scale2, mneg2, j0 + 32, row_last, pmax, sum2);
+                    else softmax_chunk<false>(r1, pk, scale2, mneg2, j0 + 32, row_last, pmax, sum2);
+                    tc::st16(tP + 16, pk);
+                    tc::wait_ld(r0);
+                    tc::ld32(tS + 96, r1);
+                    if (need_mask) softmax_chunk<true>(r0, pk, scale2, mneg2, j0 + 64, row_last, pmax, sum2);
+                    else softmax_chunk<false>(r0, pk, scale2, mneg2, j0 + 64, row_last, pmax, sum2);
+                    tc::st16(tP + 32, pk);
+                    tc::wait_ld(r1);
+                    if (need_mask) softmax_chunk<true>(r1, pk, scale2, mneg2, j0 + 96, row_last, pmax, sum2);
+                    else softmax_chunk<false>(r1, pk, scale2, mneg2, j0 + 96, row_last, pmax, sum2);
+                    tc::st16(tP + 48, pk);
+                    float s0, s1;
+                    unpack_f32x2(sum2, s0, s1);
+                    return good ? s0 + s1 : NAN;
+                };
+
+                if (j == 0) {
+                    const float tmax = tile_max();
+                    if (tmax > -INFINITY) m_ref = tmax;
+                }
+                uint32_t pmax = 0;           // bf16x2 (+0, +0)
+                float lsum = tile_pass(m_ref == -INFINITY ? 0.f : -m_ref * p.scale_log2, pmax, j > 0);
+                if (s_abort) { ok = false; break; }
+                // did any p leave the safe range (> 2^8, incl. inf)?  bf16 bit patterns are monotone for p >= 0
+                const bool over = max(pmax & 0xffffu, pmax >> 16) > 0x4380u;   // bf16(256.0)
+                if (__any_sync(0xffffffffu, over)) {
+                    // rare: the tile exceeds the reference by more than 2^8.  Move the reference to the true row
+                    // maximum, rescale O and l, redo the tile.
+                    const float m_new = fmaxf(m_ref, tile_max());
+                    const float m_upd = m_new == -INFINITY ? m_ref : m_new;
+                    if (j > 0) {
+                        const float alpha = m_ref == -INFINITY ? 0.f : ex2((m_ref - m_upd) * p.scale_log2);
+                        l_run *= alpha;
+#pragma unroll
+                        for (int c = 0; c < 2; ++c) {
+                            uint32_t ro[32];
+                            tc::ld32(tO + c * 32, ro);
+                            tc::wait_ld(ro);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) ro[i] = __float_as_uint(__uint_as_float(ro[i]) * alpha);
+                            tc::st32(tO + c * 32, ro);
+                        }
+                    }
+                    m_ref = m_upd;
+                    pmax = 0;
+                    lsum = tile_pass(m_ref == -INFINITY ? 0.f : -m_ref * p.scale_log2, pmax, false);
+                }
+                l_run += lsum;
+                tc::wait_st();
+                tc::fence_before_sync();
+                if (row == 0) BN_STAMP(2, u, j);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bar_p[u]));
+            }
+            if (!ok) break;
+            tiles_done += nt;
+
+            // epilogue: O / l -> bf16 -> global
+            ok = mbar_wait(smem_u32(&bar_o[u]), units_done & 1, &s_abort);
+            ++units_done;
+            if (!ok) break;
+            if (row == 0) BN_STAMP(5, u, 0);
             tc::fence_after_sync();
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             __nv_bfloat16* dst = p.out + (((size_t)b * p.S + gi) * p.Hq + h) * PF_D;
             uint32_t r0[32], r1[32];
             tc::ld32(tO, r0);
             tc::ld32(tO + 32, r1);
+            tc::wait_ld(r0);
             tc::wait_ld(r1);
+            // the next unit's first P V overwrites O only after this group's next P arrive, which follows these loads
             if (gi < p.S) {
 #pragma unroll
                 for (int v = 0; v < 4; ++v) {
@@ -759,10 +850,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant
                     o4.w = pack_bf16(__uint_as_float(r1[v * 8 + 6]) * inv, __uint_as_float(r1[v * 8 + 7]) * inv);
                     *reinterpret_cast<uint4*>(dst + 32 + v * 8) = o4;
                 }
+#if !(BN_DBG & 128)
                 if (p.lse)
                     p.lse[((size_t)b * p.Hq + h) * p.S + gi] =
                         l_run > 0.f ? (m_ref * p.scale_log2 + log2f(l_run)) * PF_LN2 : -INFINITY;
+#endif
             }
+            if (row == 0) BN_STAMP(5, u, 1);
         }
     }
 
@@ -836,6 +930,13 @@ extern "C" int bn_attn_prefill_bf16(const void* q, const void* k, const void* v,
     if (int rc = make_tensor_map(&tmap_v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, v, dims, strides, box,
                                  CU_TENSOR_MAP_SWIZZLE_128B))
         return rc;
+    // Q as (D, Hq, S, B); one box = 128 query rows of one head
+    CUtensorMap tmap_q;
+    const uint64_t qdims[4] = {(uint64_t)PF_D, (uint64_t)Hq, (uint64_t)S, (uint64_t)B};
+    const uint64_t qstrides[3] = {(uint64_t)PF_D * 2, (uint64_t)Hq * PF_D * 2, (uint64_t)S * Hq * PF_D * 2};
+    if (int rc = make_tensor_map(&tmap_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, q, qdims, qstrides, box,
+                                 CU_TENSOR_MAP_SWIZZLE_128B))
+        return rc;
 
     PrefillParams p;
     p.q = static_cast<const __nv_bfloat16*>(q);
@@ -862,8 +963,11 @@ extern "C" int bn_attn_prefill_bf16(const void* q, const void* k, const void* v,
     if (flags & BN_PREFILL_SINGLE_TILE_KERNEL) {
         prefill_kernel_v1<<<(unsigned)(n_qtiles * B * Hq), PF_THREADS, PF_SMEM_BYTES, st>>>(tmap_k, tmap_v, p);
     } else {
-        const long long n_pairs = (n_qtiles + 1) / 2;
-        prefill_kernel<<<(unsigned)(n_pairs * B * Hq), P2_THREADS, P2_SMEM_BYTES, st>>>(tmap_k, tmap_v, p);
+        const long long n_units = (n_qtiles + 1) / 2 * B * Hq;
+        int sms = 0;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const unsigned grid = (unsigned)(n_units < sms ? n_units : sms);
+        prefill_kernel<<<grid, P2_THREADS, P2_SMEM_BYTES, st>>>(tmap_q, tmap_k, tmap_v, p, (int)n_units);
     }
     return launch_status("bn_attn_prefill_bf16");
 }
