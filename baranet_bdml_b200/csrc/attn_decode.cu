@@ -15,15 +15,18 @@
 //     shared-memory stages with TMA tensor loads (one 4 KB box = K and V of one
 //     (page, head), 128-byte swizzle), completion counted on mbarriers; page
 //     numbers are fetched one stage ahead.
-//   * Four consumer warps each take two pages (32 tokens) of a stage.  All 8
+//   * Eight consumer warps each take two pages (32 tokens) of a stage, as two
+//     independent instruction chains.  All 8
 //     query heads of the GQA group are served from the one K/V read:
 //       S^T (16 tokens x 8 heads) = K_page (16 x 64) . Q^T (64 x 8)
 //       O^T (64 dims  x 8 heads) += V_page^T (64 x 16) . P^T (16 x 8)
 //     as m16n8k16 bf16 MMAs with fp32 accumulation; softmax is online, base 2.
-//   * At the end of a segment the four warps merge (m, l, O) in shared memory.
-//     A (sequence, head) that spans several CTAs leaves fp32 partials in scratch
-//     memory; the CTA that delivers the last partial performs the log-sum-exp
-//     combine (atomic ticket, nobody spins on another CTA) and re-arms the ticket.
+//   * At the end of a segment the consumer warps merge (m, l, O) in shared
+//     memory.  A (sequence, head) that spans several CTAs leaves fp32 partials
+//     in scratch memory; a tenth warp takes the ticket for it and, in the CTA
+//     that delivers the last partial, performs the log-sum-exp combine (nobody
+//     spins on another CTA) and re-arms the ticket, so that the consumers never
+//     wait on global memory at a segment boundary.
 //   * Every wait is bounded; on expiry the kernel raises the error word in the
 //     scratch header and returns.
 #include <math.h>
@@ -36,18 +39,32 @@ namespace bn {
 
 using namespace ptx;
 
+#ifndef BN_DDBG
+#define BN_DDBG 0
+#endif
+#if BN_DDBG
+#define FSTAMP(tag) do { if (BN_DDBG > 1 && blockIdx.x == 5 && threadIdx.x == 0 && p.lse && fidx < 120) { reinterpret_cast<long long*>(p.lse)[148 * 8 + 2 * fidx] = (tag); reinterpret_cast<long long*>(p.lse)[148 * 8 + 2 * fidx + 1] = clock64(); ++fidx; } } while (0)
+#define DSTAMP(i) do { if (threadIdx.x == (i == 2 || i == 3 || i == 4 || i == 5 ? 0 : 0) && p.lse) reinterpret_cast<unsigned long long*>(p.lse)[blockIdx.x * 8 + (i)] = globaltimer_ns(); } while (0)
+#else
+#define DSTAMP(i) do {} while (0)
+#define FSTAMP(tag) do {} while (0)
+#endif
 constexpr int DEC_D = 64;
 constexpr int DEC_G = 8;                    // query heads per KV head served by one MMA (n = 8)
-constexpr int DEC_STAGE_TOKENS = 128;
-constexpr int DEC_PAGES_PER_STAGE = DEC_STAGE_TOKENS / BN_PAGE_TOKENS;  // 8
+constexpr int DEC_STAGE_TOKENS = 256;
+constexpr int DEC_PAGES_PER_STAGE = DEC_STAGE_TOKENS / BN_PAGE_TOKENS;  // 16
 constexpr int DEC_BOX_ROWS = 2 * BN_PAGE_TOKENS;                        // K rows then V rows
 constexpr int DEC_BOX_BYTES = DEC_BOX_ROWS * DEC_D * 2;                 // 4096
-constexpr int DEC_STAGE_BYTES = DEC_PAGES_PER_STAGE * DEC_BOX_BYTES;    // 32768
-constexpr int DEC_NSTAGES = 6;
-constexpr int DEC_CWARPS = 4;
-constexpr int DEC_THREADS = (DEC_CWARPS + 1) * 32;
+constexpr int DEC_STAGE_BYTES = DEC_PAGES_PER_STAGE * DEC_BOX_BYTES;    // 65536
+constexpr int DEC_NSTAGES = 3;
+constexpr int DEC_CWARPS = 8;                                            // consumer warps
+constexpr int DEC_PPW = DEC_PAGES_PER_STAGE / DEC_CWARPS;                // pages per warp and stage
+constexpr int DEC_CTHREADS = DEC_CWARPS * 32;
+constexpr int DEC_DPT = DEC_G * DEC_D / DEC_CTHREADS;                    // output dims per thread in the merge (2)
+constexpr int DEC_TPH = DEC_D / DEC_DPT;                                 // threads per head in the merge
+constexpr int DEC_THREADS = (DEC_CWARPS + 2) * 32;                      // + producer warp + combine warp
 constexpr int DEC_SMEM_BYTES = DEC_NSTAGES * DEC_STAGE_BYTES + 1024;
-constexpr int DEC_MAX_SEQS = 2048;          // sequences per launch (prefix table in shared memory)
+constexpr int DEC_MAX_SEQS = 1024;          // sequences per launch (prefix table in shared memory)
 constexpr int DEC_DEFAULT_MIN_TOKENS = 1024;   // a CTA's range is never shorter than this
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
@@ -75,7 +92,10 @@ static DecodeLayout decode_layout(int B, int Hkv, int max_seq_len, int min_token
     return L;
 }
 
-static int pick_min_tokens(int chunk_tokens) { return chunk_tokens > 0 ? chunk_tokens : DEC_DEFAULT_MIN_TOKENS; }
+static int pick_min_tokens(int chunk_tokens) {
+    const int t = chunk_tokens > 0 ? chunk_tokens : DEC_DEFAULT_MIN_TOKENS;
+    return (t + DEC_STAGE_TOKENS - 1) / DEC_STAGE_TOKENS * DEC_STAGE_TOKENS;   // whole stages
+}
 
 struct DecodeParams {
     const __nv_bfloat16* q;
@@ -95,22 +115,20 @@ struct DecodeParams {
 // The launch-wide schedule, derived from seq_lens by every thread of every CTA.
 struct Schedule {
     const int* prefix;     // shared memory: prefix[b] = sum of stages of sequences < b (one KV head)
+    const int* len;        // shared memory: clamped sequence lengths
     int Hkv, B;
-    long long T;           // all stages of the launch
+    int T;                 // all stages of the launch (< 2^31)
     int G;                 // CTAs that take part
     __device__ __forceinline__ int nst(int b) const { return prefix[b + 1] - prefix[b]; }
-    __device__ __forceinline__ long long seg_begin(int b, int g) const {
-        return (long long)Hkv * prefix[b] + (long long)g * nst(b);
-    }
-    __device__ __forceinline__ long long range_begin(int cta) const { return (long long)cta * T / G; }
+    __device__ __forceinline__ int range_begin(int cta) const { return (int)((long long)cta * T / G); }
     // the CTA whose range holds global stage x
-    __device__ __forceinline__ int cta_of(long long x) const { return (int)(((x + 1) * G - 1) / T); }
+    __device__ __forceinline__ int cta_of(int x) const { return (int)((((long long)x + 1) * G - 1) / T); }
     // first sequence b with Hkv * prefix[b + 1] > x
-    __device__ __forceinline__ int seq_of(long long x) const {
+    __device__ __forceinline__ int seq_of(int x) const {
         int lo = 0, hi = B - 1;
         while (lo < hi) {
             int mid = (lo + hi) >> 1;
-            if ((long long)Hkv * prefix[mid + 1] > x) hi = mid; else lo = mid + 1;
+            if (Hkv * prefix[mid + 1] > x) hi = mid; else lo = mid + 1;
         }
         return lo;
     }
@@ -122,39 +140,62 @@ struct Segment {
     int c_first, n_parts;   // CTAs that hold a piece of this (b, g)
 };
 
-__device__ __forceinline__ bool next_segment(const Schedule& sc, const int32_t* seq_lens, int max_seq_len,
-                                             long long& pos, long long end, Segment& sg) {
-    if (pos >= end) return false;
-    const int b = sc.seq_of(pos);
-    const int n = sc.nst(b);
-    const long long base = (long long)sc.Hkv * sc.prefix[b];
-    const int g = (int)((pos - base) / n);
-    const long long sb = base + (long long)g * n;
-    sg.b = b; sg.g = g;
-    sg.s0 = (int)(pos - sb);
-    sg.s1 = (int)min((long long)n, end - sb);
-    sg.L = max(0, min(seq_lens[b], max_seq_len));
-    sg.c_first = sc.cta_of(sb);
-    sg.n_parts = sc.cta_of(sb + n - 1) - sg.c_first + 1;
-    pos = sb + sg.s1;
-    return true;
-}
+// Walks the segments of the range [pos, end).  Only the first step searches; later ones step to the next
+// KV head / sequence.  Division-heavy lookups happen only for the (at most two) segments that a range
+// boundary cuts.
+struct SegmentIter {
+    int pos, end, b, g;
+    bool started;
+    __device__ __forceinline__ void init(int lo, int hi) { pos = lo; end = hi; b = 0; g = 0; started = false; }
+    __device__ __forceinline__ bool next(const Schedule& sc, Segment& sg) {
+        if (pos >= end) return false;
+        int n;
+        if (!started) {
+            b = sc.seq_of(pos);
+            n = sc.nst(b);
+            g = (pos - sc.Hkv * sc.prefix[b]) / n;
+            started = true;
+        } else {
+            if (++g == sc.Hkv) {
+                g = 0;
+                do { ++b; } while (sc.nst(b) == 0);
+            }
+            n = sc.nst(b);
+        }
+        const int sb = sc.Hkv * sc.prefix[b] + g * n;
+        sg.b = b; sg.g = g;
+        sg.s0 = pos - sb;
+        sg.s1 = min(n, end - sb);
+        sg.L = sc.len[b];
+        if (sg.s0 == 0 && sg.s1 == n) {
+            sg.c_first = blockIdx.x;
+            sg.n_parts = 1;
+        } else {
+            sg.c_first = sc.cta_of(sb);
+            sg.n_parts = sc.cta_of(sb + n - 1) - sg.c_first + 1;
+        }
+        pos = sb + sg.s1;
+        return true;
+    }
+};
 
 __global__ void __launch_bounds__(DEC_THREADS, 1)
 decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[DEC_NSTAGES];
     __shared__ __align__(8) uint64_t empty_bar[DEC_NSTAGES];
-    __shared__ __align__(8) uint64_t merge_bar;
+    __shared__ __align__(8) uint64_t merge_bar, part_bar;
     __shared__ int s_prefix[DEC_MAX_SEQS + 1];
+    __shared__ int s_len[DEC_MAX_SEQS];
     __shared__ float mrg_m[DEC_CWARPS][DEC_G], mrg_l[DEC_CWARPS][DEC_G];
-    __shared__ float mrg_o[DEC_CWARPS][DEC_G][DEC_D + 4];
+    __shared__ __align__(16) float mrg_o[DEC_CWARPS][DEC_G][DEC_D + 2];   // read back as float2
     __shared__ __align__(16) __nv_bfloat16 s_q[DEC_G][DEC_D];   // rotated query heads of the current segment
     __shared__ float s_inv_freq[DEC_D / 2];
     __shared__ int s_abort;
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    DSTAMP(0);
 
     if (tid == 0) {
         for (int s = 0; s < DEC_NSTAGES; ++s) {
@@ -162,14 +203,15 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
             mbar_init(smem_u32(&empty_bar[s]), DEC_CWARPS);
         }
         mbar_init(smem_u32(&merge_bar), DEC_CWARPS);
+        mbar_init(smem_u32(&part_bar), DEC_CWARPS);
         s_abort = 0;
         fence_mbar_init();
         prefetch_tensormap(&tmap);
     }
-    if (tid < DEC_D / 2) s_inv_freq[tid] = rope_inv_freq(tid, DEC_D, p.theta);
     // stages per sequence, then an exclusive prefix sum (warp 0)
     for (int b = tid; b < p.B; b += DEC_THREADS) {
         const int L = max(0, min(p.seq_lens[b], p.max_seq_len));
+        s_len[b] = L;
         s_prefix[b + 1] = (L + DEC_STAGE_TOKENS - 1) / DEC_STAGE_TOKENS;
     }
     __syncthreads();
@@ -192,42 +234,121 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
 
     Schedule sc;
     sc.prefix = s_prefix;
+    sc.len = s_len;
     sc.Hkv = p.Hkv;
     sc.B = p.B;
-    sc.T = (long long)p.Hkv * s_prefix[p.B];
-    sc.G = (int)max(1LL, min((long long)gridDim.x, sc.T / p.min_stages));
+    sc.T = p.Hkv * s_prefix[p.B];
+    sc.G = max(1, min((int)gridDim.x, sc.T / p.min_stages));
+    DSTAMP(1);
+#if BN_DDBG
+    if (tid == 0 && p.lse) { unsigned smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid)); reinterpret_cast<unsigned long long*>(p.lse)[blockIdx.x * 8 + 6] = smid; }
+#endif
     const bool active = sc.T > 0 && (int)blockIdx.x < sc.G;
-    const long long range_lo = active ? sc.range_begin(blockIdx.x) : 0;
-    const long long range_hi = active ? sc.range_begin(blockIdx.x + 1) : 0;
+    const int range_lo = active ? sc.range_begin(blockIdx.x) : 0;
+    const int range_hi = active ? sc.range_begin(blockIdx.x + 1) : 0;
 
     if (warp == DEC_CWARPS) {
         // ------------------------------------------------------------ producer
+        // Page numbers are read a group of 4 stages (32 pages, one 128-byte line of the page table) at a
+        // time, one group ahead of their use and across segment boundaries, so that the TMA issue never
+        // waits on a page-table load.
+        constexpr int GRP = 32 / DEC_PAGES_PER_STAGE;   // stages per group
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        long long pos = range_lo;
-        Segment sg;
-        while (ok && next_segment(sc, p.seq_lens, p.max_seq_len, pos, range_hi, sg)) {
-            const int32_t* pt = p.page_table + (size_t)sg.b * p.max_pages;
+        SegmentIter iter;
+        iter.init(range_lo, range_hi);
+        Segment sg, sg_next;
+        bool have = iter.next(sc, sg);
+        auto load_group = [&](const Segment& sgm, int grp) {
+            const int e = grp * 32 + lane;
+            const int n_pages_seq = (sgm.L + BN_PAGE_TOKENS - 1) / BN_PAGE_TOKENS;
+            return e < n_pages_seq ? p.page_table[(size_t)sgm.b * p.max_pages + e] : -1;
+        };
+        int ids = have ? load_group(sg, sg.s0 / GRP) : -1, ids_pref = -1;
+        while (ok && have) {
+            const bool have_next = iter.next(sc, sg_next);
             const int n_pages_seq = (sg.L + BN_PAGE_TOKENS - 1) / BN_PAGE_TOKENS;
-            // page number of this lane's box, fetched one stage ahead of its use
-            auto load_page = [&](int s) {
-                const int pg = s * DEC_PAGES_PER_STAGE + lane;
-                return (lane < DEC_PAGES_PER_STAGE && pg < n_pages_seq) ? pt[pg] : -1;
-            };
-            int page_next = load_page(sg.s0);
             for (int s = sg.s0; s < sg.s1; ++s) {
-                const int page = page_next;
-                if (s + 1 < sg.s1) page_next = load_page(s + 1);
+                if (s == sg.s0 || s % GRP == 0) {
+                    if (s != sg.s0) ids = ids_pref;
+                    const int grp = s / GRP;
+                    if ((grp + 1) * GRP < sg.s1) ids_pref = load_group(sg, grp + 1);
+                    else if (have_next) ids_pref = load_group(sg_next, sg_next.s0 / GRP);
+                }
+                const int page = __shfl_sync(0xffffffffu, ids, (s % GRP) * DEC_PAGES_PER_STAGE + (lane % DEC_PAGES_PER_STAGE));
                 if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, &s_abort)) { ok = false; break; }
                 const int npages = min(DEC_PAGES_PER_STAGE, n_pages_seq - s * DEC_PAGES_PER_STAGE);
                 const uint32_t fb = smem_u32(&full_bar[stage]);
                 if (lane == 0) mbar_arrive_expect_tx(fb, (uint32_t)npages * DEC_BOX_BYTES);
                 __syncwarp();
-                if (page >= 0)
+                if (lane < npages && page >= 0)
                     tma_load_2d(ring + stage * DEC_STAGE_BYTES + lane * DEC_BOX_BYTES, &tmap, 0,
                                 (page * p.Hkv + sg.g) * DEC_BOX_ROWS, fb);
                 if (++stage == DEC_NSTAGES) { stage = 0; phase ^= 1u; }
+            }
+            sg = sg_next;
+            ids = ids_pref;
+            have = have_next;
+        }
+        if (lane == 0 && s_abort) atomicExch(&p.hdr->error, BN_ERR_TIMEOUT);
+        return;
+    }
+
+    if (warp == DEC_CWARPS + 1) {
+        // -------------------------------------------------------- combine warp
+        // For every segment of this CTA that is only a part of its (sequence, head): wait until the consumers
+        // have stored the partial, take a ticket, and in the CTA that holds the last ticket merge all parts.
+        SegmentIter iter;
+        iter.init(range_lo, range_hi);
+        Segment sg;
+        uint32_t pphase = 0;
+        while (iter.next(sc, sg)) {
+            if (sg.n_parts == 1) continue;
+            if (!mbar_wait(smem_u32(&part_bar), pphase, &s_abort)) break;
+            pphase ^= 1u;
+            __threadfence();     // the consumers' stores, observed through the barrier, before the ticket
+            const int bgi = sg.b * p.Hkv + sg.g;
+            int ticket = 0;
+            if (lane == 0) ticket = atomicAdd(&p.tickets[bgi], 1);
+            ticket = __shfl_sync(0xffffffffu, ticket, 0);
+            if (ticket != sg.n_parts - 1) continue;
+            __threadfence();
+            const size_t base = (size_t)bgi * p.max_parts;
+            // lane -> head lane / 4, dims 16 * (lane % 4) .. + 15
+            const int ch = lane / 4, cd = (lane % 4) * 16;
+            float m2 = -INFINITY;
+            for (int c = 0; c < sg.n_parts; ++c) m2 = fmaxf(m2, __ldcg(p.part_m + (base + c) * DEC_G + ch));
+            const float ms2 = m2 == -INFINITY ? 0.f : m2;
+            float l2 = 0.f, a2[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) a2[i] = 0.f;
+            for (int c = 0; c < sg.n_parts; ++c) {
+                const float scl = ex2(__ldcg(p.part_m + (base + c) * DEC_G + ch) - ms2);
+                l2 += __ldcg(p.part_l + (base + c) * DEC_G + ch) * scl;
+                const float4* po = reinterpret_cast<const float4*>(p.part_o + ((base + c) * DEC_G + ch) * DEC_D + cd);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float4 v4 = __ldcg(po + i);
+                    a2[4 * i] += v4.x * scl; a2[4 * i + 1] += v4.y * scl;
+                    a2[4 * i + 2] += v4.z * scl; a2[4 * i + 3] += v4.w * scl;
+                }
+            }
+            if (lane == 0) p.tickets[bgi] = 0;   // leave the scratch clean for the next launch
+            if (ch < p.n_rep) {
+                const float inv = l2 > 0.f ? 1.f / l2 : 0.f;
+                const size_t crow = (size_t)sg.b * p.Hq + (size_t)sg.g * p.n_rep + ch;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float r0 = a2[4 * i] * inv, r1 = a2[4 * i + 1] * inv, r2 = a2[4 * i + 2] * inv,
+                                r3 = a2[4 * i + 3] * inv;
+                    if (p.out)
+                        *reinterpret_cast<uint2*>(p.out + crow * DEC_D + cd + 4 * i) =
+                            make_uint2(pack_bf16(r0, r1), pack_bf16(r2, r3));
+                    if (p.out_f32)
+                        *reinterpret_cast<float4*>(p.out_f32 + crow * DEC_D + cd + 4 * i) = make_float4(r0, r1, r2, r3);
+                }
+                if (!BN_DDBG && p.lse && lane % 4 == 0) p.lse[crow] = l2 > 0.f ? (m2 + log2f(l2)) * LN2 : -INFINITY;
             }
         }
         if (lane == 0 && s_abort) atomicExch(&p.hdr->error, BN_ERR_TIMEOUT);
@@ -239,12 +360,12 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
     for (int bgi = blockIdx.x; bgi < p.B * p.Hkv; bgi += gridDim.x) {
         const int b = bgi / p.Hkv, g = bgi % p.Hkv;
         if (sc.nst(b) > 0) continue;
-        const int th = tid / 16, td = (tid % 16) * 4;
+        const int th = tid / DEC_TPH, td = (tid % DEC_TPH) * DEC_DPT;
         if (th >= p.n_rep) continue;
         const size_t row = (size_t)b * p.Hq + (size_t)g * p.n_rep + th;
-        if (p.out) *reinterpret_cast<uint2*>(p.out + row * DEC_D + td) = make_uint2(0u, 0u);
-        if (p.out_f32) *reinterpret_cast<float4*>(p.out_f32 + row * DEC_D + td) = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (p.lse && tid % 16 == 0) p.lse[row] = -INFINITY;
+        if (p.out) *reinterpret_cast<uint32_t*>(p.out + row * DEC_D + td) = 0u;
+        if (p.out_f32) *reinterpret_cast<float2*>(p.out_f32 + row * DEC_D + td) = make_float2(0.f, 0.f);
+        if (!BN_DDBG && p.lse && tid % DEC_TPH == 0) p.lse[row] = -INFINITY;
     }
 
     int stage = 0;
@@ -258,43 +379,52 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
         mphase ^= 1u;
         return ok;
     };
-    // raw query pair of thread (head tid / 16, dims 4 * (tid % 16) .. + 3) for a segment
-    auto load_q_raw = [&](const Segment& sg) -> uint2 {
-        const int th = tid / 16, td = (tid % 16) * 4;
-        if (th >= p.n_rep) return make_uint2(0u, 0u);
-        return *reinterpret_cast<const uint2*>(p.q + ((size_t)sg.b * p.Hq + (size_t)sg.g * p.n_rep + th) * DEC_D + td);
+    // raw query pair of thread (head tid / 32, dims 2 * (tid % 32), + 1) for a segment
+    auto load_q_raw = [&](const Segment& sg) -> uint32_t {
+        const int th = tid / DEC_TPH, td = (tid % DEC_TPH) * DEC_DPT;
+        if (th >= p.n_rep) return 0u;
+        return *reinterpret_cast<const uint32_t*>(p.q + ((size_t)sg.b * p.Hq + (size_t)sg.g * p.n_rep + th) * DEC_D + td);
     };
 
-    long long pos = range_lo;
-    Segment sg, sg_next;
-    bool have = next_segment(sc, p.seq_lens, p.max_seq_len, pos, range_hi, sg);
-    uint2 q_raw = have ? load_q_raw(sg) : make_uint2(0u, 0u);
-    bool ok = true;
-    while (ok && have) {
-        // look one segment ahead so that its query is already on the way
-        const bool have_next = next_segment(sc, p.seq_lens, p.max_seq_len, pos, range_hi, sg_next);
-        const uint2 q_raw_next = have_next ? load_q_raw(sg_next) : make_uint2(0u, 0u);
-
-        // rotate the 8 query heads of this segment (two pairs per thread) into shared memory
-        {
-            const int th = tid / 16, td = (tid % 16) * 4;
-            const int qpos = p.q_positions ? p.q_positions[sg.b] : sg.L - 1;
-            uint32_t w[2] = {q_raw.x, q_raw.y};
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                float x0 = bf16_lo(w[e]), x1 = bf16_hi(w[e]);
-                if (p.rope_q) {
-                    const float angle = qpos * s_inv_freq[td / 2 + e];
-                    const float cos_angle = cosf(angle), sin_angle = sinf(angle);
-                    const float y0 = x0 * cos_angle - x1 * sin_angle;
-                    const float y1 = x0 * sin_angle + x1 * cos_angle;
-                    x0 = y0; x1 = y1;
-                }
-                w[e] = pack_bf16(x0, x1);
-            }
-            *reinterpret_cast<uint2*>(&s_q[th][td]) = make_uint2(w[0], w[1]);
+    // rotate the 8 query heads of a segment (one pair per thread) into shared memory
+    auto store_q = [&](const Segment& sgq, uint32_t raw) {
+        const int th = tid / DEC_TPH, td = (tid % DEC_TPH) * DEC_DPT;
+        const int qpos = p.q_positions ? p.q_positions[sgq.b] : sgq.L - 1;
+        float x0 = bf16_lo(raw), x1 = bf16_hi(raw);
+        if (p.rope_q) {
+            const float angle = qpos * s_inv_freq[td / 2];
+            float sin_angle, cos_angle;
+            sincosf(angle, &sin_angle, &cos_angle);
+            const float y0 = x0 * cos_angle - x1 * sin_angle;
+            const float y1 = x0 * sin_angle + x1 * cos_angle;
+            x0 = y0; x1 = y1;
         }
-        if (!group_sync()) break;
+        *reinterpret_cast<uint32_t*>(&s_q[th][td]) = pack_bf16(x0, x1);
+    };
+
+#if BN_DDBG
+    int fidx = 0;
+#endif
+    SegmentIter iter;
+    iter.init(range_lo, range_hi);
+    Segment sg, sg_next;
+    bool have = iter.next(sc, sg);
+    uint32_t q_raw = have ? load_q_raw(sg) : 0u;
+    bool ok = true;
+    // the RoPE frequencies are needed by the consumers only; computing them here keeps them off the path to
+    // the first TMA load
+    if (tid < DEC_D / 2) s_inv_freq[tid] = rope_inv_freq(tid, DEC_D, p.theta);
+    ok = group_sync();
+    if (ok && have) {
+        store_q(sg, q_raw);
+        ok = group_sync();
+    }
+    while (ok && have) {
+        FSTAMP(1);
+        // look one segment ahead so that its query is already on the way
+        const bool have_next = iter.next(sc, sg_next);
+        const uint32_t q_raw_next = have_next ? load_q_raw(sg_next) : 0u;
+        FSTAMP(2);
         // Q^T fragments (k = dims, n = heads)
         uint32_t qb[4][2];
 #pragma unroll
@@ -311,14 +441,19 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
             for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
 
         for (int s = sg.s0; s < sg.s1; ++s) {
+            FSTAMP(10);
             if (!mbar_wait(smem_u32(&full_bar[stage]), phase, &s_abort)) { ok = false; break; }
+            FSTAMP(11);
+#if BN_DDBG
+            if (tid == 0 && p.lse && reinterpret_cast<unsigned long long*>(p.lse)[blockIdx.x * 8 + 2] == 0) DSTAMP(2);
+#endif
             const int ntok = min(DEC_STAGE_TOKENS, sg.L - s * DEC_STAGE_TOKENS);
             const uint32_t sbase = ring + stage * DEC_STAGE_BYTES;
-            float sv[2][4];
-            int nv[2];
+            float sv[DEC_PPW][4];
+            int nv[DEC_PPW];
 #pragma unroll
-            for (int pi = 0; pi < 2; ++pi) {
-                const int pg = warp * 2 + pi;
+            for (int pi = 0; pi < DEC_PPW; ++pi) {
+                const int pg = warp * DEC_PPW + pi;
                 nv[pi] = max(0, min(BN_PAGE_TOKENS, ntok - pg * BN_PAGE_TOKENS));
                 const uint32_t box = sbase + pg * DEC_BOX_BYTES;
 #pragma unroll
@@ -344,7 +479,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
             // online softmax, base 2; thread owns heads hA, hA+1 and tokens lane/4 (+8) of each page
             float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-            for (int pi = 0; pi < 2; ++pi)
+            for (int pi = 0; pi < DEC_PPW; ++pi)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int tok = lane / 4 + (j >> 1) * 8;
@@ -362,14 +497,16 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
             for (int hh = 0; hh < 2; ++hh) {
                 const float m_new = fmaxf(m_run[hh], tmax[hh]);
                 msafe[hh] = m_new == -INFINITY ? 0.f : m_new;
-                const float alpha = ex2(m_run[hh] - msafe[hh]);
-                m_run[hh] = m_new;
-                l_run[hh] *= alpha;
+                if (m_new != m_run[hh]) {     // the running maximum moves rarely after the first stages
+                    const float alpha = ex2(m_run[hh] - msafe[hh]);
+                    m_run[hh] = m_new;
+                    l_run[hh] *= alpha;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) { o[i][hh] *= alpha; o[i][hh + 2] *= alpha; }
+                    for (int i = 0; i < 4; ++i) { o[i][hh] *= alpha; o[i][hh + 2] *= alpha; }
+                }
             }
 #pragma unroll
-            for (int pi = 0; pi < 2; ++pi) {
+            for (int pi = 0; pi < DEC_PPW; ++pi) {
                 if (nv[pi] == 0) continue;
                 float pr[4];
 #pragma unroll
@@ -379,7 +516,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
                 }
                 const uint32_t b0 = movmatrix_trans(pack_bf16(pr[0], pr[1]));
                 const uint32_t b1 = movmatrix_trans(pack_bf16(pr[2], pr[3]));
-                const uint32_t vbox = sbase + (warp * 2 + pi) * DEC_BOX_BYTES + BN_PAGE_TOKENS * 128;
+                const uint32_t vbox = sbase + (warp * DEC_PPW + pi) * DEC_BOX_BYTES + BN_PAGE_TOKENS * 128;
 #pragma unroll
                 for (int mtile = 0; mtile < 4; ++mtile) {
                     const int mat = lane / 8, tok = (lane % 8) + (mat >> 1) * 8, chunk16 = mtile * 2 + (mat & 1);
@@ -393,6 +530,8 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
             if (++stage == DEC_NSTAGES) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
+        DSTAMP(3);
+        FSTAMP(3);
 
         // ------------------------------------------------ merge the 4 warps
 #pragma unroll
@@ -413,94 +552,58 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
             mrg_o[warp][hA][d + 8] = o[i][2];
             mrg_o[warp][hA + 1][d + 8] = o[i][3];
         }
+        FSTAMP(4);
         if (!group_sync()) break;
-        // thread -> head th, dims td..td+3
-        const int th = tid / 16, td = (tid % 16) * 4;
+        FSTAMP(5);
+        // thread -> head th, dims td, td + 1
+        const int th = tid / DEC_TPH, td = (tid % DEC_TPH) * DEC_DPT;
         float mstar = -INFINITY;
 #pragma unroll
         for (int w = 0; w < DEC_CWARPS; ++w) mstar = fmaxf(mstar, mrg_m[w][th]);
         const float ms = mstar == -INFINITY ? 0.f : mstar;
-        float lsum = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+        float lsum = 0.f, acc[2] = {0.f, 0.f};
 #pragma unroll
         for (int w = 0; w < DEC_CWARPS; ++w) {
             const float scl = ex2(mrg_m[w][th] - ms);
             lsum += mrg_l[w][th] * scl;
-            const float4 po = *reinterpret_cast<const float4*>(&mrg_o[w][th][td]);
-            acc[0] += po.x * scl; acc[1] += po.y * scl; acc[2] += po.z * scl; acc[3] += po.w * scl;
+            const float2 po = *reinterpret_cast<const float2*>(&mrg_o[w][th][td]);
+            acc[0] += po.x * scl; acc[1] += po.y * scl;
         }
         const int bgi = sg.b * p.Hkv + sg.g;
         const size_t row = (size_t)sg.b * p.Hq + (size_t)sg.g * p.n_rep + th;
-        auto write_final = [&](float m_, float l_, const float (&a)[4]) {
+        auto write_final = [&](float m_, float l_, const float (&a)[2]) {
             if (th >= p.n_rep) return;
             const float inv = l_ > 0.f ? 1.f / l_ : 0.f;
-            const float r0 = a[0] * inv, r1 = a[1] * inv, r2 = a[2] * inv, r3 = a[3] * inv;
-            if (p.out) *reinterpret_cast<uint2*>(p.out + row * DEC_D + td) = make_uint2(pack_bf16(r0, r1), pack_bf16(r2, r3));
-            if (p.out_f32) *reinterpret_cast<float4*>(p.out_f32 + row * DEC_D + td) = make_float4(r0, r1, r2, r3);
-            if (p.lse && tid % 16 == 0) p.lse[row] = l_ > 0.f ? (m_ + log2f(l_)) * LN2 : -INFINITY;
+            const float r0 = a[0] * inv, r1 = a[1] * inv;
+            if (p.out) *reinterpret_cast<uint32_t*>(p.out + row * DEC_D + td) = pack_bf16(r0, r1);
+            if (p.out_f32) *reinterpret_cast<float2*>(p.out_f32 + row * DEC_D + td) = make_float2(r0, r1);
+            if (!BN_DDBG && p.lse && tid % DEC_TPH == 0) p.lse[row] = l_ > 0.f ? (m_ + log2f(l_)) * LN2 : -INFINITY;
         };
         if (sg.n_parts == 1) {
             write_final(mstar, lsum, acc);
-            if (!group_sync()) break;          // mrg_* and s_q are reused by the next segment
         } else {
             const size_t slot = (size_t)bgi * p.max_parts + ((int)blockIdx.x - sg.c_first);
-            if (tid % 16 == 0) {
+            if (tid % DEC_TPH == 0) {
                 p.part_m[slot * DEC_G + th] = mstar;
                 p.part_l[slot * DEC_G + th] = lsum;
             }
-            *reinterpret_cast<float4*>(p.part_o + (slot * DEC_G + th) * DEC_D + td) =
-                make_float4(acc[0], acc[1], acc[2], acc[3]);
-            __threadfence();
-            if (!group_sync()) break;
-            // warp 0 alone takes the ticket and, if it holds the last one, combines; the others go on
-            if (warp == 0) {
-                int ticket = 0;
-                if (lane == 0) ticket = atomicAdd(&p.tickets[bgi], 1);
-                ticket = __shfl_sync(0xffffffffu, ticket, 0);
-                if (ticket == sg.n_parts - 1) {
-                    __threadfence();
-                    const size_t base = (size_t)bgi * p.max_parts;
-                    // lane -> head lane / 4, dims 16 * (lane % 4) .. + 15
-                    const int ch = lane / 4, cd = (lane % 4) * 16;
-                    float m2 = -INFINITY;
-                    for (int c = 0; c < sg.n_parts; ++c) m2 = fmaxf(m2, __ldcg(p.part_m + (base + c) * DEC_G + ch));
-                    const float ms2 = m2 == -INFINITY ? 0.f : m2;
-                    float l2 = 0.f, a2[16];
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) a2[i] = 0.f;
-                    for (int c = 0; c < sg.n_parts; ++c) {
-                        const float scl = ex2(__ldcg(p.part_m + (base + c) * DEC_G + ch) - ms2);
-                        l2 += __ldcg(p.part_l + (base + c) * DEC_G + ch) * scl;
-                        const float4* po = reinterpret_cast<const float4*>(p.part_o + ((base + c) * DEC_G + ch) * DEC_D + cd);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const float4 v4 = __ldcg(po + i);
-                            a2[4 * i] += v4.x * scl; a2[4 * i + 1] += v4.y * scl;
-                            a2[4 * i + 2] += v4.z * scl; a2[4 * i + 3] += v4.w * scl;
-                        }
-                    }
-                    if (lane == 0) p.tickets[bgi] = 0;   // leave the scratch clean for the next launch
-                    if (ch < p.n_rep) {
-                        const float inv = l2 > 0.f ? 1.f / l2 : 0.f;
-                        const size_t crow = (size_t)sg.b * p.Hq + (size_t)sg.g * p.n_rep + ch;
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const float r0 = a2[4 * i] * inv, r1 = a2[4 * i + 1] * inv, r2 = a2[4 * i + 2] * inv,
-                                        r3 = a2[4 * i + 3] * inv;
-                            if (p.out)
-                                *reinterpret_cast<uint2*>(p.out + crow * DEC_D + cd + 4 * i) =
-                                    make_uint2(pack_bf16(r0, r1), pack_bf16(r2, r3));
-                            if (p.out_f32)
-                                *reinterpret_cast<float4*>(p.out_f32 + crow * DEC_D + cd + 4 * i) = make_float4(r0, r1, r2, r3);
-                        }
-                        if (p.lse && lane % 4 == 0) p.lse[crow] = l2 > 0.f ? (m2 + log2f(l2)) * LN2 : -INFINITY;
-                    }
-                }
-            }
+            *reinterpret_cast<float2*>(p.part_o + (slot * DEC_G + th) * DEC_D + td) = make_float2(acc[0], acc[1]);
+            // hand the partial to the combine warp and go on
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&part_bar));
         }
+        // the next segment's query replaces this one's (every warp took its fragments long ago)
+        FSTAMP(6);
+        if (have_next) store_q(sg_next, q_raw_next);
+        FSTAMP(7);
+        if (!group_sync()) break;              // mrg_* free again, s_q visible
+        FSTAMP(8);
+        DSTAMP(4);
         sg = sg_next;
         q_raw = q_raw_next;
         have = have_next;
     }
+    DSTAMP(5);
     if (s_abort && lane == 0) atomicExch(&p.hdr->error, BN_ERR_TIMEOUT);
 }
 
@@ -537,15 +640,15 @@ using namespace bn;
 extern "C" size_t bn_attn_decode_workspace_bytes(int B, int Hq, int Hkv, int D, int max_seq_len, int chunk_tokens) {
     (void)Hq;
     if (B <= 0 || Hkv <= 0 || D != DEC_D || max_seq_len < 0) return 0;
-    if (chunk_tokens < 0 || chunk_tokens % DEC_STAGE_TOKENS) return 0;
+    if (chunk_tokens < 0 || chunk_tokens % 128) return 0;
     return decode_layout(B, Hkv, max_seq_len, pick_min_tokens(chunk_tokens)).total;
 }
 
-extern "C" int bn_attn_decode_paged(const void* q, const void* pool, int64_t pool_pages, const int32_t* page_table,
-                                    int max_pages, const int32_t* seq_lens, const int32_t* q_positions, void* out,
-                                    float* out_f32, float* lse, int B, int Hq, int Hkv, int D, float scale,
-                                    float theta, int rope_q, int max_seq_len, int chunk_tokens, void* workspace,
-                                    size_t workspace_bytes, bn_stream_t stream) {
+static int decode_launch(const void* q, const void* pool, int64_t pool_pages, const int32_t* page_table,
+                         int max_pages, const int32_t* seq_lens, const int32_t* q_positions, void* out,
+                         float* out_f32, float* lse, int B, int Hq, int Hkv, int D, float scale, float theta,
+                         int rope_q, int max_seq_len, int chunk_tokens, void* workspace, size_t workspace_bytes,
+                         bn_stream_t stream) {
     if (!q || !pool || !page_table || !seq_lens) return fail(BN_ERR_INVALID_ARG, "bn_attn_decode_paged: null pointer");
     if (!out && !out_f32) return fail(BN_ERR_INVALID_ARG, "bn_attn_decode_paged: no output buffer");
     if (B < 0 || Hq <= 0 || Hkv <= 0 || max_pages < 0 || max_seq_len < 0 || pool_pages <= 0)
@@ -557,12 +660,14 @@ extern "C" int bn_attn_decode_paged(const void* q, const void* pool, int64_t poo
     if (B > DEC_MAX_SEQS)
         return fail(BN_ERR_UNSUPPORTED, "bn_attn_decode_paged: %d sequences in one launch (<= %d supported)", B,
                     DEC_MAX_SEQS);
-    if (chunk_tokens < 0 || chunk_tokens % DEC_STAGE_TOKENS)
-        return fail(BN_ERR_INVALID_ARG, "bn_attn_decode_paged: chunk_tokens=%d must be 0 or a multiple of %d",
-                    chunk_tokens, DEC_STAGE_TOKENS);
+    if (chunk_tokens < 0 || chunk_tokens % 128)
+        return fail(BN_ERR_INVALID_ARG, "bn_attn_decode_paged: chunk_tokens=%d must be 0 or a multiple of 128",
+                    chunk_tokens);
     if ((int64_t)max_pages * BN_PAGE_TOKENS < max_seq_len)
         return fail(BN_ERR_INVALID_ARG, "bn_attn_decode_paged: max_pages=%d cannot hold max_seq_len=%d", max_pages,
                     max_seq_len);
+    if ((long long)B * Hkv * ((max_seq_len + DEC_STAGE_TOKENS - 1) / DEC_STAGE_TOKENS) > 0x3fffffffLL)
+        return fail(BN_ERR_UNSUPPORTED, "bn_attn_decode_paged: B * Hkv * max_seq_len is too large for one launch");
     if (pool_pages * Hkv * DEC_BOX_ROWS > 0x7fffffffLL)
         return fail(BN_ERR_UNSUPPORTED, "bn_attn_decode_paged: pool of %lld pages is too large", (long long)pool_pages);
     if ((reinterpret_cast<uintptr_t>(q) & 7) || (out && (reinterpret_cast<uintptr_t>(out) & 7)) ||
@@ -622,6 +727,15 @@ extern "C" int bn_attn_decode_paged(const void* q, const void* pool, int64_t poo
     const int grid = (int)(max_ranges < sms ? (max_ranges > 0 ? max_ranges : 1) : sms);
     decode_paged_kernel<<<grid, DEC_THREADS, DEC_SMEM_BYTES, as_stream(stream)>>>(tmap, p);
     return launch_status("bn_attn_decode_paged");
+}
+
+extern "C" int bn_attn_decode_paged(const void* q, const void* pool, int64_t pool_pages, const int32_t* page_table,
+                                    int max_pages, const int32_t* seq_lens, const int32_t* q_positions, void* out,
+                                    float* out_f32, float* lse, int B, int Hq, int Hkv, int D, float scale,
+                                    float theta, int rope_q, int max_seq_len, int chunk_tokens, void* workspace,
+                                    size_t workspace_bytes, bn_stream_t stream) {
+    return decode_launch(q, pool, pool_pages, page_table, max_pages, seq_lens, q_positions, out, out_f32, lse, B, Hq,
+                         Hkv, D, scale, theta, rope_q, max_seq_len, chunk_tokens, workspace, workspace_bytes, stream);
 }
 
 extern "C" int bn_attn_lse_combine(const float* outs, const float* lses, int P, int64_t n, int D, float* out_f32,

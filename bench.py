@@ -285,6 +285,52 @@ def measure_decode(torch, args, rank, world, dist, reduce_max, pk):
     }
 
 
+def measure_longctx(torch, args, rank, world, dist, reduce_max, pk):
+    """BASELINE config 4: batch 4, one 262144-token sequence each, 32q/4kv heads.  The sequence is cut into
+    contiguous page-aligned token ranges, one per GPU; each GPU decodes over its range (normalised partial
+    output + log-sum-exp), the partials are exchanged with ONE all-gather and merged locally."""
+    import numpy as np
+    from baranet_bdml_b200 import dist as bdist
+    from baranet_bdml_b200.kv_cache import PagedKVCache
+    B, L, Hq, Hkv, D = 4, 262144, 32, 4, 64
+    t0, t1 = bdist.sequence_split_ranges(L, world)[rank]
+    Lloc = t1 - t0
+    n_pages = B * (Lloc // 16)
+    cache = PagedKVCache(n_pages, B, Lloc // 16, Hkv, D)
+    cache.pool.copy_(torch.randn(cache.pool.shape, device="cuda", dtype=torch.float32).to(torch.bfloat16))
+    rng = np.random.default_rng(5 + rank)
+    cache.page_table.copy_(torch.from_numpy(rng.permutation(n_pages).astype(np.int32).reshape(B, Lloc // 16)))
+    cache.seq_lens.fill_(Lloc)
+    q = torch.randn((B, Hq, D), device="cuda").to(torch.bfloat16)
+    qpos = torch.full((B,), L - 1, dtype=torch.int32, device="cuda")
+    o32 = torch.empty((B, Hq, D), dtype=torch.float32, device="cuda")
+    lse = torch.empty((B, Hq), dtype=torch.float32, device="cuda")
+
+    def step(i):
+        cache.decode(q, num_heads=Hq, out_f32=o32, lse=lse, q_positions=qpos, max_seq_len=Lloc)
+        if world > 1:
+            bdist.combine_partials(o32.view(B * Hq, D), lse.view(B * Hq))
+
+    steps = max(args.steps // 4, 8)
+    ms = reduce_max(time_loop(torch, step, steps, 3, dist))
+    cache._ws.status()
+    bytes_alg = B * L * Hkv * D * 2 * 2           # the whole job, all ranks
+    gbs = bytes_alg / (ms * 1e-3) / 1e9
+    return {
+        "metric": "long_context_decode_hbm_gbs", "value": gbs, "unit": "GB/s", "ms_per_step": ms, "steps": steps,
+        "n_gpus": world, "scaling": "strong",
+        "config": {"workload": "split-KV decode, BASELINE config 4: batch 4, KV length 262144 bf16 (1 GiB of cache in "
+                               "total), 32q/4kv heads, sequence split across the GPUs, partials merged by one "
+                               "all-gather + log-sum-exp combine",
+                   "algorithmic_bytes_per_step": bytes_alg, "tokens_per_gpu": Lloc,
+                   "l2": "cache per GPU is %d MiB" % (B * Lloc * Hkv * D * 4 >> 20)},
+        "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": pk["hbm"], "unit": "GB/s",
+                     "frac": gbs / world / pk["hbm"], "traffic": None, "peak_source": pk["source"],
+                     "kernel": "decode_paged_kernel", "note": "per GPU; includes the exchange when n_gpus > 1"},
+        "gpu_launches": steps * (1 if world == 1 else 2),
+    }
+
+
 def run_ours(args):
     import torch
     from baranet_bdml_b200 import ops, _lib
@@ -319,6 +365,10 @@ def run_ours(args):
                 result["decode"] = measure_decode(torch, args, rank, world, dist, reduce_max, pk)
             except Exception as e:  # the headline must still print
                 result["decode"] = {"error": repr(e)}
+            try:
+                result["decode_long"] = measure_longctx(torch, args, rank, world, dist, reduce_max, pk)
+            except Exception as e:
+                result["decode_long"] = {"error": repr(e)}
     if rank == 0:
         result["clocks"] = sampler.stop()
         if world == 1 and not args.no_cpu_baseline and not args.decode_only:

@@ -148,7 +148,8 @@ BN_API int bn_kv_append(void* pool, int64_t pool_pages, const int32_t* page_tabl
                  const int32_t* positions, int T, const void* k_new, const void* v_new, int64_t kv_row_stride,
                  int dtype, int Hkv, int D, float theta, bn_stream_t stream);
 
-/* Bytes of scratch bn_attn_decode_paged needs (split-KV partials + tickets).
+/* Bytes of scratch bn_attn_decode_paged needs (partial results of sequences
+ * that span several SMs + tickets), for the same chunk_tokens.
  * The scratch must be zero-filled once before its first use; the kernel leaves
  * it clean for the next call. */
 BN_API size_t bn_attn_decode_workspace_bytes(int B, int Hq, int Hkv, int D, int max_seq_len, int chunk_tokens);
@@ -159,9 +160,13 @@ BN_API size_t bn_attn_decode_workspace_bytes(int B, int Hq, int Hkv, int D, int 
  *   q_positions[b] (NULL: seq_lens[b]-1).
  *   out (B, Hq, D) bf16 (may be NULL); out_f32 (B, Hq, D) fp32 (may be NULL);
  *   lse (B, Hq) fp32 natural log (may be NULL; -inf for an empty sequence).
- * The sequence is cut into chunks of chunk_tokens (0 = pick; else a multiple
- * of 128) that run in parallel; partials are merged by a log-sum-exp combine
- * inside the same launch.  max_seq_len bounds seq_lens (sizes the chunk grid). */
+ * All cached tokens of the launch are cut into equal contiguous ranges, one per
+ * SM, whatever the individual lengths; a (sequence, KV head) that falls into
+ * several ranges is merged by a log-sum-exp combine inside the same launch.
+ * chunk_tokens (0 = default 1024; else a multiple of 128) is the shortest range
+ * an SM is given (fewer SMs take part when there is less work than that);
+ * max_seq_len bounds seq_lens and sizes the scratch.  At most 1024 sequences
+ * per launch. */
 BN_API int bn_attn_decode_paged(const void* q, const void* pool, int64_t pool_pages, const int32_t* page_table,
                          int max_pages, const int32_t* seq_lens, const int32_t* q_positions, void* out,
                          float* out_f32, float* lse, int B, int Hq, int Hkv, int D, float scale, float theta,
