@@ -738,6 +738,55 @@ extern "C" int bn_attn_decode_paged(const void* q, const void* pool, int64_t poo
                          Hkv, D, scale, theta, rope_q, max_seq_len, chunk_tokens, workspace, workspace_bytes, stream);
 }
 
+// ---------------------------------------------------------------------------
+// Decode without a caller-supplied scratch buffer
+// ---------------------------------------------------------------------------
+// Scratch of the split-KV combine for callers that cannot allocate device memory.  The array lives in the
+// library's device image: every GPU that loads the library holds these bytes until the process exits.
+constexpr int DEC_STATIC_MAX_BG = 256;        // sequences x KV heads
+constexpr int DEC_STATIC_MAX_SEQ_LEN = 4096;  // tokens per sequence
+constexpr size_t DEC_STATIC_BYTES =
+    256 + 1024 +                                                             // header + tickets
+    2 * (size_t)DEC_STATIC_MAX_BG * (DEC_STATIC_MAX_SEQ_LEN / DEC_DEFAULT_MIN_TOKENS + 2) * DEC_G * sizeof(float) +
+    (size_t)DEC_STATIC_MAX_BG * (DEC_STATIC_MAX_SEQ_LEN / DEC_DEFAULT_MIN_TOKENS + 2) * DEC_G * DEC_D * sizeof(float);
+static __device__ __align__(256) unsigned char g_decode_static_scratch[DEC_STATIC_BYTES];
+
+extern "C" int bn_attn_decode_paged_static(const void* q, const void* pool, int64_t pool_pages,
+                                           const int32_t* page_table, int max_pages, const int32_t* seq_lens,
+                                           const int32_t* q_positions, void* out, float* out_f32, float* lse, int B,
+                                           int Hq, int Hkv, int D, float scale, float theta, int rope_q,
+                                           int max_seq_len, bn_stream_t stream) {
+    if (B < 0 || Hkv <= 0 || max_seq_len < 0)
+        return fail(BN_ERR_INVALID_ARG, "bn_attn_decode_paged_static: bad sizes B=%d Hkv=%d max_seq_len=%d", B, Hkv,
+                    max_seq_len);
+    if ((long long)B * Hkv > DEC_STATIC_MAX_BG || max_seq_len > DEC_STATIC_MAX_SEQ_LEN)
+        return fail(BN_ERR_UNSUPPORTED,
+                    "bn_attn_decode_paged_static: B*Hkv=%lld, max_seq_len=%d exceed the built-in scratch (B*Hkv <= %d, "
+                    "max_seq_len <= %d); use bn_attn_decode_paged with a caller-owned buffer",
+                    (long long)B * Hkv, max_seq_len, DEC_STATIC_MAX_BG, DEC_STATIC_MAX_SEQ_LEN);
+    if (int rc = require_sm100()) return rc;
+    // Per device, once: the array's name is only a host-side handle, so ask the runtime for the device address
+    // (with that device current) and clear the words that must start at zero.
+    constexpr int kMaxDevices = 64;
+    static void* s_scratch[kMaxDevices] = {};
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+        return fail(BN_ERR_CUDA, "bn_attn_decode_paged_static: cudaGetDevice: %s", cudaGetErrorString(e));
+    void* scratch = s_scratch[dev];
+    if (!scratch) {
+        e = cudaGetSymbolAddress(&scratch, g_decode_static_scratch);
+        if (e != cudaSuccess || !scratch)
+            return fail(BN_ERR_CUDA, "bn_attn_decode_paged_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        e = cudaMemsetAsync(scratch, 0, 256 + 1024, as_stream(stream));
+        if (e != cudaSuccess)
+            return fail(BN_ERR_CUDA, "bn_attn_decode_paged_static: cudaMemsetAsync: %s", cudaGetErrorString(e));
+        s_scratch[dev] = scratch;
+    }
+    return decode_launch(q, pool, pool_pages, page_table, max_pages, seq_lens, q_positions, out, out_f32, lse, B, Hq,
+                         Hkv, D, scale, theta, rope_q, max_seq_len, 0, scratch, DEC_STATIC_BYTES, stream);
+}
+
 extern "C" int bn_attn_lse_combine(const float* outs, const float* lses, int P, int64_t n, int D, float* out_f32,
                                    void* out_bf16, float* lse, bn_stream_t stream) {
     if (!outs || !lses || (!out_f32 && !out_bf16)) return fail(BN_ERR_INVALID_ARG, "bn_attn_lse_combine: null pointer");

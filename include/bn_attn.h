@@ -173,6 +173,28 @@ BN_API int bn_attn_decode_paged(const void* q, const void* pool, int64_t pool_pa
                          int rope_q, int max_seq_len, int chunk_tokens, void* workspace, size_t workspace_bytes,
                          bn_stream_t stream);
 
+/* The same decode for callers that cannot hand over a scratch buffer.
+ * (No counterpart in the reference, which has neither a KV cache nor a decode operator.)
+ *
+ * Who needs it: code that runs where device allocation is off limits — a plugin called from inside someone else's
+ * memory plan (a serving engine that has already carved up all of HBM, an inference graph whose buffers were fixed
+ * at load time), or a real-time loop that may not touch the allocator because cudaMalloc/cudaFree synchronise the
+ * device.  Such a caller still owns q, the cache and the outputs, but has nowhere to put the split-KV partials.
+ *
+ * Here the partials live in an array built into the library's device image (about 3.3 MB, held by every GPU that
+ * loads the library until the process exits).  The call makes no cudaMalloc / cudaFree and calls no allocating
+ * routine.  Limits: B * Hkv <= 256 and max_seq_len <= 4096; anything larger returns BN_ERR_UNSUPPORTED and
+ * belongs to bn_attn_decode_paged.  Arguments as bn_attn_decode_paged, minus chunk_tokens and the workspace.
+ *
+ * The first call on each device looks up the array's device address and clears its header with that device
+ * current; make that first call outside any stream capture.  All calls on a device share the one array, which
+ * keeps what the previous call left (the kernel re-arms its own counters): calls that overlap on the GPU — two
+ * streams, two host threads — race on it; issue them on one stream or otherwise serialise them. */
+BN_API int bn_attn_decode_paged_static(const void* q, const void* pool, int64_t pool_pages, const int32_t* page_table,
+                                       int max_pages, const int32_t* seq_lens, const int32_t* q_positions, void* out,
+                                       float* out_f32, float* lse, int B, int Hq, int Hkv, int D, float scale,
+                                       float theta, int rope_q, int max_seq_len, bn_stream_t stream);
+
 /* Log-sum-exp merge of P partial attention results (split-KV across GPUs):
  *   outs (P, n, D) fp32 normalised partial outputs, lses (P, n) natural log
  *   (-inf = empty part)  ->  out_f32 (n, D) and/or out_bf16 (n, D), lse (n). */
