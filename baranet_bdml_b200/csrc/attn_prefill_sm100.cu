@@ -431,10 +431,16 @@ __device__ __forceinline__ float ex2_fma_pipe(float x) {
 
 // exp2 of 32 scores -> 16 packed bf16x2.  The row sum is accumulated two-wide in `sum2`; `pmax` tracks the
 // largest p (packed bf16x2).  scale2 / mneg2 hold (scale_log2, scale_log2) and (-m*scale_log2, same).
+// Written as three sweeps over the registers (scale, exponential, pack) so that the 32 exponentials are
+// independent instructions back to back in the MUFU pipe.
+#ifndef BN_CHUNK_VARIANT
+#define BN_CHUNK_VARIANT 0
+#endif
 template <bool MASK>
-__device__ __forceinline__ void softmax_chunk(const uint32_t (&r)[32], uint32_t (&pk)[16], uint64_t scale2,
+__device__ __forceinline__ void softmax_chunk(uint32_t (&r)[32], uint32_t (&pk)[16], uint64_t scale2,
                                               uint64_t mneg2, int first_key, int row_last, uint32_t& pmax,
                                               uint64_t& sum2) {
+#if BN_CHUNK_VARIANT == 0
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
         float x0, x1;
@@ -450,6 +456,36 @@ __device__ __forceinline__ void softmax_chunk(const uint32_t (&r)[32], uint32_t 
         pk[i / 2] = pack_bf16(p0, p1);
         asm("max.bf16x2 %0, %0, %1;" : "+r"(pmax) : "r"(pk[i / 2]));
     }
+#else
+    float x[32];
+#pragma unroll
+    for (int i = 0; i < 32; i += 2)
+        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), scale2, mneg2), x[i], x[i + 1]);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        const bool emu = ((i >> 1) & 7) < BN_EMU;
+        x[i] = emu ? ex2_fma_pipe(x[i]) : ex2(x[i]);
+        if (MASK) {
+            if (first_key + i > row_last) x[i] = 0.f;
+        }
+    }
+    uint64_t sa = 0, sb = 0;
+    uint32_t ma = 0, mb = 0;
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+        sa = add_f32x2(sa, pack_f32x2(x[i], x[i + 1]));
+        sb = add_f32x2(sb, pack_f32x2(x[i + 2], x[i + 3]));
+        pk[i / 2] = pack_bf16(x[i], x[i + 1]);
+        pk[i / 2 + 1] = pack_bf16(x[i + 2], x[i + 3]);
+#if BN_CHUNK_VARIANT != 2
+        asm("max.bf16x2 %0, %0, %1;" : "+r"(ma) : "r"(pk[i / 2]));
+        asm("max.bf16x2 %0, %0, %1;" : "+r"(mb) : "r"(pk[i / 2 + 1]));
+#endif
+    }
+    sum2 = add_f32x2(sum2, add_f32x2(sa, sb));
+    asm("max.bf16x2 %0, %0, %1;" : "+r"(ma) : "r"(mb));
+    asm("max.bf16x2 %0, %0, %1;" : "+r"(pmax) : "r"(ma));
+#endif
 }
 
 struct UnitInfo {
@@ -712,7 +748,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 if (lane == 0) mbar_arrive(smem_u32(&bar_qrot[buf][u]));
             }
 
-            float m_ref = -INFINITY;   // exponent reference, raw score units
+            float m_ref = 0.f;         // exponent reference, raw score units
             float l_run = 0.f;
             const int row_last = p.causal ? min(p.S - 1, gi + p.position_offset) : p.S - 1;
             const int tile_free_last = p.causal ? min(p.S - 1, i0 + p.position_offset) : p.S - 1;   // no mask needed up to here
@@ -747,15 +783,18 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                     uint32_t r0[32], r1[32], pk[16];
                     tc::ld32(tS + 0, r0);
                     tc::wait_ld(r0);
+                    if (row == 0) BN_STAMP(7, u, j);
                     tc::ld32(tS + 32, r1);
                     if (need_mask) softmax_chunk<true>(r0, pk, scale2, mneg2, j0, row_last, pmax, sum2);
                     else softmax_chunk<false>(r0, pk, scale2, mneg2, j0, row_last, pmax, sum2);
+                    if (row == 0) BN_STAMP(8, u, j);
                     // P(j-1) is still being read by its P V until bar_pv says otherwise
                     bool good = true;
                     if (first_store_needs_pv) {
                         good = mbar_wait(smem_u32(&bar_pv[u]), (tiles_done + j - 1) & 1, &s_abort);
                         tc::fence_after_sync();
                     }
+                    if (row == 0) BN_STAMP(9, u, j);
                     tc::st16(tP + 0, pk);
                     tc::wait_ld(r1);
                     tc::ld32(tS + 64, r0);
@@ -771,27 +810,31 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                     if (need_mask) softmax_chunk<true>(r1, pk, scale2, mneg2, j0 + 96, row_last, pmax, sum2);
                     else softmax_chunk<false>(r1, pk, scale2, mneg2, j0 + 96, row_last, pmax, sum2);
                     tc::st16(tP + 48, pk);
+                    if (row == 0) BN_STAMP(10, u, j);
                     float s0, s1;
                     unpack_f32x2(sum2, s0, s1);
                     return good ? s0 + s1 : NAN;
                 };
 
-                if (j == 0) {
-                    const float tmax = tile_max();
-                    if (tmax > -INFINITY) m_ref = tmax;
-                }
+                // The exponent reference starts at 0 and moves only when it has to: p = 2^(s*c - ref) may be
+                // anywhere in [2^-64, 2^64] without any loss (bf16 and fp32 keep their relative precision over
+                // that range), so for ordinary score magnitudes there is never a second pass or an O rescale.
+                if (j == 0) m_ref = 0.f;
                 uint32_t pmax = 0;           // bf16x2 (+0, +0)
-                float lsum = tile_pass(m_ref == -INFINITY ? 0.f : -m_ref * p.scale_log2, pmax, j > 0);
+                float lsum = tile_pass(-m_ref * p.scale_log2, pmax, j > 0);
                 if (s_abort) { ok = false; break; }
-                // did any p leave the safe range (> 2^8, incl. inf)?  bf16 bit patterns are monotone for p >= 0
-                const bool over = max(pmax & 0xffffu, pmax >> 16) > 0x4380u;   // bf16(256.0)
+                // Did any p leave the safe range?  bf16 bit patterns are monotone for p >= 0.  Too large: > 2^64
+                // (incl. inf).  Too small matters on the first tile only, where key 0 is valid for every row: a
+                // largest p below 2^-64 means the whole row may have underflowed.
+                const uint32_t pm = max(pmax & 0xffffu, pmax >> 16);
+                const bool over = pm > 0x5F80u || (j == 0 && pm < 0x1F80u);
                 if (__any_sync(0xffffffffu, over)) {
-                    // rare: the tile exceeds the reference by more than 2^8.  Move the reference to the true row
-                    // maximum, rescale O and l, redo the tile.
-                    const float m_new = fmaxf(m_ref, tile_max());
+                    // rare: move the reference to the true row maximum, rescale O and l, redo the tile.
+                    const float tmax = tile_max();
+                    const float m_new = j == 0 ? tmax : fmaxf(m_ref, tmax);   // the first tile may also move it down
                     const float m_upd = m_new == -INFINITY ? m_ref : m_new;
                     if (j > 0) {
-                        const float alpha = m_ref == -INFINITY ? 0.f : ex2((m_ref - m_upd) * p.scale_log2);
+                        const float alpha = ex2((m_ref - m_upd) * p.scale_log2);
                         l_run *= alpha;
 #pragma unroll
                         for (int c = 0; c < 2; ++c) {
@@ -805,7 +848,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                     }
                     m_ref = m_upd;
                     pmax = 0;
-                    lsum = tile_pass(m_ref == -INFINITY ? 0.f : -m_ref * p.scale_log2, pmax, false);
+                    lsum = tile_pass(-m_ref * p.scale_log2, pmax, false);
                 }
                 l_run += lsum;
                 tc::wait_st();

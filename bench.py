@@ -105,6 +105,8 @@ def cpu_prefill_sample(n_batches: int, steps: int = 1, warmup: int = 0):
     """Times the plain-C restatement (all host threads) on `n_batches` batch elements of config 2."""
     import numpy as np
     from oracle import cref, ref_attention as R
+    # all the host cores this process may use (torchrun presets OMP_NUM_THREADS=1 for its children)
+    cref.set_num_threads(len(os.sched_getaffinity(0)))
     c = PREFILL
     rng = np.random.default_rng(0)
     q = R.round_bf16(rng.standard_normal((n_batches, c["S"], c["Hq"], c["D"]), dtype=np.float32))
