@@ -39,16 +39,6 @@ namespace bn {
 
 using namespace ptx;
 
-#ifndef BN_DDBG
-#define BN_DDBG 0
-#endif
-#if BN_DDBG
-#define FSTAMP(tag) do { if (BN_DDBG > 1 && blockIdx.x == 5 && threadIdx.x == 0 && p.lse && fidx < 120) { reinterpret_cast<long long*>(p.lse)[148 * 8 + 2 * fidx] = (tag); reinterpret_cast<long long*>(p.lse)[148 * 8 + 2 * fidx + 1] = clock64(); ++fidx; } } while (0)
-#define DSTAMP(i) do { if (threadIdx.x == (i == 2 || i == 3 || i == 4 || i == 5 ? 0 : 0) && p.lse) reinterpret_cast<unsigned long long*>(p.lse)[blockIdx.x * 8 + (i)] = globaltimer_ns(); } while (0)
-#else
-#define DSTAMP(i) do {} while (0)
-#define FSTAMP(tag) do {} while (0)
-#endif
 constexpr int DEC_D = 64;
 constexpr int DEC_G = 8;                    // query heads per KV head served by one MMA (n = 8)
 constexpr int DEC_STAGE_TOKENS = 256;
@@ -195,7 +185,6 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    DSTAMP(0);
 
     if (tid == 0) {
         for (int s = 0; s < DEC_NSTAGES; ++s) {
@@ -239,10 +228,6 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
     sc.B = p.B;
     sc.T = p.Hkv * s_prefix[p.B];
     sc.G = max(1, min((int)gridDim.x, sc.T / p.min_stages));
-    DSTAMP(1);
-#if BN_DDBG
-    if (tid == 0 && p.lse) { unsigned smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid)); reinterpret_cast<unsigned long long*>(p.lse)[blockIdx.x * 8 + 6] = smid; }
-#endif
     const bool active = sc.T > 0 && (int)blockIdx.x < sc.G;
     const int range_lo = active ? sc.range_begin(blockIdx.x) : 0;
     const int range_hi = active ? sc.range_begin(blockIdx.x + 1) : 0;
@@ -348,7 +333,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
                     if (p.out_f32)
                         *reinterpret_cast<float4*>(p.out_f32 + crow * DEC_D + cd + 4 * i) = make_float4(r0, r1, r2, r3);
                 }
-                if (!BN_DDBG && p.lse && lane % 4 == 0) p.lse[crow] = l2 > 0.f ? (m2 + log2f(l2)) * LN2 : -INFINITY;
+                if (p.lse && lane % 4 == 0) p.lse[crow] = l2 > 0.f ? (m2 + log2f(l2)) * LN2 : -INFINITY;
             }
         }
         if (lane == 0 && s_abort) atomicExch(&p.hdr->error, BN_ERR_TIMEOUT);
@@ -365,7 +350,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
         const size_t row = (size_t)b * p.Hq + (size_t)g * p.n_rep + th;
         if (p.out) *reinterpret_cast<uint32_t*>(p.out + row * DEC_D + td) = 0u;
         if (p.out_f32) *reinterpret_cast<float2*>(p.out_f32 + row * DEC_D + td) = make_float2(0.f, 0.f);
-        if (!BN_DDBG && p.lse && tid % DEC_TPH == 0) p.lse[row] = -INFINITY;
+        if (p.lse && tid % DEC_TPH == 0) p.lse[row] = -INFINITY;
     }
 
     int stage = 0;
@@ -402,9 +387,6 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
         *reinterpret_cast<uint32_t*>(&s_q[th][td]) = pack_bf16(x0, x1);
     };
 
-#if BN_DDBG
-    int fidx = 0;
-#endif
     SegmentIter iter;
     iter.init(range_lo, range_hi);
     Segment sg, sg_next;
@@ -420,11 +402,9 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
         ok = group_sync();
     }
     while (ok && have) {
-        FSTAMP(1);
         // look one segment ahead so that its query is already on the way
         const bool have_next = iter.next(sc, sg_next);
         const uint32_t q_raw_next = have_next ? load_q_raw(sg_next) : 0u;
-        FSTAMP(2);
         // Q^T fragments (k = dims, n = heads)
         uint32_t qb[4][2];
 #pragma unroll
@@ -441,12 +421,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
             for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
 
         for (int s = sg.s0; s < sg.s1; ++s) {
-            FSTAMP(10);
             if (!mbar_wait(smem_u32(&full_bar[stage]), phase, &s_abort)) { ok = false; break; }
-            FSTAMP(11);
-#if BN_DDBG
-            if (tid == 0 && p.lse && reinterpret_cast<unsigned long long*>(p.lse)[blockIdx.x * 8 + 2] == 0) DSTAMP(2);
-#endif
             const int ntok = min(DEC_STAGE_TOKENS, sg.L - s * DEC_STAGE_TOKENS);
             const uint32_t sbase = ring + stage * DEC_STAGE_BYTES;
             float sv[DEC_PPW][4];
@@ -530,8 +505,6 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
             if (++stage == DEC_NSTAGES) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        DSTAMP(3);
-        FSTAMP(3);
 
         // ------------------------------------------------ merge the 4 warps
 #pragma unroll
@@ -552,9 +525,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
             mrg_o[warp][hA][d + 8] = o[i][2];
             mrg_o[warp][hA + 1][d + 8] = o[i][3];
         }
-        FSTAMP(4);
         if (!group_sync()) break;
-        FSTAMP(5);
         // thread -> head th, dims td, td + 1
         const int th = tid / DEC_TPH, td = (tid % DEC_TPH) * DEC_DPT;
         float mstar = -INFINITY;
@@ -577,7 +548,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
             const float r0 = a[0] * inv, r1 = a[1] * inv;
             if (p.out) *reinterpret_cast<uint32_t*>(p.out + row * DEC_D + td) = pack_bf16(r0, r1);
             if (p.out_f32) *reinterpret_cast<float2*>(p.out_f32 + row * DEC_D + td) = make_float2(r0, r1);
-            if (!BN_DDBG && p.lse && tid % DEC_TPH == 0) p.lse[row] = l_ > 0.f ? (m_ + log2f(l_)) * LN2 : -INFINITY;
+            if (p.lse && tid % DEC_TPH == 0) p.lse[row] = l_ > 0.f ? (m_ + log2f(l_)) * LN2 : -INFINITY;
         };
         if (sg.n_parts == 1) {
             write_final(mstar, lsum, acc);
@@ -593,38 +564,34 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
             if (lane == 0) mbar_arrive(smem_u32(&part_bar));
         }
         // the next segment's query replaces this one's (every warp took its fragments long ago)
-        FSTAMP(6);
         if (have_next) store_q(sg_next, q_raw_next);
-        FSTAMP(7);
         if (!group_sync()) break;              // mrg_* free again, s_q visible
-        FSTAMP(8);
-        DSTAMP(4);
         sg = sg_next;
         q_raw = q_raw_next;
         have = have_next;
     }
-    DSTAMP(5);
     if (s_abort && lane == 0) atomicExch(&p.hdr->error, BN_ERR_TIMEOUT);
 }
 
 // ---------------------------------------------------------------------------
 // LSE combine of P partial results (used for the cross-GPU sequence split)
 // ---------------------------------------------------------------------------
-__global__ void lse_combine_kernel(const float* __restrict__ outs, const float* __restrict__ lses, int P, int64_t n,
-                                   int D, float* __restrict__ out_f32, __nv_bfloat16* __restrict__ out_bf16,
+__global__ void lse_combine_kernel(const float* __restrict__ outs, int64_t outs_part_stride,
+                                   const float* __restrict__ lses, int64_t lses_part_stride, int P, int64_t n, int D,
+                                   float* __restrict__ out_f32, __nv_bfloat16* __restrict__ out_bf16,
                                    float* __restrict__ lse) {
     const int64_t row = blockIdx.x;
     float mstar = -INFINITY;
-    for (int pp = 0; pp < P; ++pp) mstar = fmaxf(mstar, lses[(int64_t)pp * n + row]);
+    for (int pp = 0; pp < P; ++pp) mstar = fmaxf(mstar, lses[pp * lses_part_stride + row]);
     const float ms = mstar == -INFINITY ? 0.f : mstar;
     float tot = 0.f;
-    for (int pp = 0; pp < P; ++pp) tot += expf(lses[(int64_t)pp * n + row] - ms);
+    for (int pp = 0; pp < P; ++pp) tot += expf(lses[pp * lses_part_stride + row] - ms);
     const float inv = tot > 0.f ? 1.f / tot : 0.f;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float acc = 0.f;
         for (int pp = 0; pp < P; ++pp) {
-            const float l = lses[(int64_t)pp * n + row];
-            if (l > -INFINITY) acc += outs[((int64_t)pp * n + row) * D + d] * expf(l - ms);
+            const float l = lses[pp * lses_part_stride + row];
+            if (l > -INFINITY) acc += outs[pp * outs_part_stride + row * D + d] * expf(l - ms);
         }
         acc *= inv;
         if (out_f32) out_f32[row * D + d] = acc;
@@ -787,13 +754,19 @@ extern "C" int bn_attn_decode_paged_static(const void* q, const void* pool, int6
                          Hkv, D, scale, theta, rope_q, max_seq_len, 0, scratch, DEC_STATIC_BYTES, stream);
 }
 
-extern "C" int bn_attn_lse_combine(const float* outs, const float* lses, int P, int64_t n, int D, float* out_f32,
-                                   void* out_bf16, float* lse, bn_stream_t stream) {
+extern "C" int bn_attn_lse_combine_strided(const float* outs, int64_t outs_part_stride, const float* lses,
+                                           int64_t lses_part_stride, int P, int64_t n, int D, float* out_f32,
+                                           void* out_bf16, float* lse, bn_stream_t stream) {
     if (!outs || !lses || (!out_f32 && !out_bf16)) return fail(BN_ERR_INVALID_ARG, "bn_attn_lse_combine: null pointer");
     if (P <= 0 || n < 0 || D <= 0) return fail(BN_ERR_INVALID_ARG, "bn_attn_lse_combine: bad sizes P=%d D=%d", P, D);
     if (int rc = require_sm100()) return rc;
     if (n == 0) return BN_OK;
-    lse_combine_kernel<<<(unsigned)n, 64, 0, as_stream(stream)>>>(outs, lses, P, n, D, out_f32,
-                                                                static_cast<__nv_bfloat16*>(out_bf16), lse);
+    lse_combine_kernel<<<(unsigned)n, 64, 0, as_stream(stream)>>>(outs, outs_part_stride, lses, lses_part_stride, P, n,
+                                                                D, out_f32, static_cast<__nv_bfloat16*>(out_bf16), lse);
     return launch_status("bn_attn_lse_combine");
+}
+
+extern "C" int bn_attn_lse_combine(const float* outs, const float* lses, int P, int64_t n, int D, float* out_f32,
+                                   void* out_bf16, float* lse, bn_stream_t stream) {
+    return bn_attn_lse_combine_strided(outs, n * D, lses, n, P, n, D, out_f32, out_bf16, lse, stream);
 }

@@ -37,9 +37,6 @@ namespace bn {
 
 using namespace ptx;
 
-#ifndef BN_DBG
-#define BN_DBG 0
-#endif
 constexpr int PF_D = 64;
 constexpr int PF_BM = 128;           // query rows per CTA
 constexpr int PF_BN = 128;           // keys per tile
@@ -397,57 +394,31 @@ prefill_kernel_v1(const __grid_constant__ CUtensorMap tmap_k, const __grid_const
 // buffered across units) and are rotated in place by their softmax group.
 // TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,320) O1 [320,384)
 //                     P0 [384,448) P1 [448,512)
-// Softmax is ONE pass per tile: the exponent reference is the running maximum
-// of the earlier tiles; if a tile turns out to exceed it by more than 2^8 the
-// warp rescales O, moves the reference and redoes the tile (the first tile of a
-// unit takes its true maximum first).  Part of the exponentials can be evaluated
-// on the FMA pipe (Cody-Waite split + cubic): at head_dim 64 the MUFU unit, not
-// the tensor pipe, is the first limit.
-#if (BN_DBG & 128)
-// timeline instrumentation: the lse buffer receives clock64() stamps of CTA 0's first unit
-#define BN_STAMP(ev, u_, j_) do { if (blockIdx.x == 0 && it == 0 && p.lse) reinterpret_cast<long long*>(p.lse)[((ev) * 2 + (u_)) * 32 + (j_)] = clock64(); } while (0)
-#else
-#define BN_STAMP(ev, u_, j_) do {} while (0)
-#endif
-#ifndef BN_EMU
-#define BN_EMU 0    // of every 8 (pairs of) exponentials, how many go to the FMA pipe
-#endif
+// Softmax is ONE pass per tile with an exponent reference that starts at 0 and
+// moves only when a probability would leave [2^-64, 2^64] (bf16 and fp32 keep
+// their relative precision over that range): then the warp takes the true row
+// maximum, rescales O and l and redoes the tile.  The MMA warp issues the next
+// Q K^T of a tile before its P V, so the tile's next softmax starts while the
+// P V still runs.  At head_dim 64 the MUFU unit (one exponential per score), not
+// the tensor pipe, is the first limit; moving a share of the exponentials to the
+// FMA pipe (Cody-Waite split + cubic) was measured and did not pay, because a
+// softmax group that runs alone is bound by instruction latency, not by MUFU.
 constexpr int P2_THREADS = 320;
 constexpr int P2_NSTAGE = 4;
 constexpr int P2_SMEM_BYTES = 1024 + PF_TILE_BYTES * (4 + 2 * P2_NSTAGE);
 constexpr uint32_t P2_TMEM_COLS = 512;
 
-__device__ __forceinline__ float ex2_fma_pipe(float x) {
-    // 2^x for x <= ~8: n = round(x) via the 1.5*2^23 trick, 2^(x-n) by a cubic (rel. err 7.5e-5),
-    // then n is added to the exponent field
-    x = fmaxf(x, -125.0f);
-    const float t = x + 12582912.0f;
-    const float f = x - (t - 12582912.0f);
-    float p = fmaf(f, 0.0551716499f, 0.2426111251f);
-    p = fmaf(p, f, 0.6932609677f);
-    p = fmaf(p, f, 0.9999280572f);
-    return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
-}
-
 // exp2 of 32 scores -> 16 packed bf16x2.  The row sum is accumulated two-wide in `sum2`; `pmax` tracks the
 // largest p (packed bf16x2).  scale2 / mneg2 hold (scale_log2, scale_log2) and (-m*scale_log2, same).
-// Written as three sweeps over the registers (scale, exponential, pack) so that the 32 exponentials are
-// independent instructions back to back in the MUFU pipe.
-#ifndef BN_CHUNK_VARIANT
-#define BN_CHUNK_VARIANT 0
-#endif
 template <bool MASK>
 __device__ __forceinline__ void softmax_chunk(uint32_t (&r)[32], uint32_t (&pk)[16], uint64_t scale2,
                                               uint64_t mneg2, int first_key, int row_last, uint32_t& pmax,
                                               uint64_t& sum2) {
-#if BN_CHUNK_VARIANT == 0
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
         float x0, x1;
         unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), scale2, mneg2), x0, x1);
-        const bool emu = ((i >> 1) & 7) < BN_EMU;
-        float p0 = emu ? ex2_fma_pipe(x0) : ex2(x0);
-        float p1 = emu ? ex2_fma_pipe(x1) : ex2(x1);
+        float p0 = ex2(x0), p1 = ex2(x1);
         if (MASK) {
             if (first_key + i > row_last) p0 = 0.f;
             if (first_key + i + 1 > row_last) p1 = 0.f;
@@ -456,36 +427,6 @@ __device__ __forceinline__ void softmax_chunk(uint32_t (&r)[32], uint32_t (&pk)[
         pk[i / 2] = pack_bf16(p0, p1);
         asm("max.bf16x2 %0, %0, %1;" : "+r"(pmax) : "r"(pk[i / 2]));
     }
-#else
-    float x[32];
-#pragma unroll
-    for (int i = 0; i < 32; i += 2)
-        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), scale2, mneg2), x[i], x[i + 1]);
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        const bool emu = ((i >> 1) & 7) < BN_EMU;
-        x[i] = emu ? ex2_fma_pipe(x[i]) : ex2(x[i]);
-        if (MASK) {
-            if (first_key + i > row_last) x[i] = 0.f;
-        }
-    }
-    uint64_t sa = 0, sb = 0;
-    uint32_t ma = 0, mb = 0;
-#pragma unroll
-    for (int i = 0; i < 32; i += 4) {
-        sa = add_f32x2(sa, pack_f32x2(x[i], x[i + 1]));
-        sb = add_f32x2(sb, pack_f32x2(x[i + 2], x[i + 3]));
-        pk[i / 2] = pack_bf16(x[i], x[i + 1]);
-        pk[i / 2 + 1] = pack_bf16(x[i + 2], x[i + 3]);
-#if BN_CHUNK_VARIANT != 2
-        asm("max.bf16x2 %0, %0, %1;" : "+r"(ma) : "r"(pk[i / 2]));
-        asm("max.bf16x2 %0, %0, %1;" : "+r"(mb) : "r"(pk[i / 2 + 1]));
-#endif
-    }
-    sum2 = add_f32x2(sum2, add_f32x2(sa, sb));
-    asm("max.bf16x2 %0, %0, %1;" : "+r"(ma) : "r"(mb));
-    asm("max.bf16x2 %0, %0, %1;" : "+r"(pmax) : "r"(ma));
-#endif
 }
 
 struct UnitInfo {
@@ -595,7 +536,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 for (int j = 0; ok && j < w.n_max; ++j) {
                     ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &s_abort);
                     if (!ok) break;
-                    BN_STAMP(6, 0, j);
                     mbar_arrive_expect_tx(smem_u32(&bar_kfull[stage]), PF_TILE_BYTES);
                     tma_load_4d(sK + stage * PF_TILE_BYTES, &tmap_k, 0, w.g, j * PF_BN, w.b, smem_u32(&bar_kfull[stage]));
                     mbar_arrive_expect_tx(smem_u32(&bar_vfull[stage]), PF_TILE_BYTES);
@@ -643,7 +583,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             };
             if (w.n_max > 0) ok = mbar_wait(smem_u32(&bar_kfull[stage]), phase, &s_abort);
             if (!ok) break;
-            if (lane == 0) BN_STAMP(0, 1, 0);
             if (w.n_t[0] > 0) issue_qk(0, stage, 0);
             if (w.n_t[1] > 0) issue_qk(1, stage, 0);
             for (int j = 0; ok && j < w.n_max; ++j) {
@@ -655,7 +594,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                     if (j >= w.n_t[u]) continue;
                     ok = mbar_wait(smem_u32(&bar_p[u]), (tiles_done[u] + j) & 1, &s_abort);
                     if (!ok) break;
-                    if (lane == 0) BN_STAMP(3, u, j);
                     // S_u(j+1) = Q_u K(j+1)^T first: its S columns are free because P_u(j) has been written, and
                     // the softmax of tile j+1 can start while P_u(j) V(j) still runs
                     if (j + 1 < w.n_t[u]) {
@@ -682,7 +620,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                         if (last_user) tc::commit(smem_u32(&bar_empty[stage]));   // K(j)/V(j) may be overwritten
                     }
                     __syncwarp();
-                    if (lane == 0) BN_STAMP(4, u, j);
                 }
                 stage = nstage;
                 phase = nphase;
@@ -712,7 +649,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             const int b = w.b, h = w.h;
             const int i0 = (2 * w.qp + u) * PF_BM;
             const int gi = i0 + row;
-            if (tid == 0) BN_STAMP(0, 0, 0);
 
             // prologue: rotate the TMA-loaded Q row in place (128-byte-swizzled, K-major)
             {
@@ -756,7 +692,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             for (int j = 0; j < nt; ++j) {
                 ok = mbar_wait(smem_u32(&bar_s[u]), (tiles_done + j) & 1, &s_abort);
                 if (!ok) break;
-                if (row == 0) BN_STAMP(1, u, j);
                 tc::fence_after_sync();
                 const int j0 = j * PF_BN;
                 const bool need_mask = (j0 + PF_BN - 1) > tile_free_last;
@@ -783,18 +718,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                     uint32_t r0[32], r1[32], pk[16];
                     tc::ld32(tS + 0, r0);
                     tc::wait_ld(r0);
-                    if (row == 0) BN_STAMP(7, u, j);
                     tc::ld32(tS + 32, r1);
                     if (need_mask) softmax_chunk<true>(r0, pk, scale2, mneg2, j0, row_last, pmax, sum2);
                     else softmax_chunk<false>(r0, pk, scale2, mneg2, j0, row_last, pmax, sum2);
-                    if (row == 0) BN_STAMP(8, u, j);
                     // P(j-1) is still being read by its P V until bar_pv says otherwise
                     bool good = true;
                     if (first_store_needs_pv) {
                         good = mbar_wait(smem_u32(&bar_pv[u]), (tiles_done + j - 1) & 1, &s_abort);
                         tc::fence_after_sync();
                     }
-                    if (row == 0) BN_STAMP(9, u, j);
                     tc::st16(tP + 0, pk);
                     tc::wait_ld(r1);
                     tc::ld32(tS + 64, r0);
@@ -810,7 +742,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                     if (need_mask) softmax_chunk<true>(r1, pk, scale2, mneg2, j0 + 96, row_last, pmax, sum2);
                     else softmax_chunk<false>(r1, pk, scale2, mneg2, j0 + 96, row_last, pmax, sum2);
                     tc::st16(tP + 48, pk);
-                    if (row == 0) BN_STAMP(10, u, j);
                     float s0, s1;
                     unpack_f32x2(sum2, s0, s1);
                     return good ? s0 + s1 : NAN;
@@ -853,7 +784,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 l_run += lsum;
                 tc::wait_st();
                 tc::fence_before_sync();
-                if (row == 0) BN_STAMP(2, u, j);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bar_p[u]));
             }
@@ -864,7 +794,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             ok = mbar_wait(smem_u32(&bar_o[u]), units_done & 1, &s_abort);
             ++units_done;
             if (!ok) break;
-            if (row == 0) BN_STAMP(5, u, 0);
             tc::fence_after_sync();
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             __nv_bfloat16* dst = p.out + (((size_t)b * p.S + gi) * p.Hq + h) * PF_D;
@@ -893,13 +822,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                     o4.w = pack_bf16(__uint_as_float(r1[v * 8 + 6]) * inv, __uint_as_float(r1[v * 8 + 7]) * inv);
                     *reinterpret_cast<uint4*>(dst + 32 + v * 8) = o4;
                 }
-#if !(BN_DBG & 128)
                 if (p.lse)
                     p.lse[((size_t)b * p.Hq + h) * p.S + gi] =
                         l_run > 0.f ? (m_ref * p.scale_log2 + log2f(l_run)) * PF_LN2 : -INFINITY;
-#endif
             }
-            if (row == 0) BN_STAMP(5, u, 1);
         }
     }
 

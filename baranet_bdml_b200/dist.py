@@ -74,3 +74,34 @@ def combine_partials(out_partial: torch.Tensor, lse_partial: torch.Tensor, group
         from . import ops
         merge = ops.lse_combine
     return merge(outs, lses)
+
+
+class PartialExchange:
+    """The exchange step of the sequence-split decode with nothing but three launches per step: the decode
+    kernel writes its normalised partial output and log-sum-exp straight into `out_view` / `lse_view` (two
+    regions of one contiguous send buffer), `combine()` gathers every rank's buffer with one all-gather and
+    merges them with bn_attn_lse_combine_strided.  All buffers are allocated once."""
+
+    def __init__(self, n: int, D: int, group=None, device="cuda"):
+        import torch.distributed as dist
+        self.n, self.D, self.group = int(n), int(D), group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.send = torch.empty(self.n * (self.D + 1), dtype=torch.float32, device=device)
+        self.recv = torch.empty(self.world * self.n * (self.D + 1), dtype=torch.float32, device=device)
+        self.out_view = self.send[: self.n * self.D].view(self.n, self.D)
+        self.lse_view = self.send[self.n * self.D:]
+        self.out = torch.empty((self.n, self.D), dtype=torch.float32, device=device)
+        self.lse = torch.empty((self.n,), dtype=torch.float32, device=device)
+
+    def combine(self) -> Tuple[torch.Tensor, torch.Tensor]:
+        import torch.distributed as dist
+        from . import _lib
+        src = self.send
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.recv, self.send, group=self.group)
+            src = self.recv
+        stride = self.n * (self.D + 1)
+        _lib.check(_lib.load().bn_attn_lse_combine_strided(
+            src.data_ptr(), stride, src.data_ptr() + 4 * self.n * self.D, stride, self.world, self.n, self.D,
+            self.out.data_ptr(), None, self.lse.data_ptr(), torch.cuda.current_stream().cuda_stream))
+        return self.out, self.lse

@@ -33,6 +33,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+_emit = print
+
 PREFILL = dict(B=8, S=2048, Hq=32, Hkv=4, D=64)
 DECODE = dict(B=64, Hq=32, Hkv=4, D=64, Lmin=1024, Lmax=4096, page=16)
 
@@ -141,7 +143,7 @@ def run_reference_arm(args):
         "e2e": {"value": r["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    _emit(json.dumps(line))
 
 
 # ----------------------------------------------------------------------------- GPU arm
@@ -305,13 +307,13 @@ def measure_longctx(torch, args, rank, world, dist, reduce_max, pk):
     cache.seq_lens.fill_(Lloc)
     q = torch.randn((B, Hq, D), device="cuda").to(torch.bfloat16)
     qpos = torch.full((B,), L - 1, dtype=torch.int32, device="cuda")
-    o32 = torch.empty((B, Hq, D), dtype=torch.float32, device="cuda")
-    lse = torch.empty((B, Hq), dtype=torch.float32, device="cuda")
+    ex = bdist.PartialExchange(B * Hq, D)
+    o32, lse = ex.out_view.view(B, Hq, D), ex.lse_view.view(B, Hq)
 
     def step(i):
         cache.decode(q, num_heads=Hq, out_f32=o32, lse=lse, q_positions=qpos, max_seq_len=Lloc)
         if world > 1:
-            bdist.combine_partials(o32.view(B * Hq, D), lse.view(B * Hq))
+            ex.combine()
 
     steps = max(args.steps // 4, 8)
     ms = reduce_max(time_loop(torch, step, steps, 3, dist))
@@ -329,7 +331,7 @@ def measure_longctx(torch, args, rank, world, dist, reduce_max, pk):
         "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": pk["hbm"], "unit": "GB/s",
                      "frac": gbs / world / pk["hbm"], "traffic": None, "peak_source": pk["source"],
                      "kernel": "decode_paged_kernel", "note": "per GPU; includes the exchange when n_gpus > 1"},
-        "gpu_launches": steps * (1 if world == 1 else 2),
+        "gpu_launches": steps * (1 if world == 1 else 2),   # + one NCCL all-gather per step when n_gpus > 1
     }
 
 
@@ -377,12 +379,21 @@ def run_ours(args):
             r = cpu_prefill_sample(n_batches=2)
             result["cpu_baseline"] = {"value": r["value"], "unit": "TFLOP/s", "cores": r["cores"], "kind": "port",
                                       "sample": r["sample"], "seconds": r["seconds"]}
-        print(json.dumps(result), flush=True)
+        _emit(json.dumps(result))
     if dist is not None:
         dist.destroy_process_group()
 
 
 def main():
+    # stdout carries exactly one JSON line: everything else that writes to file descriptor 1 (NCCL's version
+    # banner, library chatter) is sent to stderr, and the line is written to the real stdout at the end
+    real_stdout = os.fdopen(os.dup(1), "w")
+    sys.stdout.flush()
+    os.dup2(2, 1)
+    global _emit
+    def _emit(line):
+        real_stdout.write(line + "\n")
+        real_stdout.flush()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)

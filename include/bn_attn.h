@@ -201,6 +201,14 @@ BN_API int bn_attn_decode_paged_static(const void* q, const void* pool, int64_t 
 BN_API int bn_attn_lse_combine(const float* outs, const float* lses, int P, int64_t n, int D, float* out_f32,
                         void* out_bf16, float* lse, bn_stream_t stream);
 
+/* Same merge with explicit strides (in floats) between the parts of `outs` and
+ * of `lses`, so that the P parts may sit in one gathered buffer per rank,
+ * e.g. [n*D outputs | n log-sum-exps] repeated P times (what one all-gather of
+ * each rank's contiguous send buffer produces). */
+BN_API int bn_attn_lse_combine_strided(const float* outs, int64_t outs_part_stride, const float* lses,
+                                       int64_t lses_part_stride, int P, int64_t n, int D, float* out_f32,
+                                       void* out_bf16, float* lse, bn_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -185,3 +185,35 @@ def test_lse_combine_edge_cases(lib):
     assert np.array_equal(np.isfinite(g), np.isfinite(rlse))
     assert np.abs(g[np.isfinite(g)] - rlse[np.isfinite(rlse)]).max() <= 1e-5
     assert np.abs(got.cpu().numpy()[4] - outs[2, 4]).max() <= 1e-6
+
+
+def test_lse_combine_on_a_gathered_buffer(lib):
+    """The layout one all-gather produces: per rank [n*D outputs | n log-sum-exps], P ranks back to back."""
+    from baranet_bdml_b200 import _lib
+    rng = np.random.default_rng(9)
+    P, n, Dd = 4, 12, 64
+    outs = rng.standard_normal((P, n, Dd), dtype=np.float32)
+    lses = (rng.standard_normal((P, n)) * 3).astype(np.float32)
+    lses[2, 5] = -np.inf
+    buf = np.concatenate([np.concatenate([outs[r].reshape(-1), lses[r]]) for r in range(P)]).astype(np.float32)
+    t = torch.from_numpy(buf).cuda()
+    out = torch.empty((n, Dd), dtype=torch.float32, device="cuda")
+    lse = torch.empty((n,), dtype=torch.float32, device="cuda")
+    stride = n * (Dd + 1)
+    _lib.check(lib.bn_attn_lse_combine_strided(t.data_ptr(), stride, t.data_ptr() + 4 * n * Dd, stride, P, n, Dd,
+                                               out.data_ptr(), None, lse.data_ptr(), None))
+    torch.cuda.synchronize()
+    ref, rlse = R.lse_combine(outs, lses)
+    assert np.abs(out.cpu().numpy() - ref).max() <= 1e-5
+    assert np.abs(lse.cpu().numpy() - rlse).max() <= 1e-5
+
+
+def test_partial_exchange_single_rank(lib):
+    """PartialExchange without a process group: the merge of one part is the part itself."""
+    from baranet_bdml_b200.dist import PartialExchange
+    ex = PartialExchange(6, 64)
+    ex.out_view.copy_(torch.arange(6 * 64, dtype=torch.float32, device="cuda").view(6, 64))
+    ex.lse_view.copy_(torch.linspace(-2, 2, 6, device="cuda"))
+    o, l = ex.combine()
+    torch.cuda.synchronize()
+    assert torch.equal(o, ex.out_view) and torch.allclose(l, ex.lse_view, atol=1e-6)
