@@ -712,27 +712,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 };
                 // one pass over the tile: P = exp2(S * scale_log2 - m_ref * scale_log2) -> TMEM, with the load of the
                 // next 32 columns in flight while the current 32 are processed
-                // last key any row of this WARP may see: 32-column chunks beyond it are entirely masked for the
-                // warp (the upper-right part of a diagonal tile) and are written as zeros without any arithmetic
-                const int warp_last = __shfl_sync(0xffffffffu, row_last, 31);
                 auto tile_pass = [&](float mneg, uint32_t& pmax, bool first_store_needs_pv) {
                     uint64_t sum2 = 0;   // (0.f, 0.f)
                     const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2), mneg2 = pack_f32x2(mneg, mneg);
                     uint32_t r0[32], r1[32], pk[16];
-                    auto chunk = [&](uint32_t (&r)[32], int c) {
-                        if (need_mask && j0 + c * 32 > warp_last) {
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) pk[i] = 0u;
-                        } else if (need_mask) {
-                            softmax_chunk<true>(r, pk, scale2, mneg2, j0 + c * 32, row_last, pmax, sum2);
-                        } else {
-                            softmax_chunk<false>(r, pk, scale2, mneg2, j0 + c * 32, row_last, pmax, sum2);
-                        }
-                    };
                     tc::ld32(tS + 0, r0);
                     tc::wait_ld(r0);
                     tc::ld32(tS + 32, r1);
-                    chunk(r0, 0);
+                    if (need_mask) softmax_chunk<true>(r0, pk, scale2, mneg2, j0, row_last, pmax, sum2);
+                    else softmax_chunk<false>(r0, pk, scale2, mneg2, j0, row_last, pmax, sum2);
                     // P(j-1) is still being read by its P V until bar_pv says otherwise
                     bool good = true;
                     if (first_store_needs_pv) {
@@ -742,14 +730,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                     tc::st16(tP + 0, pk);
                     tc::wait_ld(r1);
                     tc::ld32(tS + 64, r0);
-                    chunk(r1, 1);
+                    if (need_mask) softmax_chunk<true>(r1, pk, scale2, mneg2, j0 + 32, row_last, pmax, sum2);
+                    else softmax_chunk<false>(r1, pk, scale2, mneg2, j0 + 32, row_last, pmax, sum2);
                     tc::st16(tP + 16, pk);
                     tc::wait_ld(r0);
                     tc::ld32(tS + 96, r1);
-                    chunk(r0, 2);
+                    if (need_mask) softmax_chunk<true>(r0, pk, scale2, mneg2, j0 + 64, row_last, pmax, sum2);
+                    else softmax_chunk<false>(r0, pk, scale2, mneg2, j0 + 64, row_last, pmax, sum2);
                     tc::st16(tP + 32, pk);
                     tc::wait_ld(r1);
-                    chunk(r1, 3);
+                    if (need_mask) softmax_chunk<true>(r1, pk, scale2, mneg2, j0 + 96, row_last, pmax, sum2);
+                    else softmax_chunk<false>(r1, pk, scale2, mneg2, j0 + 96, row_last, pmax, sum2);
                     tc::st16(tP + 48, pk);
                     float s0, s1;
                     unpack_f32x2(sum2, s0, s1);
