@@ -37,6 +37,8 @@ _emit = print
 
 PREFILL = dict(B=8, S=2048, Hq=32, Hkv=4, D=64)
 DECODE = dict(B=64, Hq=32, Hkv=4, D=64, Lmin=1024, Lmax=4096, page=16)
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
+NCU_TRAFFIC = {"prefill_kernel": 85.144e6 + 27.124e6, "decode_paged_kernel": 163.590e6 + 4.757e6}
 
 
 def peaks():
@@ -253,7 +255,9 @@ def measure_prefill(torch, ops, args, rank, world, dist, reduce_max, pk):
                    "l2": f"inputs rotate over {n_sets} buffer sets of 151 MB each (> 126 MB L2)",
                    "flops_per_step_per_gpu": flops, "launches_per_step": 2},
         "roofline": {"bound": "tensor", "achieved": ach, "peak": pk["tensor"], "unit": "TFLOP/s",
-                     "frac": ach / pk["tensor"], "traffic": None, "peak_source": pk["source"] + " (bf16 burst)",
+                     "frac": ach / pk["tensor"], "traffic": NCU_TRAFFIC["prefill_kernel"],
+                     "traffic_unit": "bytes of DRAM traffic per launch (ncu capture, profiles/prefill_kernel_config2.md)",
+                     "peak_source": pk["source"] + " (bf16 burst)",
                      "kernel": "prefill_kernel", "kernel_ms": ms_kernel},
         "e2e": None if ms_e2e is None else {
             "value": flops * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
@@ -284,7 +288,9 @@ def measure_decode(torch, args, rank, world, dist, reduce_max, pk):
                    "tokens_in_cache": tokens, "algorithmic_bytes_per_step": bytes_alg,
                    "l2": f"{dsets} distinct caches rotate"},
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s", "frac": gbs / pk["hbm"],
-                     "traffic": None, "peak_source": pk["source"], "kernel": "decode_paged_kernel"},
+                     "traffic": NCU_TRAFFIC["decode_paged_kernel"],
+                     "traffic_unit": "bytes of DRAM traffic per launch (ncu capture, profiles/decode_paged_kernel_config3.md)",
+                     "peak_source": pk["source"], "kernel": "decode_paged_kernel"},
         "gpu_launches": dsteps,
     }
 
