@@ -107,6 +107,7 @@ struct PrefillParams {
     const float2* table;
     int* error_word;
     int B, S, Hq, Hkv, n_rep, n_qtiles, position_offset, causal;
+    float inv_bh, inv_hq, inv_n_rep;     // reciprocals of B*Hq, Hq, n_rep for the persistent kernel's unit decode
     float scale_log2;
 };
 
@@ -434,15 +435,21 @@ struct UnitInfo {
     int n_t[2], n_max;
 };
 
+// k / d and k % d for 0 <= k < 2^22 without the integer-division sequence: float estimate, then a correction
+__device__ __forceinline__ void fast_divmod(int k, int d, float inv_d, int& q, int& r) {
+    q = __float2int_rz(__int2float_rz(k) * inv_d);
+    r = k - q * d;
+    if (r < 0) { --q; r += d; }
+    if (r >= d) { ++q; r -= d; }
+}
+
 __device__ __forceinline__ UnitInfo unit_info(const PrefillParams& p, int k) {
     UnitInfo w;
-    const int BH = p.B * p.Hq;
-    const int n_pairs = (p.n_qtiles + 1) / 2;
-    w.qp = n_pairs - 1 - k / BH;               // heaviest (latest) pair of query tiles first
-    const int bh = k % BH;                      // the heads of a KV group are neighbours
-    w.b = bh / p.Hq;
-    w.h = bh % p.Hq;
-    w.g = w.h / p.n_rep;
+    int qi, bh, rem;
+    fast_divmod(k, p.B * p.Hq, p.inv_bh, qi, bh);
+    w.qp = (p.n_qtiles + 1) / 2 - 1 - qi;      // heaviest (latest) pair of query tiles first
+    fast_divmod(bh, p.Hq, p.inv_hq, w.b, w.h);   // the heads of a KV group are neighbours
+    fast_divmod(w.h, p.n_rep, p.inv_n_rep, w.g, rem);
     const int n_ktiles_all = (p.S + PF_BN - 1) / PF_BN;
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
@@ -640,49 +647,58 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         int q_use = 0;
         uint32_t tiles_done = 0, units_done = 0;
         bool ok = true;
-        for (int it = 0; ok; ++it) {
-            const int k = unit_of(it, n_units);
-            if (k < 0) break;
-            const UnitInfo w = unit_info(p, k);
+        // the next unit (from round `from` on) in which this group's query tile exists; it < 0: none
+        auto find_unit = [&](int from, int& it, UnitInfo& w) {
+            for (it = from;; ++it) {
+                const int k = unit_of(it, n_units);
+                if (k < 0) { it = -1; return; }
+                w = unit_info(p, k);
+                if (w.n_t[u] > 0) return;
+            }
+        };
+        // RoPE on this thread's row of the TMA-loaded Q tile, in place (128-byte-swizzled, K-major)
+        auto rotate_q = [&](const UnitInfo& w) -> bool {
+            const int buf = q_use & 1;
+            const uint32_t par = (q_use >> 1) & 1;
+            ++q_use;
+            const int gi = (2 * w.qp + u) * PF_BM + row;
+            const float4* tab = reinterpret_cast<const float4*>(p.table + (size_t)min(gi, p.S - 1) * (PF_D / 2));
+            float4 cs[16];
+#pragma unroll
+            for (int c = 0; c < 16; ++c) cs[c] = __ldg(tab + c);
+            if (!mbar_wait(smem_u32(&bar_qfull[buf][u]), par, &s_abort)) return false;
+            const uint32_t qrow = sQ + (buf * 2 + u) * PF_TILE_BYTES + row * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const uint32_t addr = qrow + ((c ^ (row & 7)) << 4);
+                uint32_t w4[4];
+                asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(w4[0]), "=r"(w4[1]), "=r"(w4[2]), "=r"(w4[3]) : "r"(addr));
+#pragma unroll
+                for (int e = 0; e < 4; e += 2) {
+                    const float4 t4 = cs[c * 2 + e / 2];   // (cos, sin) of pairs 4c+e, 4c+e+1
+                    float x0 = bf16_lo(w4[e]), x1 = bf16_hi(w4[e]);
+                    w4[e] = pack_bf16(x0 * t4.x - x1 * t4.y, x0 * t4.y + x1 * t4.x);
+                    x0 = bf16_lo(w4[e + 1]); x1 = bf16_hi(w4[e + 1]);
+                    w4[e + 1] = pack_bf16(x0 * t4.z - x1 * t4.w, x0 * t4.w + x1 * t4.z);
+                }
+                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(w4[0]), "r"(w4[1]), "r"(w4[2]),
+                             "r"(w4[3]) : "memory");
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_qrot[buf][u]));
+            return true;
+        };
+        int it;
+        UnitInfo w;
+        find_unit(0, it, w);
+        if (it >= 0) ok = rotate_q(w);
+        while (ok && it >= 0) {
             const int nt = w.n_t[u];
-            if (nt == 0) continue;
             const int b = w.b, h = w.h;
             const int i0 = (2 * w.qp + u) * PF_BM;
             const int gi = i0 + row;
-
-            // prologue: rotate the TMA-loaded Q row in place (128-byte-swizzled, K-major)
-            {
-                const int buf = q_use & 1;
-                const uint32_t par = (q_use >> 1) & 1;
-                ++q_use;
-                const float4* tab = reinterpret_cast<const float4*>(p.table + (size_t)min(gi, p.S - 1) * (PF_D / 2));
-                float4 cs[16];
-#pragma unroll
-                for (int c = 0; c < 16; ++c) cs[c] = __ldg(tab + c);
-                ok = mbar_wait(smem_u32(&bar_qfull[buf][u]), par, &s_abort);
-                if (!ok) break;
-                const uint32_t qrow = sQ + (buf * 2 + u) * PF_TILE_BYTES + row * 128;
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const uint32_t addr = qrow + ((c ^ (row & 7)) << 4);
-                    uint32_t w4[4];
-                    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
-                                 : "=r"(w4[0]), "=r"(w4[1]), "=r"(w4[2]), "=r"(w4[3]) : "r"(addr));
-#pragma unroll
-                    for (int e = 0; e < 4; e += 2) {
-                        const float4 t4 = cs[c * 2 + e / 2];   // (cos, sin) of pairs 4c+e, 4c+e+1
-                        float x0 = bf16_lo(w4[e]), x1 = bf16_hi(w4[e]);
-                        w4[e] = pack_bf16(x0 * t4.x - x1 * t4.y, x0 * t4.y + x1 * t4.x);
-                        x0 = bf16_lo(w4[e + 1]); x1 = bf16_hi(w4[e + 1]);
-                        w4[e + 1] = pack_bf16(x0 * t4.z - x1 * t4.w, x0 * t4.w + x1 * t4.z);
-                    }
-                    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(w4[0]), "r"(w4[1]), "r"(w4[2]),
-                                 "r"(w4[3]) : "memory");
-                }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bar_qrot[buf][u]));
-            }
 
             float m_ref = 0.f;         // exponent reference, raw score units
             float l_run = 0.f;
@@ -790,6 +806,16 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             if (!ok) break;
             tiles_done += nt;
 
+            // The next unit's Q tile is rotated BEFORE this unit's epilogue: the MMA warp needs it to start the
+            // next unit, while the epilogue has to wait for the last P V anyway.
+            int it_next;
+            UnitInfo w_next;
+            find_unit(it + 1, it_next, w_next);
+            if (it_next >= 0) {
+                ok = rotate_q(w_next);
+                if (!ok) break;
+            }
+
             // epilogue: O / l -> bf16 -> global
             ok = mbar_wait(smem_u32(&bar_o[u]), units_done & 1, &s_abort);
             ++units_done;
@@ -826,6 +852,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                     p.lse[((size_t)b * p.Hq + h) * p.S + gi] =
                         l_run > 0.f ? (m_ref * p.scale_log2 + log2f(l_run)) * PF_LN2 : -INFINITY;
             }
+            it = it_next;
+            w = w_next;
         }
     }
 
@@ -932,7 +960,11 @@ extern "C" int bn_attn_prefill_bf16(const void* q, const void* k, const void* v,
     if (flags & BN_PREFILL_SINGLE_TILE_KERNEL) {
         prefill_kernel_v1<<<(unsigned)(n_qtiles * B * Hq), PF_THREADS, PF_SMEM_BYTES, st>>>(tmap_k, tmap_v, p);
     } else {
-        const long long n_units = (n_qtiles + 1) / 2 * B * Hq;
+        const long long n_units = (long long)(n_qtiles + 1) / 2 * B * Hq;
+        if (n_units >= (1ll << 22)) return fail(BN_ERR_UNSUPPORTED, "bn_attn_prefill_bf16: more than 2^22 work units");
+        p.inv_bh = 1.0f / (float)(B * Hq);
+        p.inv_hq = 1.0f / (float)Hq;
+        p.inv_n_rep = 1.0f / (float)p.n_rep;
         int sms = 0;
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         const unsigned grid = (unsigned)(n_units < sms ? n_units : sms);

@@ -67,6 +67,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Non-blocking test (try_wait may suspend the thread for a while before it answers; this one never does): for
+// a thread that polls several barriers in turn.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // Wait for the phase with the given parity to complete.  The wait is bounded:
 // after `limit_ns` of wall time, or as soon as *abort_flag (shared memory) is
 // non-zero, it gives up, raises *abort_flag and returns false, so that every

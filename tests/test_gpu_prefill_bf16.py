@@ -64,6 +64,20 @@ def test_prefill_non_causal(lib, S, single):
     assert np.abs(got[0].reshape(S, Hq * D) - ref).max() <= GATE
 
 
+@pytest.mark.parametrize("Hq,Hkv", [(4, 4), (3, 1), (6, 2), (2, 1)])
+@pytest.mark.parametrize("S", [130, 513])
+def test_prefill_group_sizes(lib, Hq, Hkv, S):
+    """Odd group sizes (incl. one query head per KV head) make the persistent kernel pair two consecutive row
+    tiles of one head, even ones two heads of a group on the same rows: both pairings against the oracle."""
+    B, D = 2, 64
+    q, k, v = make_inputs(B, S, Hq, Hkv, D, 31 * S + Hq)
+    got, lse = run(q, k, v, 3, True, want_lse=True)
+    for b in range(B):
+        ref, ref_lse = oracle(q, k, v, 3, True, b)
+        assert np.abs(got[b].reshape(S, Hq * D) - ref).max() <= GATE
+        assert np.abs(lse[b].T - ref_lse).max() <= 2e-2
+
+
 def test_prefill_growing_scores_take_the_rescale_path(lib):
     """Keys whose scores grow along the sequence force the running reference to move by more than 2^8
     several times (the rescale-and-redo path of the single-pass softmax)."""
