@@ -404,6 +404,13 @@ prefill_kernel_v1(const __grid_constant__ CUtensorMap tmap_k, const __grid_const
 // the tensor pipe, is the first limit; moving a share of the exponentials to the
 // FMA pipe (Cody-Waite split + cubic) was measured and did not pay, because a
 // softmax group that runs alone is bound by instruction latency, not by MUFU.
+// Optional event log for performance work (compiled out unless built with -DBN_TIMELINE): the warps of CTA 0
+// append (clock64, code) pairs to the caller's lse buffer, 2048 entries per warp, INSTEAD of the log-sum-exp.
+#ifdef BN_TIMELINE
+#define BN_LOG(code) do { if (blockIdx.x == 0 && p.lse && log_n < 2048) { long long* L_ = reinterpret_cast<long long*>(p.lse) + ((size_t)(threadIdx.x / 32) * 2048 + log_n) * 2; L_[0] = clock64(); L_[1] = (long long)(code); ++log_n; } } while (0)
+#else
+#define BN_LOG(code) do {} while (0)
+#endif
 constexpr int P2_THREADS = 320;
 constexpr int P2_NSTAGE = 4;
 constexpr int P2_SMEM_BYTES = 1024 + PF_TILE_BYTES * (4 + 2 * P2_NSTAGE);
@@ -481,6 +488,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     __shared__ int s_abort;
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+#ifdef BN_TIMELINE
+    int log_n = 0;
+#endif
     const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sQ = smem0;                                        // [buffer][tile] = 4 tiles
     const uint32_t sK = smem0 + PF_TILE_BYTES * 4;                    // P2_NSTAGE tiles
@@ -590,8 +600,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             };
             if (w.n_max > 0) ok = mbar_wait(smem_u32(&bar_kfull[stage]), phase, &s_abort);
             if (!ok) break;
+            if (elect_one()) BN_LOG(20);
             if (w.n_t[0] > 0) issue_qk(0, stage, 0);
             if (w.n_t[1] > 0) issue_qk(1, stage, 0);
+            if (elect_one()) BN_LOG(21);
             for (int j = 0; ok && j < w.n_max; ++j) {
                 const int nstage = (stage + 1 == P2_NSTAGE) ? 0 : stage + 1;
                 const uint32_t nphase = (stage + 1 == P2_NSTAGE) ? phase ^ 1u : phase;
@@ -601,6 +613,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                     if (j >= w.n_t[u]) continue;
                     ok = mbar_wait(smem_u32(&bar_p[u]), (tiles_done[u] + j) & 1, &s_abort);
                     if (!ok) break;
+                    if (elect_one()) BN_LOG(24 | u << 8 | j << 16);
                     // S_u(j+1) = Q_u K(j+1)^T first: its S columns are free because P_u(j) has been written, and
                     // the softmax of tile j+1 can start while P_u(j) V(j) still runs
                     if (j + 1 < w.n_t[u]) {
@@ -625,6 +638,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                         if (j == w.n_t[u] - 1) tc::commit(smem_u32(&bar_o[u]));
                         const bool last_user = (u == 1) || (j >= w.n_t[1]);
                         if (last_user) tc::commit(smem_u32(&bar_empty[stage]));   // K(j)/V(j) may be overwritten
+                        BN_LOG(25 | u << 8 | j << 16);
                     }
                     __syncwarp();
                 }
@@ -656,34 +670,34 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 if (w.n_t[u] > 0) return;
             }
         };
-        // RoPE on this thread's row of the TMA-loaded Q tile, in place (128-byte-swizzled, K-major)
+        // RoPE on the TMA-loaded Q tile, in place (128-byte-swizzled, K-major).  Each warp rotates the 32 rows of
+        // its TMEM lane quarter, a row at a time with lane = rotation pair: the row of the cos/sin table is one
+        // coalesced 256-byte load and the lanes touch the 32 banks of the row's 128 bytes.
         auto rotate_q = [&](const UnitInfo& w) -> bool {
             const int buf = q_use & 1;
             const uint32_t par = (q_use >> 1) & 1;
             ++q_use;
-            const int gi = (2 * w.qp + u) * PF_BM + row;
-            const float4* tab = reinterpret_cast<const float4*>(p.table + (size_t)min(gi, p.S - 1) * (PF_D / 2));
-            float4 cs[16];
+            const int r_first = (warp % 4) * 32;
+            const int gi_first = (2 * w.qp + u) * PF_BM + r_first;
+            float2 cs[32];
 #pragma unroll
-            for (int c = 0; c < 16; ++c) cs[c] = __ldg(tab + c);
+            for (int r = 0; r < 32; ++r) cs[r] = __ldg(p.table + (size_t)min(gi_first + r, p.S - 1) * (PF_D / 2) + lane);
             if (!mbar_wait(smem_u32(&bar_qfull[buf][u]), par, &s_abort)) return false;
-            const uint32_t qrow = sQ + (buf * 2 + u) * PF_TILE_BYTES + row * 128;
+            const uint32_t tile = sQ + (buf * 2 + u) * PF_TILE_BYTES + r_first * 128 + (lane & 3) * 4;
+            const uint32_t chunk = (uint32_t)lane >> 2;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const uint32_t addr = qrow + ((c ^ (row & 7)) << 4);
-                uint32_t w4[4];
-                asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(w4[0]), "=r"(w4[1]), "=r"(w4[2]), "=r"(w4[3]) : "r"(addr));
+            for (int r0 = 0; r0 < 32; r0 += 8) {
+                uint32_t x[8];
 #pragma unroll
-                for (int e = 0; e < 4; e += 2) {
-                    const float4 t4 = cs[c * 2 + e / 2];   // (cos, sin) of pairs 4c+e, 4c+e+1
-                    float x0 = bf16_lo(w4[e]), x1 = bf16_hi(w4[e]);
-                    w4[e] = pack_bf16(x0 * t4.x - x1 * t4.y, x0 * t4.y + x1 * t4.x);
-                    x0 = bf16_lo(w4[e + 1]); x1 = bf16_hi(w4[e + 1]);
-                    w4[e + 1] = pack_bf16(x0 * t4.z - x1 * t4.w, x0 * t4.w + x1 * t4.z);
+                for (int r = 0; r < 8; ++r)       // row r_first + r0 + r: its low three bits are r
+                    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(x[r]) : "r"(tile + (r0 + r) * 128 + ((chunk ^ r) << 4)));
+#pragma unroll
+                for (int r = 0; r < 8; ++r) {
+                    const float2 t2 = cs[r0 + r];
+                    const float x0 = bf16_lo(x[r]), x1 = bf16_hi(x[r]);
+                    const uint32_t y = pack_bf16(x0 * t2.x - x1 * t2.y, x0 * t2.y + x1 * t2.x);
+                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(tile + (r0 + r) * 128 + ((chunk ^ r) << 4)), "r"(y) : "memory");
                 }
-                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(w4[0]), "r"(w4[1]), "r"(w4[2]),
-                             "r"(w4[3]) : "memory");
             }
             fence_proxy_async_smem();
             __syncwarp();
@@ -708,6 +722,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             for (int j = 0; j < nt; ++j) {
                 ok = mbar_wait(smem_u32(&bar_s[u]), (tiles_done + j) & 1, &s_abort);
                 if (!ok) break;
+                if (lane == 0) BN_LOG(2 | u << 8 | j << 16);
                 tc::fence_after_sync();
                 const int j0 = j * PF_BN;
                 const bool need_mask = (j0 + PF_BN - 1) > tile_free_last;
@@ -802,6 +817,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 tc::fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bar_p[u]));
+                if (lane == 0) BN_LOG(6 | u << 8 | j << 16);
             }
             if (!ok) break;
             tiles_done += nt;
@@ -811,15 +827,18 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             int it_next;
             UnitInfo w_next;
             find_unit(it + 1, it_next, w_next);
+            if (lane == 0) BN_LOG(7 | u << 8);
             if (it_next >= 0) {
                 ok = rotate_q(w_next);
                 if (!ok) break;
             }
+            if (lane == 0) BN_LOG(8 | u << 8);
 
             // epilogue: O / l -> bf16 -> global
             ok = mbar_wait(smem_u32(&bar_o[u]), units_done & 1, &s_abort);
             ++units_done;
             if (!ok) break;
+            if (lane == 0) BN_LOG(9 | u << 8);
             tc::fence_after_sync();
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             __nv_bfloat16* dst = p.out + (((size_t)b * p.S + gi) * p.Hq + h) * PF_D;
@@ -848,10 +867,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                     o4.w = pack_bf16(__uint_as_float(r1[v * 8 + 6]) * inv, __uint_as_float(r1[v * 8 + 7]) * inv);
                     *reinterpret_cast<uint4*>(dst + 32 + v * 8) = o4;
                 }
+#ifndef BN_TIMELINE
                 if (p.lse)
                     p.lse[((size_t)b * p.Hq + h) * p.S + gi] =
                         l_run > 0.f ? (m_ref * p.scale_log2 + log2f(l_run)) * PF_LN2 : -INFINITY;
+#endif
             }
+            if (lane == 0) BN_LOG(10 | u << 8);
             it = it_next;
             w = w_next;
         }
