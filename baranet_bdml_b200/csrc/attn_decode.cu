@@ -197,6 +197,10 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
         fence_mbar_init();
         prefetch_tensormap(&tmap);
     }
+    // Everything above touches no global memory, so with a programmatic dependent launch it overlaps the tail of
+    // the previous kernel of the stream; nothing below runs before that kernel's writes are visible.
+    grid_dependency_wait();
+    grid_launch_dependents();
     // stages per sequence, then an exclusive prefix sum (warp 0)
     for (int b = tid; b < p.B; b += DEC_THREADS) {
         const int L = max(0, min(p.seq_lens[b], p.max_seq_len));
@@ -250,6 +254,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
             const int n_pages_seq = (sgm.L + BN_PAGE_TOKENS - 1) / BN_PAGE_TOKENS;
             return e < n_pages_seq ? p.page_table[(size_t)sgm.b * p.max_pages + e] : -1;
         };
+        const uint64_t stream_policy = l2_policy_evict_first();     // every cache byte is read once per launch
         int ids = have ? load_group(sg, sg.s0 / GRP) : -1, ids_pref = -1;
         while (ok && have) {
             const bool have_next = iter.next(sc, sg_next);
@@ -268,8 +273,8 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
                 if (lane == 0) mbar_arrive_expect_tx(fb, (uint32_t)npages * DEC_BOX_BYTES);
                 __syncwarp();
                 if (lane < npages && page >= 0)
-                    tma_load_2d(ring + stage * DEC_STAGE_BYTES + lane * DEC_BOX_BYTES, &tmap, 0,
-                                (page * p.Hkv + sg.g) * DEC_BOX_ROWS, fb);
+                    tma_load_2d_hint(ring + stage * DEC_STAGE_BYTES + lane * DEC_BOX_BYTES, &tmap, 0,
+                                     (page * p.Hkv + sg.g) * DEC_BOX_ROWS, fb, stream_policy);
                 if (++stage == DEC_NSTAGES) { stage = 0; phase ^= 1u; }
             }
             sg = sg_next;
@@ -302,22 +307,43 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
             const size_t base = (size_t)bgi * p.max_parts;
             // lane -> head lane / 4, dims 16 * (lane % 4) .. + 15
             const int ch = lane / 4, cd = (lane % 4) * 16;
-            float m2 = -INFINITY;
-            for (int c = 0; c < sg.n_parts; ++c) m2 = fmaxf(m2, __ldcg(p.part_m + (base + c) * DEC_G + ch));
-            const float ms2 = m2 == -INFINITY ? 0.f : m2;
-            float l2 = 0.f, a2[16];
+            // parts are merged four at a time: all their loads are issued before the first use, so a merge of up
+            // to four parts costs one L2 round trip, not one per part
+            float m2 = -INFINITY, l2 = 0.f, a2[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) a2[i] = 0.f;
-            for (int c = 0; c < sg.n_parts; ++c) {
-                const float scl = ex2(__ldcg(p.part_m + (base + c) * DEC_G + ch) - ms2);
-                l2 += __ldcg(p.part_l + (base + c) * DEC_G + ch) * scl;
-                const float4* po = reinterpret_cast<const float4*>(p.part_o + ((base + c) * DEC_G + ch) * DEC_D + cd);
+            for (int c0 = 0; c0 < sg.n_parts; c0 += 4) {
+                float pm[4], pl[4];
+                float4 po[4][4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const float4 v4 = __ldcg(po + i);
-                    a2[4 * i] += v4.x * scl; a2[4 * i + 1] += v4.y * scl;
-                    a2[4 * i + 2] += v4.z * scl; a2[4 * i + 3] += v4.w * scl;
+                    const bool on = c0 + i < sg.n_parts;
+                    const size_t e = (base + (on ? c0 + i : 0)) * DEC_G + ch;
+                    pm[i] = on ? __ldcg(p.part_m + e) : -INFINITY;
+                    pl[i] = on ? __ldcg(p.part_l + e) : 0.f;
+                    const float4* src = reinterpret_cast<const float4*>(p.part_o + e * DEC_D + cd);
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) po[i][v] = on ? __ldcg(src + v) : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
+                float mnew = m2;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) mnew = fmaxf(mnew, pm[i]);
+                const float ms2 = mnew == -INFINITY ? 0.f : mnew;
+                const float keep = ex2(m2 - ms2);          // 0 while nothing has been merged yet (m2 = -inf)
+                l2 *= keep;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) a2[i] *= keep;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float scl = ex2(pm[i] - ms2);
+                    l2 += pl[i] * scl;
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        a2[4 * v] += po[i][v].x * scl; a2[4 * v + 1] += po[i][v].y * scl;
+                        a2[4 * v + 2] += po[i][v].z * scl; a2[4 * v + 3] += po[i][v].w * scl;
+                    }
+                }
+                m2 = mnew;
             }
             if (lane == 0) p.tickets[bgi] = 0;   // leave the scratch clean for the next launch
             if (ch < p.n_rep) {
@@ -692,7 +718,23 @@ static int decode_launch(const void* q, const void* pool, int64_t pool_pages, co
     // no more CTAs than ranges of the minimum length can exist
     const long long max_ranges = (long long)B * Hkv * ((max_seq_len + min_tokens - 1) / min_tokens + 1);
     const int grid = (int)(max_ranges < sms ? (max_ranges > 0 ? max_ranges : 1) : sms);
-    decode_paged_kernel<<<grid, DEC_THREADS, DEC_SMEM_BYTES, as_stream(stream)>>>(tmap, p);
+    // Programmatic dependent launch: the kernel's set-up (barriers, tensor-map fetch) may overlap the tail of the
+    // previous kernel of the stream; the kernel itself waits for that kernel's completion before it reads or
+    // writes global memory.  If the attribute is refused, fall back to an ordinary launch.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(DEC_THREADS);
+    cfg.dynamicSmemBytes = DEC_SMEM_BYTES;
+    cfg.stream = as_stream(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, decode_paged_kernel, tmap, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        decode_paged_kernel<<<grid, DEC_THREADS, DEC_SMEM_BYTES, as_stream(stream)>>>(tmap, p);
+    }
     return launch_status("bn_attn_decode_paged");
 }
 

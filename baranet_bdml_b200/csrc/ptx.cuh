@@ -116,6 +116,30 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
         : "memory");
 }
 
+// L2 eviction policy for data that is read exactly once: it leaves the cache first, so small tables that every
+// launch re-reads (page tables, lengths, queries) stay resident while the big stream passes through
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t smem_dst, const CUtensorMap* m, int x, int y, uint32_t bar,
+                                                 uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%2, %3}], [%4], %5;"
+        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(bar), "l"(policy)
+        : "memory");
+}
+
+// Programmatic dependent launch: `grid_dependency_wait` returns once every kernel this launch depends on has
+// completed and its writes are visible (a no-op for an ordinary launch); `grid_launch_dependents` lets the next
+// kernel of the stream, if it was launched with the programmatic-serialization attribute, start its own
+// prologue as soon as this grid's blocks make room.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const CUtensorMap* m, int c0, int c1, int c2, int c3,
                                             uint32_t bar) {
     asm volatile(
