@@ -74,6 +74,18 @@ rope_k_kernel(const __nv_bfloat16* __restrict__ k, __nv_bfloat16* __restrict__ k
     __shared__ float2 cs[RK_POS][PF_D / 2];
     const int s0 = blockIdx.x * RK_POS, b = blockIdx.y;
     if (blockIdx.x == 0 && b == 0 && threadIdx.x == 0) *error_word = 0;
+    // 16-byte pieces (4 rotation pairs) of this block's positions: issue the loads before the cos/sin work
+    const int chunks_per_pos = Hkv * (PF_D / 8);
+    const int n_chunks = min(RK_POS, S - s0) * chunks_per_pos;
+    const uint4* src = reinterpret_cast<const uint4*>(k + ((size_t)b * S + s0) * Hkv * PF_D);
+    uint4* dst = reinterpret_cast<uint4*>(krot + ((size_t)b * S + s0) * Hkv * PF_D);
+    constexpr int RK_UNROLL = 2;
+    uint4 raw[RK_UNROLL];
+#pragma unroll
+    for (int i = 0; i < RK_UNROLL; ++i) {
+        const int e = threadIdx.x + i * 256;
+        raw[i] = e < n_chunks ? __ldg(src + e) : make_uint4(0, 0, 0, 0);
+    }
     {
         const int ds = threadIdx.x / (PF_D / 2), i = threadIdx.x % (PF_D / 2);
         const float freq = rope_inv_freq(i, PF_D, theta);
@@ -83,18 +95,23 @@ rope_k_kernel(const __nv_bfloat16* __restrict__ k, __nv_bfloat16* __restrict__ k
         if (b == 0 && s0 + ds < S) table[(size_t)(s0 + ds) * (PF_D / 2) + i] = v;
     }
     __syncthreads();
-    const int pairs = Hkv * (PF_D / 2);
-    for (int e = threadIdx.x; e < RK_POS * pairs; e += blockDim.x) {
-        const int ds = e / pairs, r = e % pairs, i = r % (PF_D / 2);
-        if (s0 + ds >= S) break;
-        const float2 v = cs[ds][i];
-        const size_t idx = ((size_t)b * S + s0 + ds) * Hkv * PF_D + 2 * r;
-        const uint32_t raw = *reinterpret_cast<const uint32_t*>(k + idx);
-        const float x0 = bf16_lo(raw), x1 = bf16_hi(raw);
-        const float y0 = x0 * v.x - x1 * v.y;
-        const float y1 = x0 * v.y + x1 * v.x;
-        *reinterpret_cast<uint32_t*>(krot + idx) = pack_bf16(y0, y1);
+    auto rotate = [&](uint4 x, int e) {
+        const int ds = e / chunks_per_pos, c = e % (PF_D / 8);     // position, and which 4 pairs of the head
+        uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const float2 v = cs[ds][c * 4 + t];
+            const float x0 = bf16_lo(w[t]), x1 = bf16_hi(w[t]);
+            w[t] = pack_bf16(x0 * v.x - x1 * v.y, x0 * v.y + x1 * v.x);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    };
+#pragma unroll
+    for (int i = 0; i < RK_UNROLL; ++i) {
+        const int e = threadIdx.x + i * 256;
+        if (e < n_chunks) dst[e] = rotate(raw[i], e);
     }
+    for (int e = threadIdx.x + RK_UNROLL * 256; e < n_chunks; e += 256) dst[e] = rotate(__ldg(src + e), e);
 }
 
 // ---------------------------------------------------------------------------
