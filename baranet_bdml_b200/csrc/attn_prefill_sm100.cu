@@ -428,7 +428,7 @@ prefill_kernel_v1(const __grid_constant__ CUtensorMap tmap_k, const __grid_const
 #else
 #define BN_LOG(code) do {} while (0)
 #endif
-constexpr int P2_THREADS = 320;
+constexpr int P2_THREADS = 576;
 constexpr int P2_NSTAGE = 4;
 constexpr int P2_SMEM_BYTES = 1024 + PF_TILE_BYTES * (4 + 2 * P2_NSTAGE);
 constexpr uint32_t P2_TMEM_COLS = 512;
@@ -441,6 +441,26 @@ __device__ __forceinline__ void softmax_chunk(uint32_t (&r)[32], uint32_t (&pk)[
                                               uint64_t& sum2) {
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
+        float x0, x1;
+        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), scale2, mneg2), x0, x1);
+        float p0 = ex2(x0), p1 = ex2(x1);
+        if (MASK) {
+            if (first_key + i > row_last) p0 = 0.f;
+            if (first_key + i + 1 > row_last) p1 = 0.f;
+        }
+        sum2 = add_f32x2(sum2, pack_f32x2(p0, p1));
+        pk[i / 2] = pack_bf16(p0, p1);
+        asm("max.bf16x2 %0, %0, %1;" : "+r"(pmax) : "r"(pk[i / 2]));
+    }
+}
+
+// 16-score form of the same, for the kernel whose softmax threads each own half a row
+template <bool MASK>
+__device__ __forceinline__ void softmax_chunk16(uint32_t (&r)[16], uint32_t (&pk)[8], uint64_t scale2,
+                                                uint64_t mneg2, int first_key, int row_last, uint32_t& pmax,
+                                                uint64_t& sum2) {
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) {
         float x0, x1;
         unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), scale2, mneg2), x0, x1);
         float p0 = ex2(x0), p1 = ex2(x1);
@@ -503,6 +523,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     __shared__ __align__(8) uint64_t bar_kfull[P2_NSTAGE], bar_vfull[P2_NSTAGE], bar_empty[P2_NSTAGE];
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
+    __shared__ float s_xchg[2][2][PF_BM];      // [tile][column half][row]: exchange between the two threads of a row
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
 #ifdef BN_TIMELINE
@@ -517,11 +538,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         for (int i = 0; i < 2; ++i) {
             for (int u = 0; u < 2; ++u) {
                 mbar_init(smem_u32(&bar_qfull[i][u]), 1);
-                mbar_init(smem_u32(&bar_qrot[i][u]), 4);
+                mbar_init(smem_u32(&bar_qrot[i][u]), 8);
                 mbar_init(smem_u32(&bar_qfree[i][u]), 1);
             }
             mbar_init(smem_u32(&bar_s[i]), 1);
-            mbar_init(smem_u32(&bar_p[i]), 4);
+            mbar_init(smem_u32(&bar_p[i]), 8);
             mbar_init(smem_u32(&bar_o[i]), 1);
             mbar_init(smem_u32(&bar_pv[i]), 1);
         }
@@ -533,7 +554,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         s_abort = 0;
         fence_mbar_init();
     }
-    if (warp == 8) {
+    if (warp == 16) {
         tc::tmem_alloc(smem_u32(&s_tmem_base), P2_TMEM_COLS);
         tc::tmem_relinquish();
     }
@@ -542,7 +563,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     tc::fence_after_sync();
     const uint32_t tmem = s_tmem_base;
 
-    if (warp == 9) {
+    if (warp == 17) {
         // ---------------------------------------------------------- TMA producer
         if (lane == 0) {
             prefetch_tensormap(&tmap_q);
@@ -578,7 +599,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 }
             }
         }
-    } else if (warp == 8) {
+    } else if (warp == 16) {
         // ------------------------------------------------------------ MMA issuer
         constexpr uint32_t IDESC_QK = tc::idesc_bf16(PF_BM, PF_BN, 0);
         constexpr uint32_t IDESC_PV = tc::idesc_bf16(PF_BM, PF_D, 1);
@@ -668,13 +689,19 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             units_done[1] += w.n_t[1] > 0;
         }
     } else {
-        // ------------------------------------------- softmax groups (warps 0..7)
-        const int u = warp / 4;                     // which query tile of the pair
-        const int row = tid % 128;                  // TMEM lane = query row inside the tile
+        // ------------------------------------------ softmax groups (warps 0..15)
+        // Eight warps per query tile: TWO threads per query row, each owning 64 of a step's 128 keys (and 32 of the
+        // 64 output columns).  Four softmax warps per scheduler instead of two hide the latencies of TMEM loads,
+        // barrier waits and the exponential's result.  The two threads of a row share the exponent reference;
+        // their only per-step exchange is one named barrier that ORs the "probability left the safe range" flag.
+        const int u = warp / 8;                     // which query tile of the pair
+        const int hf = (warp / 4) % 2;              // which half of the keys of a step (and of the O columns)
+        const int row = (warp % 4) * 32 + lane;     // TMEM lane = query row inside the tile
+        const int pair_bar = 1 + u * 4 + (warp % 4);   // named barrier of the two warps that share these 32 rows
         const uint32_t lane_base = ((uint32_t)((warp % 4) * 32)) << 16;
-        const uint32_t tS = tmem + lane_base + u * 128;
-        const uint32_t tO = tmem + lane_base + 256 + u * 64;
-        const uint32_t tP = tmem + lane_base + 384 + u * 64;
+        const uint32_t tS = tmem + lane_base + u * 128 + hf * 64;
+        const uint32_t tO = tmem + lane_base + 256 + u * 64 + hf * 32;
+        const uint32_t tP = tmem + lane_base + 384 + u * 64 + hf * 32;
         int q_use = 0;
         uint32_t tiles_done = 0, units_done = 0;
         bool ok = true;
@@ -687,23 +714,23 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 if (w.n_t[u] > 0) return;
             }
         };
-        // RoPE on the TMA-loaded Q tile, in place (128-byte-swizzled, K-major).  Each warp rotates the 32 rows of
-        // its TMEM lane quarter, a row at a time with lane = rotation pair: the row of the cos/sin table is one
+        // RoPE on the TMA-loaded Q tile, in place (128-byte-swizzled, K-major).  Each of the tile's eight warps
+        // rotates 16 rows, a row at a time with lane = rotation pair: the row of the cos/sin table is one
         // coalesced 256-byte load and the lanes touch the 32 banks of the row's 128 bytes.
         auto rotate_q = [&](const UnitInfo& w) -> bool {
             const int buf = q_use & 1;
             const uint32_t par = (q_use >> 1) & 1;
             ++q_use;
-            const int r_first = (warp % 4) * 32;
+            const int r_first = (warp % 8) * 16;
             const int gi_first = (2 * w.qp + u) * PF_BM + r_first;
-            float2 cs[32];
+            float2 cs[16];
 #pragma unroll
-            for (int r = 0; r < 32; ++r) cs[r] = __ldg(p.table + (size_t)min(gi_first + r, p.S - 1) * (PF_D / 2) + lane);
+            for (int r = 0; r < 16; ++r) cs[r] = __ldg(p.table + (size_t)min(gi_first + r, p.S - 1) * (PF_D / 2) + lane);
             if (!mbar_wait(smem_u32(&bar_qfull[buf][u]), par, &s_abort)) return false;
             const uint32_t tile = sQ + (buf * 2 + u) * PF_TILE_BYTES + r_first * 128 + (lane & 3) * 4;
             const uint32_t chunk = (uint32_t)lane >> 2;
 #pragma unroll
-            for (int r0 = 0; r0 < 32; r0 += 8) {
+            for (int r0 = 0; r0 < 16; r0 += 8) {
                 uint32_t x[8];
 #pragma unroll
                 for (int r = 0; r < 8; ++r)       // row r_first + r0 + r: its low three bits are r
@@ -731,65 +758,50 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             const int i0 = (2 * w.qp + u) * PF_BM;
             const int gi = i0 + row;
 
-            float m_ref = 0.f;         // exponent reference, raw score units
-            float l_run = 0.f;
+            float m_ref = 0.f;         // exponent reference, raw score units (the same in both threads of a row)
+            float l_run = 0.f;         // this thread's half of the row sum
             const int row_last = p.causal ? min(p.S - 1, gi + p.position_offset) : p.S - 1;
             const int tile_free_last = p.causal ? min(p.S - 1, i0 + p.position_offset) : p.S - 1;   // no mask needed up to here
 
             for (int j = 0; j < nt; ++j) {
                 ok = mbar_wait(smem_u32(&bar_s[u]), (tiles_done + j) & 1, &s_abort);
                 if (!ok) break;
-                if (lane == 0) BN_LOG(2 | u << 8 | j << 16);
                 tc::fence_after_sync();
-                const int j0 = j * PF_BN;
-                const bool need_mask = (j0 + PF_BN - 1) > tile_free_last;
+                const int j0 = j * PF_BN + hf * 64;             // first key of this thread's 64 columns
+                const bool need_mask = (j0 + 63) > tile_free_last;
 
-                // row maximum of this tile (raw score units), by re-reading S: first tile and the rare redo only
-                auto tile_max = [&]() {
-                    float tmax = -INFINITY;
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t r[32];
-                        tc::ld32(tS + c * 32, r);
-                        tc::wait_ld(r);
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (!need_mask || j0 + c * 32 + i <= row_last) tmax = fmaxf(tmax, __uint_as_float(r[i]));
-                    }
-                    return tmax;
-                };
-                // one pass over the tile: P = exp2(S * scale_log2 - m_ref * scale_log2) -> TMEM, with the load of the
-                // next 32 columns in flight while the current 32 are processed
-                auto tile_pass = [&](float mneg, uint32_t& pmax, bool first_store_needs_pv) {
+                // one pass over this thread's 64 columns: P = exp2(S * scale_log2 - m_ref * scale_log2) -> TMEM, with
+                // the load of the next 16 columns in flight while the current 16 are processed
+                auto half_pass = [&](float mneg, uint32_t& pmax, bool first_store_needs_pv) {
                     uint64_t sum2 = 0;   // (0.f, 0.f)
                     const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2), mneg2 = pack_f32x2(mneg, mneg);
-                    uint32_t r0[32], r1[32], pk[16];
-                    tc::ld32(tS + 0, r0);
+                    uint32_t r0[16], r1[16], pk[8];
+                    auto chunk = [&](uint32_t (&r)[16], int c) {
+                        if (need_mask) softmax_chunk16<true>(r, pk, scale2, mneg2, j0 + c * 16, row_last, pmax, sum2);
+                        else softmax_chunk16<false>(r, pk, scale2, mneg2, j0 + c * 16, row_last, pmax, sum2);
+                    };
+                    tc::ld16(tS + 0, r0);
                     tc::wait_ld(r0);
-                    tc::ld32(tS + 32, r1);
-                    if (need_mask) softmax_chunk<true>(r0, pk, scale2, mneg2, j0, row_last, pmax, sum2);
-                    else softmax_chunk<false>(r0, pk, scale2, mneg2, j0, row_last, pmax, sum2);
+                    tc::ld16(tS + 16, r1);
+                    chunk(r0, 0);
                     // P(j-1) is still being read by its P V until bar_pv says otherwise
                     bool good = true;
                     if (first_store_needs_pv) {
                         good = mbar_wait(smem_u32(&bar_pv[u]), (tiles_done + j - 1) & 1, &s_abort);
                         tc::fence_after_sync();
                     }
-                    tc::st16(tP + 0, pk);
+                    tc::st8(tP + 0, pk);
                     tc::wait_ld(r1);
-                    tc::ld32(tS + 64, r0);
-                    if (need_mask) softmax_chunk<true>(r1, pk, scale2, mneg2, j0 + 32, row_last, pmax, sum2);
-                    else softmax_chunk<false>(r1, pk, scale2, mneg2, j0 + 32, row_last, pmax, sum2);
-                    tc::st16(tP + 16, pk);
+                    tc::ld16(tS + 32, r0);
+                    chunk(r1, 1);
+                    tc::st8(tP + 8, pk);
                     tc::wait_ld(r0);
-                    tc::ld32(tS + 96, r1);
-                    if (need_mask) softmax_chunk<true>(r0, pk, scale2, mneg2, j0 + 64, row_last, pmax, sum2);
-                    else softmax_chunk<false>(r0, pk, scale2, mneg2, j0 + 64, row_last, pmax, sum2);
-                    tc::st16(tP + 32, pk);
+                    tc::ld16(tS + 48, r1);
+                    chunk(r0, 2);
+                    tc::st8(tP + 16, pk);
                     tc::wait_ld(r1);
-                    if (need_mask) softmax_chunk<true>(r1, pk, scale2, mneg2, j0 + 96, row_last, pmax, sum2);
-                    else softmax_chunk<false>(r1, pk, scale2, mneg2, j0 + 96, row_last, pmax, sum2);
-                    tc::st16(tP + 48, pk);
+                    chunk(r1, 3);
+                    tc::st8(tP + 24, pk);
                     float s0, s1;
                     unpack_f32x2(sum2, s0, s1);
                     return good ? s0 + s1 : NAN;
@@ -798,43 +810,52 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 // The exponent reference starts at 0 and moves only when it has to: p = 2^(s*c - ref) may be
                 // anywhere in [2^-64, 2^64] without any loss (bf16 and fp32 keep their relative precision over
                 // that range), so for ordinary score magnitudes there is never a second pass or an O rescale.
-                if (j == 0) m_ref = 0.f;
                 uint32_t pmax = 0;           // bf16x2 (+0, +0)
-                float lsum = tile_pass(-m_ref * p.scale_log2, pmax, j > 0);
+                float lsum = half_pass(-m_ref * p.scale_log2, pmax, tiles_done + j > 0);
                 if (s_abort) { ok = false; break; }
                 // Did any p leave the safe range?  bf16 bit patterns are monotone for p >= 0.  Too large: > 2^64
-                // (incl. inf).  Too small matters on the first tile only, where key 0 is valid for every row: a
+                // (incl. inf).  Too small matters on the first 64 keys only, where key 0 is valid for every row: a
                 // largest p below 2^-64 means the whole row may have underflowed.
                 const uint32_t pm = max(pmax & 0xffffu, pmax >> 16);
-                const bool over = pm > 0x5F80u || (j == 0 && pm < 0x1F80u);
-                if (__any_sync(0xffffffffu, over)) {
-                    // rare: move the reference to the true row maximum, rescale O and l, redo the tile.
-                    const float tmax = tile_max();
-                    const float m_new = j == 0 ? tmax : fmaxf(m_ref, tmax);   // the first tile may also move it down
+                const bool over = pm > 0x5F80u || (j == 0 && hf == 0 && pm < 0x1F80u);
+                if (named_bar_or(pair_bar, 64, over)) {
+                    // rare, and taken by both warps of these rows together: move the reference to the true row
+                    // maximum, rescale O and l, redo the step.
+                    float hmax = -INFINITY;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t r[16];
+                        tc::ld16(tS + c * 16, r);
+                        tc::wait_ld(r);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            if (!need_mask || j0 + c * 16 + i <= row_last) hmax = fmaxf(hmax, __uint_as_float(r[i]));
+                    }
+                    s_xchg[u][hf][row] = hmax;
+                    named_bar_sync(pair_bar, 64);
+                    const float tmax = fmaxf(hmax, s_xchg[u][hf ^ 1][row]);
+                    const float m_new = j == 0 ? tmax : fmaxf(m_ref, tmax);   // the first step may also move it down
                     const float m_upd = m_new == -INFINITY ? m_ref : m_new;
                     if (j > 0) {
                         const float alpha = ex2((m_ref - m_upd) * p.scale_log2);
                         l_run *= alpha;
+                        uint32_t ro[32];           // this thread's 32 of the 64 O columns
+                        tc::ld32(tO, ro);
+                        tc::wait_ld(ro);
 #pragma unroll
-                        for (int c = 0; c < 2; ++c) {
-                            uint32_t ro[32];
-                            tc::ld32(tO + c * 32, ro);
-                            tc::wait_ld(ro);
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) ro[i] = __float_as_uint(__uint_as_float(ro[i]) * alpha);
-                            tc::st32(tO + c * 32, ro);
-                        }
+                        for (int i = 0; i < 32; ++i) ro[i] = __float_as_uint(__uint_as_float(ro[i]) * alpha);
+                        tc::st32(tO, ro);
                     }
                     m_ref = m_upd;
                     pmax = 0;
-                    lsum = tile_pass(-m_ref * p.scale_log2, pmax, false);
+                    lsum = half_pass(-m_ref * p.scale_log2, pmax, false);
+                    named_bar_sync(pair_bar, 64);      // the exchange slots may be written again
                 }
                 l_run += lsum;
                 tc::wait_st();
                 tc::fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bar_p[u]));
-                if (lane == 0) BN_LOG(6 | u << 8 | j << 16);
             }
             if (!ok) break;
             tiles_done += nt;
@@ -844,63 +865,53 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             int it_next;
             UnitInfo w_next;
             find_unit(it + 1, it_next, w_next);
-            if (lane == 0) BN_LOG(7 | u << 8);
             if (it_next >= 0) {
                 ok = rotate_q(w_next);
                 if (!ok) break;
             }
-            if (lane == 0) BN_LOG(8 | u << 8);
 
-            // epilogue: O / l -> bf16 -> global
+            // epilogue: O / l -> bf16 -> global; each thread of a row writes its 32 columns
             ok = mbar_wait(smem_u32(&bar_o[u]), units_done & 1, &s_abort);
             ++units_done;
             if (!ok) break;
-            if (lane == 0) BN_LOG(9 | u << 8);
             tc::fence_after_sync();
-            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            __nv_bfloat16* dst = p.out + (((size_t)b * p.S + gi) * p.Hq + h) * PF_D;
-            uint32_t r0[32], r1[32];
-            tc::ld32(tO, r0);
-            tc::ld32(tO + 32, r1);
-            tc::wait_ld(r0);
-            tc::wait_ld(r1);
+            s_xchg[u][hf][row] = l_run;
+            named_bar_sync(pair_bar, 64);
+            const float l_row = l_run + s_xchg[u][hf ^ 1][row];
+            const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+            __nv_bfloat16* dst = p.out + (((size_t)b * p.S + gi) * p.Hq + h) * PF_D + hf * 32;
+            uint32_t ro[32];
+            tc::ld32(tO, ro);
+            tc::wait_ld(ro);
             // the next unit's first P V overwrites O only after this group's next P arrive, which follows these loads
             if (gi < p.S) {
 #pragma unroll
                 for (int v = 0; v < 4; ++v) {
                     uint4 o4;
-                    o4.x = pack_bf16(__uint_as_float(r0[v * 8 + 0]) * inv, __uint_as_float(r0[v * 8 + 1]) * inv);
-                    o4.y = pack_bf16(__uint_as_float(r0[v * 8 + 2]) * inv, __uint_as_float(r0[v * 8 + 3]) * inv);
-                    o4.z = pack_bf16(__uint_as_float(r0[v * 8 + 4]) * inv, __uint_as_float(r0[v * 8 + 5]) * inv);
-                    o4.w = pack_bf16(__uint_as_float(r0[v * 8 + 6]) * inv, __uint_as_float(r0[v * 8 + 7]) * inv);
+                    o4.x = pack_bf16(__uint_as_float(ro[v * 8 + 0]) * inv, __uint_as_float(ro[v * 8 + 1]) * inv);
+                    o4.y = pack_bf16(__uint_as_float(ro[v * 8 + 2]) * inv, __uint_as_float(ro[v * 8 + 3]) * inv);
+                    o4.z = pack_bf16(__uint_as_float(ro[v * 8 + 4]) * inv, __uint_as_float(ro[v * 8 + 5]) * inv);
+                    o4.w = pack_bf16(__uint_as_float(ro[v * 8 + 6]) * inv, __uint_as_float(ro[v * 8 + 7]) * inv);
                     *reinterpret_cast<uint4*>(dst + v * 8) = o4;
                 }
-#pragma unroll
-                for (int v = 0; v < 4; ++v) {
-                    uint4 o4;
-                    o4.x = pack_bf16(__uint_as_float(r1[v * 8 + 0]) * inv, __uint_as_float(r1[v * 8 + 1]) * inv);
-                    o4.y = pack_bf16(__uint_as_float(r1[v * 8 + 2]) * inv, __uint_as_float(r1[v * 8 + 3]) * inv);
-                    o4.z = pack_bf16(__uint_as_float(r1[v * 8 + 4]) * inv, __uint_as_float(r1[v * 8 + 5]) * inv);
-                    o4.w = pack_bf16(__uint_as_float(r1[v * 8 + 6]) * inv, __uint_as_float(r1[v * 8 + 7]) * inv);
-                    *reinterpret_cast<uint4*>(dst + 32 + v * 8) = o4;
-                }
 #ifndef BN_TIMELINE
-                if (p.lse)
+                if (p.lse && hf == 0)
                     p.lse[((size_t)b * p.Hq + h) * p.S + gi] =
-                        l_run > 0.f ? (m_ref * p.scale_log2 + log2f(l_run)) * PF_LN2 : -INFINITY;
+                        l_row > 0.f ? (m_ref * p.scale_log2 + log2f(l_row)) * PF_LN2 : -INFINITY;
 #endif
             }
-            if (lane == 0) BN_LOG(10 | u << 8);
             it = it_next;
             w = w_next;
         }
+        // a warp that gives up (a bounded wait ran out) releases its partner, which may be waiting at the named barrier
+        if (!ok) named_bar_arrive(pair_bar, 64);
     }
 
     // common exit: everybody arrives here (all waits are bounded), then TMEM is freed
     tc::fence_before_sync();
     __syncthreads();
     if (tid == 0 && s_abort) atomicExch(p.error_word, BN_ERR_TIMEOUT);
-    if (warp == 8) {
+    if (warp == 16) {
         tc::fence_after_sync();
         tc::tmem_dealloc(tmem, P2_TMEM_COLS);
     }

@@ -101,6 +101,26 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// Named barrier `id` over `n_threads` threads (a multiple of 32) that also ORs a predicate across them
+__device__ __forceinline__ bool named_bar_or(int id, int n_threads, bool pred) {
+    uint32_t out;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %3, 0;\n\t"
+        "barrier.cta.red.or.pred p, %1, %2, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(out)
+        : "r"(id), "r"(n_threads), "r"((uint32_t)pred)
+        : "memory");
+    return out != 0;
+}
+__device__ __forceinline__ void named_bar_arrive(int id, int n_threads) {
+    asm volatile("barrier.cta.arrive %0, %1;" ::"r"(id), "r"(n_threads) : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int n_threads) {
+    asm volatile("barrier.cta.sync %0, %1;" ::"r"(id), "r"(n_threads) : "memory");
+}
+
 // ---------------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
