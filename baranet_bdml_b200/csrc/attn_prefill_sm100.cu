@@ -603,6 +603,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         // ------------------------------------------------------------ MMA issuer
         constexpr uint32_t IDESC_QK = tc::idesc_bf16(PF_BM, PF_BN, 0);
         constexpr uint32_t IDESC_PV = tc::idesc_bf16(PF_BM, PF_D, 1);
+        // a shared-memory descriptor is this constant plus the tile's address in units of 16 bytes (bits 0-13)
+        const uint64_t dZero = tc::smem_desc_sw128(0);
         int stage = 0;
         uint32_t phase = 0;
         int q_use[2] = {0, 0};
@@ -629,8 +631,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                     tc::fence_after_sync();
 #pragma unroll
                     for (int kk = 0; kk < PF_D / 16; ++kk)
-                        tc::mma_ss(tmem + u * 128, tc::smem_desc_sw128(qaddr[u] + kk * 32),
-                                   tc::smem_desc_sw128(sK + st * PF_TILE_BYTES + kk * 32), IDESC_QK, kk > 0);
+                        tc::mma_ss(tmem + u * 128, dZero + (uint64_t)((qaddr[u] >> 4) + kk * 2),
+                                   dZero + (uint64_t)(((sK + st * PF_TILE_BYTES) >> 4) + kk * 2), IDESC_QK, kk > 0);
                     tc::commit(smem_u32(&bar_s[u]));
                     if (j == w.n_t[u] - 1) tc::commit(smem_u32(&bar_qfree[(q_use[u] - 1) & 1][u]));
                 }
@@ -670,7 +672,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 #pragma unroll
                         for (int kk = 0; kk < PF_BN / 16; ++kk)
                             tc::mma_ts(tmem + 256 + u * 64, tmem + 384 + u * 64 + kk * 8,
-                                       tc::smem_desc_sw128(sV + stage * PF_TILE_BYTES + kk * 2048), IDESC_PV,
+                                       dZero + (uint64_t)(((sV + stage * PF_TILE_BYTES) >> 4) + kk * 128), IDESC_PV,
                                        (j > 0) || (kk > 0));
                         tc::commit(smem_u32(&bar_pv[u]));                          // P_u(j) may be overwritten
                         if (j == w.n_t[u] - 1) tc::commit(smem_u32(&bar_o[u]));
