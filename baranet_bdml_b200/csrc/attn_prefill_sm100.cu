@@ -11,19 +11,17 @@
 //   1. rope_k_kernel: rotates K once into scratch (K is read by 8 query heads
 //      x S/128 query tiles, so it is rotated once, not per use) and writes the
 //      cos/sin table of the S positions.
-//   2. prefill_kernel: one CTA per (batch, query head, 128-row query tile),
-//      two CTAs resident per SM.
-//        warps 0-3  softmax: one query row per thread (TMEM lane = row), so the
-//                   row max / row sum need no cross-thread traffic; they also
-//                   rotate the Q tile into swizzled shared memory (prologue)
-//                   and write O (epilogue)
-//        warp 4     TMA producer: K/V tiles of 128 keys through a 2-stage ring
-//        warp 5     MMA issuer: tcgen05.mma, S = Q K^T (128x128x64) into TMEM,
-//                   O += P V (128x64x128) with P read from TMEM
-//      TMEM (256 columns): S fp32 [0,128) | O fp32 [128,192) | P bf16 [192,256)
-//      Softmax works in base 2 with the scale folded into the exponent, masks
-//      only tiles that touch the diagonal, skips tiles above it, and rescales O
-//      only when the running maximum has grown by more than 2^8.
+//   2. prefill_kernel: persistent, one CTA per SM, two 128-row query tiles in
+//      flight, 16 softmax warps + MMA warp + TMA warp (described at the kernel).
+//      prefill_kernel_v1 (flag BN_PREFILL_SINGLE_TILE_KERNEL) is the simple
+//      variant kept as a second implementation for the tests: one CTA per
+//      (batch, query head, 128-row query tile), two CTAs per SM, 4 softmax
+//      warps (one query row per thread), TMA warp, MMA warp; TMEM (256
+//      columns): S fp32 [0,128) | O fp32 [128,192) | P bf16 [192,256).
+//   Both compute S = Q K^T (128x128x64, tcgen05.mma, operands in shared memory)
+//   into TMEM and O += P V (128x64x128) with P read from TMEM; softmax in base 2
+//   with the scale folded into the exponent; only tiles that touch the diagonal
+//   are masked, tiles above it are skipped.
 //   Every mbarrier wait is bounded; on expiry the kernel raises the error word
 //   at the head of the scratch buffer, frees its TMEM and returns.
 #include <math.h>
@@ -401,26 +399,37 @@ prefill_kernel_v1(const __grid_constant__ CUtensorMap tmap_k, const __grid_const
 // launch 2, main kernel: persistent, one CTA per SM, TWO query tiles in flight
 // ---------------------------------------------------------------------------
 // Work unit = (batch, query head, pair of 128-row query tiles); units are ordered
-// heaviest first and dealt round-robin to the CTAs (grid = number of SMs), each
+// heaviest first and dealt in snake order to the CTAs (grid = number of SMs), each
 // CTA walking its units in a loop so that the next unit's Q/K/V loads overlap the
-// current unit's tail.  Ten warps:
-//   warps 0-3  softmax group 0 (query tile 2t)      warp 8  MMA issuer
-//   warps 4-7  softmax group 1 (query tile 2t+1)    warp 9  TMA producer
+// current unit's tail.  Eighteen warps:
+//   warps 0-7   softmax of query tile 2t   (warps 0-3 keys 0..63 of a step, 4-7 keys 64..127)
+//   warps 8-15  softmax of query tile 2t+1 (same split)
+//   warp 16     MMA issuer                  warp 17  TMA producer
+// Two threads per query row: thread = (TMEM lane = row, half of the step's 128
+// keys, half of the 64 output columns).  Four softmax warps per scheduler hide
+// the latencies of TMEM loads, barrier waits and exponentials; the two threads
+// of a row share the exponent reference, their per-step exchange is one named
+// barrier (64 threads) that ORs an "out of range" flag.
 // Both tiles read the same K/V stages, so each K/V tile is fetched once per
-// 256 query rows, and the tensor pipe works on one tile (P V, then the next
-// Q K^T) while the other tile's softmax runs.  Q tiles arrive by TMA (double
-// buffered across units) and are rotated in place by their softmax group.
+// 256 query rows, and the tensor pipe works on one tile (next Q K^T, then P V)
+// while the other tile's softmax runs.  Q tiles arrive by TMA (double buffered
+// across units) and are rotated in place, a row per warp instruction (lane =
+// rotation pair), one unit AHEAD: right after a tile's last step and before its
+// epilogue, so the MMA warp can start the next unit while O is written out.
 // TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,320) O1 [320,384)
 //                     P0 [384,448) P1 [448,512)
-// Softmax is ONE pass per tile with an exponent reference that starts at 0 and
+// Softmax is ONE pass per step with an exponent reference that starts at 0 and
 // moves only when a probability would leave [2^-64, 2^64] (bf16 and fp32 keep
-// their relative precision over that range): then the warp takes the true row
-// maximum, rescales O and l and redoes the tile.  The MMA warp issues the next
-// Q K^T of a tile before its P V, so the tile's next softmax starts while the
-// P V still runs.  At head_dim 64 the MUFU unit (one exponential per score), not
-// the tensor pipe, is the first limit; moving a share of the exponentials to the
-// FMA pipe (Cody-Waite split + cubic) was measured and did not pay, because a
-// softmax group that runs alone is bound by instruction latency, not by MUFU.
+// their relative precision over that range): then the two warps of the rows
+// take the true row maximum, rescale O and l and redo the step.
+// What bounds it (measured): with the exponential replaced by an FMA the kernel
+// still takes 87 % of its time, so the chain  S ready -> TMEM loads -> P stored ->
+// MMA warp wakes -> next Q K^T issued, executed, committed  (about 850 cycles of
+// it pure hand-off latency per step and tile), not MUFU or the tensor pipe, is
+// the limit; TMEM has no room for a second S buffer per tile at 128-key steps.
+// Measured and dropped: exponentials on the FMA pipe; 64-key steps with double-
+// buffered S; one MMA warp per tile; pairing two heads on the same query rows;
+// an extra warp for the Q rotation; issuing P V before the next Q K^T.
 // Optional event log for performance work (compiled out unless built with -DBN_TIMELINE): the warps of CTA 0
 // append (clock64, code) pairs to the caller's lse buffer, 2048 entries per warp, INSTEAD of the log-sum-exp.
 #ifdef BN_TIMELINE
