@@ -38,7 +38,7 @@ _emit = print
 PREFILL = dict(B=8, S=2048, Hq=32, Hkv=4, D=64)
 DECODE = dict(B=64, Hq=32, Hkv=4, D=64, Lmin=1024, Lmax=4096, page=16)
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
-NCU_TRAFFIC = {"prefill_kernel": 85.144e6 + 27.124e6, "decode_paged_kernel": 163.590e6 + 4.757e6}
+NCU_TRAFFIC = {"prefill_kernel": 85.555e6 + 27.917e6, "decode_paged_kernel": 163.424e6 + 3.766e6}
 
 
 def peaks():
