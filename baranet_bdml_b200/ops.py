@@ -70,6 +70,76 @@ def attn_prefill_bf16(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scal
     return out
 
 
+class HostPrefillPipeline:
+    """Prefill attention for callers whose q/k/v/out live in (pinned) HOST memory, as the reference's tensors do
+    before `to_device()` (mygrad tensors are created on the host and copied per call).  Every `submit` copies that
+    call's inputs host->device, runs the two kernels and copies the result device->host, but on three streams with
+    `depth` rotating device buffers, so the copies of neighbouring calls overlap each other (PCIe is full duplex)
+    and the kernels.  `finish()` makes the current stream wait for everything submitted.
+
+    The result of submit number i is complete in its `out_host` once `finish()` (or a later synchronize) returns."""
+
+    def __init__(self, B: int, S: int, Hq: int, Hkv: int, D: int = 64, *, depth: int = 2, device=None):
+        dev = device or "cuda"
+        self.shape = (B, S, Hq, Hkv, D)
+        self.slots = []
+        for _ in range(depth):
+            self.slots.append(dict(
+                q=torch.empty((B, S, Hq, D), dtype=torch.bfloat16, device=dev),
+                k=torch.empty((B, S, Hkv, D), dtype=torch.bfloat16, device=dev),
+                v=torch.empty((B, S, Hkv, D), dtype=torch.bfloat16, device=dev),
+                o=torch.empty((B, S, Hq, D), dtype=torch.bfloat16, device=dev),
+                ws=prefill_workspace(B, S, Hq, Hkv, D, dev),
+                in_done=torch.cuda.Event(), run_done=torch.cuda.Event(), out_done=torch.cuda.Event(), used=False))
+        self.s_in, self.s_run, self.s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+        self.n = 0
+        self._started = False
+
+    def submit(self, q_host: torch.Tensor, k_host: torch.Tensor, v_host: torch.Tensor, out_host: torch.Tensor, **kw):
+        for t, n in ((q_host, "q"), (k_host, "k"), (v_host, "v"), (out_host, "out")):
+            if t.is_cuda or t.dtype != torch.bfloat16 or not t.is_contiguous():
+                raise RuntimeError(f"HostPrefillPipeline({n}): expected a contiguous bf16 host tensor")
+        if not self._started:
+            # work already queued on the caller's stream comes first
+            ev = torch.cuda.Event()
+            ev.record()
+            for st in (self.s_in, self.s_run, self.s_out):
+                st.wait_event(ev)
+            self._started = True
+        sl = self.slots[self.n % len(self.slots)]
+        self.n += 1
+        with torch.cuda.stream(self.s_in):
+            if sl["used"]:
+                self.s_in.wait_event(sl["run_done"])       # the slot's inputs are still being read until then
+            sl["q"].copy_(q_host, non_blocking=True)
+            sl["k"].copy_(k_host, non_blocking=True)
+            sl["v"].copy_(v_host, non_blocking=True)
+            sl["in_done"].record()
+        with torch.cuda.stream(self.s_run):
+            self.s_run.wait_event(sl["in_done"])
+            if sl["used"]:
+                self.s_run.wait_event(sl["out_done"])      # the slot's previous result must have left the device
+            attn_prefill_bf16(sl["q"], sl["k"], sl["v"], out=sl["o"], workspace=sl["ws"], **kw)
+            sl["run_done"].record()
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(sl["run_done"])
+            out_host.copy_(sl["o"], non_blocking=True)
+            sl["out_done"].record()
+        sl["used"] = True
+
+    def finish(self) -> None:
+        """The current stream waits for every submitted call (inputs copied, kernels run, results on the host)."""
+        cur = torch.cuda.current_stream()
+        for sl in self.slots:
+            if sl["used"]:
+                cur.wait_event(sl["out_done"])
+        self._started = False
+
+    def status(self) -> None:
+        for sl in self.slots:
+            sl["ws"].status()
+
+
 def lse_combine(outs: torch.Tensor, lses: torch.Tensor, *, out_dtype=torch.float32) -> Tuple[torch.Tensor, torch.Tensor]:
     """outs (P, n, D) fp32, lses (P, n) fp32 -> merged (n, D), lse (n)."""
     _need(outs, torch.float32, "lse_combine(outs)")

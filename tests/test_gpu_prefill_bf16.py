@@ -147,6 +147,30 @@ def test_prefill_full_config2_properties(lib, cref):
     assert np.abs(got[:, 8:10] - ref[0][:, 8:10]).max() <= GATE
 
 
+def test_host_pipeline_matches_direct_calls(lib):
+    """The host-memory front-end (copies and kernels of neighbouring calls overlap on three streams) returns, for
+    every submitted call, the bits of a plain call on the same inputs; more calls than device buffer sets."""
+    from baranet_bdml_b200 import ops
+    B, S, Hq, Hkv, D = 2, 300, 8, 2, 64
+    pipe = ops.HostPrefillPipeline(B, S, Hq, Hkv, D, depth=2)
+    calls = []
+    for i in range(5):
+        q, k, v = make_inputs(B, S, Hq, Hkv, D, 900 + i)
+        hq, hk, hv = (torch.from_numpy(a).to(torch.bfloat16).pin_memory() for a in (q, k, v))
+        ho = torch.empty((B, S, Hq, D), dtype=torch.bfloat16).pin_memory()
+        calls.append((hq, hk, hv, ho))
+        pipe.submit(hq, hk, hv, ho)
+    pipe.finish()
+    torch.cuda.synchronize()
+    pipe.status()
+    for hq, hk, hv, ho in calls:
+        want = ops.attn_prefill_bf16(hq.cuda(), hk.cuda(), hv.cuda())
+        torch.cuda.synchronize()
+        assert torch.equal(ho, want.cpu())
+    with pytest.raises(RuntimeError, match="host tensor"):
+        pipe.submit(calls[0][0].cuda(), calls[0][1], calls[0][2], calls[0][3])
+
+
 def test_prefill_rejects_bad_arguments(lib):
     from baranet_bdml_b200 import ops
     q = torch.zeros((1, 16, 8, 32), dtype=torch.bfloat16, device="cuda")
