@@ -442,44 +442,30 @@ constexpr int P2_NSTAGE = 4;
 constexpr int P2_SMEM_BYTES = 1024 + PF_TILE_BYTES * (4 + 2 * P2_NSTAGE);
 constexpr uint32_t P2_TMEM_COLS = 512;
 
-// exp2 of 32 scores -> 16 packed bf16x2.  The row sum is accumulated two-wide in `sum2`; `pmax` tracks the
-// largest p (packed bf16x2).  scale2 / mneg2 hold (scale_log2, scale_log2) and (-m*scale_log2, same).
+// exp2 of 16 scores -> 8 packed bf16x2; the row sum is accumulated in two independent chains.  The arithmetic is
+// plain scalar FFMA / FADD: the packed two-wide forms (fma.rn.f32x2, add.rn.f32x2) were measured slower here.
+// The scale, the shift and the two sums travel as register pairs (scale2, mneg2 = the value twice; sum2): in this
+// form ptxas keeps the kernel inside its 96 registers without spilling, which is worth 4 % of the run time.
 template <bool MASK>
-__device__ __forceinline__ void softmax_chunk(uint32_t (&r)[32], uint32_t (&pk)[16], uint64_t scale2,
-                                              uint64_t mneg2, int first_key, int row_last, uint32_t& pmax,
-                                              uint64_t& sum2) {
-#pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-        float x0, x1;
-        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), scale2, mneg2), x0, x1);
-        float p0 = ex2(x0), p1 = ex2(x1);
-        if (MASK) {
-            if (first_key + i > row_last) p0 = 0.f;
-            if (first_key + i + 1 > row_last) p1 = 0.f;
-        }
-        sum2 = add_f32x2(sum2, pack_f32x2(p0, p1));
-        pk[i / 2] = pack_bf16(p0, p1);
-        asm("max.bf16x2 %0, %0, %1;" : "+r"(pmax) : "r"(pk[i / 2]));
-    }
-}
-
-// 16-score form of the same, for the kernel whose softmax threads each own half a row
-template <bool MASK>
-__device__ __forceinline__ void softmax_chunk16(uint32_t (&r)[16], uint32_t (&pk)[8], uint64_t scale2,
-                                                uint64_t mneg2, int first_key, int row_last, uint32_t& pmax,
-                                                uint64_t& sum2) {
+__device__ __forceinline__ void softmax_chunk16(uint32_t (&r)[16], uint32_t (&pk)[8], uint64_t scale2, uint64_t mneg2,
+                                                int first_key, int row_last, uint64_t& sum2) {
 #pragma unroll
     for (int i = 0; i < 16; i += 2) {
-        float x0, x1;
-        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), scale2, mneg2), x0, x1);
-        float p0 = ex2(x0), p1 = ex2(x1);
+        float sc, mn, dummy;
+        unpack_f32x2(scale2, sc, dummy);
+        unpack_f32x2(mneg2, mn, dummy);
+        float p0 = ex2(fmaf(__uint_as_float(r[i]), sc, mn));
+        float p1 = ex2(fmaf(__uint_as_float(r[i + 1]), sc, mn));
         if (MASK) {
             if (first_key + i > row_last) p0 = 0.f;
             if (first_key + i + 1 > row_last) p1 = 0.f;
         }
-        sum2 = add_f32x2(sum2, pack_f32x2(p0, p1));
+        {
+            float s0_, s1_;
+            unpack_f32x2(sum2, s0_, s1_);
+            sum2 = pack_f32x2(s0_ + p0, s1_ + p1);
+        }
         pk[i / 2] = pack_bf16(p0, p1);
-        asm("max.bf16x2 %0, %0, %1;" : "+r"(pmax) : "r"(pk[i / 2]));
     }
 }
 
@@ -522,6 +508,7 @@ __device__ __forceinline__ int unit_of(int round, int n_units) {
     return k < n_units ? k : -1;
 }
 
+// 18 warps = 5 on one scheduler: 16384 / (5 * 32) leaves 96 registers per thread
 __global__ void __launch_bounds__(P2_THREADS, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p, const int n_units) {
@@ -783,13 +770,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 
                 // one pass over this thread's 64 columns: P = exp2(S * scale_log2 - m_ref * scale_log2) -> TMEM, with
                 // the load of the next 16 columns in flight while the current 16 are processed
-                auto half_pass = [&](float mneg, uint32_t& pmax, bool first_store_needs_pv) {
+                auto half_pass = [&](float mneg, bool first_store_needs_pv) {
                     uint64_t sum2 = 0;   // (0.f, 0.f)
                     const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2), mneg2 = pack_f32x2(mneg, mneg);
                     uint32_t r0[16], r1[16], pk[8];
                     auto chunk = [&](uint32_t (&r)[16], int c) {
-                        if (need_mask) softmax_chunk16<true>(r, pk, scale2, mneg2, j0 + c * 16, row_last, pmax, sum2);
-                        else softmax_chunk16<false>(r, pk, scale2, mneg2, j0 + c * 16, row_last, pmax, sum2);
+                        if (need_mask) softmax_chunk16<true>(r, pk, scale2, mneg2, j0 + c * 16, row_last, sum2);
+                        else softmax_chunk16<false>(r, pk, scale2, mneg2, j0 + c * 16, row_last, sum2);
                     };
                     tc::ld16(tS + 0, r0);
                     tc::wait_ld(r0);
@@ -821,14 +808,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 // The exponent reference starts at 0 and moves only when it has to: p = 2^(s*c - ref) may be
                 // anywhere in [2^-64, 2^64] without any loss (bf16 and fp32 keep their relative precision over
                 // that range), so for ordinary score magnitudes there is never a second pass or an O rescale.
-                uint32_t pmax = 0;           // bf16x2 (+0, +0)
-                float lsum = half_pass(-m_ref * p.scale_log2, pmax, tiles_done + j > 0);
+                float lsum = half_pass(-m_ref * p.scale_log2, tiles_done + j > 0);
                 if (s_abort) { ok = false; break; }
-                // Did any p leave the safe range?  bf16 bit patterns are monotone for p >= 0.  Too large: > 2^64
-                // (incl. inf).  Too small matters on the first 64 keys only, where key 0 is valid for every row: a
-                // largest p below 2^-64 means the whole row may have underflowed.
-                const uint32_t pm = max(pmax & 0xffffu, pmax >> 16);
-                const bool over = pm > 0x5F80u || (j == 0 && hf == 0 && pm < 0x1F80u);
+                const bool over = !(lsum <= 0x1p64f) || (j == 0 && hf == 0 && lsum < 0x1p-64f);
                 if (named_bar_or(pair_bar, 64, over)) {
                     // rare, and taken by both warps of these rows together: move the reference to the true row
                     // maximum, rescale O and l, redo the step.
@@ -858,8 +840,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                         tc::st32(tO, ro);
                     }
                     m_ref = m_upd;
-                    pmax = 0;
-                    lsum = half_pass(-m_ref * p.scale_log2, pmax, false);
+                    lsum = half_pass(-m_ref * p.scale_log2, false);
                     named_bar_sync(pair_bar, 64);      // the exchange slots may be written again
                 }
                 l_run += lsum;
