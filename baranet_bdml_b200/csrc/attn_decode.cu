@@ -110,9 +110,17 @@ struct Schedule {
     int T;                 // all stages of the launch (< 2^31)
     int G;                 // CTAs that take part
     __device__ __forceinline__ int nst(int b) const { return prefix[b + 1] - prefix[b]; }
-    __device__ __forceinline__ int range_begin(int cta) const { return (int)((long long)cta * T / G); }
+    // 32-bit division whenever the products fit (G <= 2^9 CTAs, T < 2^22 stages): the 64-bit form is an emulated
+    // sequence several times longer, and these sit on the path to the first TMA load
+    __device__ __forceinline__ bool small() const { return T < (1 << 22) && G <= (1 << 9); }
+    __device__ __forceinline__ int range_begin(int cta) const {
+        return small() ? (int)((unsigned)cta * (unsigned)T / (unsigned)G) : (int)((long long)cta * T / G);
+    }
     // the CTA whose range holds global stage x
-    __device__ __forceinline__ int cta_of(int x) const { return (int)((((long long)x + 1) * G - 1) / T); }
+    __device__ __forceinline__ int cta_of(int x) const {
+        return small() ? (int)((((unsigned)x + 1u) * (unsigned)G - 1u) / (unsigned)T)
+                       : (int)((((long long)x + 1) * G - 1) / T);
+    }
     // first sequence b with Hkv * prefix[b + 1] > x
     __device__ __forceinline__ int seq_of(int x) const {
         int lo = 0, hi = B - 1;
@@ -137,7 +145,8 @@ struct SegmentIter {
     int pos, end, b, g;
     bool started;
     __device__ __forceinline__ void init(int lo, int hi) { pos = lo; end = hi; b = 0; g = 0; started = false; }
-    __device__ __forceinline__ bool next(const Schedule& sc, Segment& sg) {
+    // `want_parts` = false skips c_first / n_parts (two divisions), which the producer never reads
+    __device__ __forceinline__ bool next(const Schedule& sc, Segment& sg, bool want_parts = true) {
         if (pos >= end) return false;
         int n;
         if (!started) {
@@ -157,7 +166,7 @@ struct SegmentIter {
         sg.s0 = pos - sb;
         sg.s1 = min(n, end - sb);
         sg.L = sc.len[b];
-        if (sg.s0 == 0 && sg.s1 == n) {
+        if ((sg.s0 == 0 && sg.s1 == n) || !want_parts) {
             sg.c_first = blockIdx.x;
             sg.n_parts = 1;
         } else {
@@ -248,7 +257,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
         SegmentIter iter;
         iter.init(range_lo, range_hi);
         Segment sg, sg_next;
-        bool have = iter.next(sc, sg);
+        bool have = iter.next(sc, sg, false);
         auto load_group = [&](const Segment& sgm, int grp) {
             const int e = grp * 32 + lane;
             const int n_pages_seq = (sgm.L + BN_PAGE_TOKENS - 1) / BN_PAGE_TOKENS;
@@ -257,7 +266,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
         const uint64_t stream_policy = l2_policy_evict_first();     // every cache byte is read once per launch
         int ids = have ? load_group(sg, sg.s0 / GRP) : -1, ids_pref = -1;
         while (ok && have) {
-            const bool have_next = iter.next(sc, sg_next);
+            const bool have_next = iter.next(sc, sg_next, false);
             const int n_pages_seq = (sg.L + BN_PAGE_TOKENS - 1) / BN_PAGE_TOKENS;
             for (int s = sg.s0; s < sg.s1; ++s) {
                 if (s == sg.s0 || s % GRP == 0) {
