@@ -26,6 +26,9 @@ SIGNATURES = {
     "bn_version": (_i, []),
     "bn_mm_f32": (_i, [_p, _i64, _i64, _p, _i64, _i64, _p, _i64, _i64, _i, _i, _i, _p]),
     "bn_rope_f32": (_i, [_p, _i64, _i64, _p, _i64, _i64, _i, _i, _i, _f, _i, _p]),
+    "bn_rmsnorm_f32": (_i, [_p, _i64, _i64, _p, _i64, _p, _i64, _i64, _i, _i, _f, _p]),
+    "bn_add_rmsnorm_f32": (_i, [_p, _i64, _i64, _p, _i64, _i64, _p, _i64, _p, _i64, _i64, _p, _i64, _i64, _i, _i, _f,
+                                _p]),
     "bn_attn_prefill_f32": (_i, [_p, _i64, _i64, _p, _i64, _i64, _p, _i64, _i64, _p, _i64, _i64,
                                  _i, _i, _i, _i, _f, _f, _i, _i, _i, _i, _p]),
     "bn_attn_prefill_bf16_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),

@@ -52,6 +52,27 @@ class LLaMAConfig:
         assert self.num_attention_heads % self.num_key_value_heads == 0
 
 
+class RMSNorm:
+    """mygrad/llama/llama_layers.py:13-29: same constructor, `weight` (1, hidden) initialised to ones, `__call__`,
+    `parameters()`.  `add_norm(residual, x)` is the fused form of the decoder layer's residual add followed by this
+    norm (llama_layers.py:279-283): returns (residual + x, norm(residual + x)) from one launch."""
+
+    def __init__(self, hidden_size: int, eps: float = 1e-6, is_cuda: bool = True):
+        self.hidden_size = hidden_size
+        self.eps = eps
+        self.is_cuda = is_cuda
+        self.weight = AGTensor(np.ones((1, hidden_size), dtype=np.float32), requires_grad=True, is_cuda=is_cuda)
+
+    def __call__(self, x: AGTensor) -> AGTensor:
+        return x.rmsnorm(self.weight, self.eps)
+
+    def add_norm(self, residual: AGTensor, x: AGTensor):
+        return residual.add_rmsnorm(x, self.weight, self.eps)
+
+    def parameters(self):
+        return [self.weight]
+
+
 class RotaryEmbedding:
     """mygrad/llama/llama_layers.py:32-42."""
 

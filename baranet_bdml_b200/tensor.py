@@ -153,6 +153,36 @@ class TensorF:
                                    self.h, self.w, head_dim, theta, position_offset, _stream_ptr()))
         return out
 
+    def rmsnorm(self, weight: "TensorF", eps: float = 1e-6) -> "TensorF":
+        """op_rmsnorm (src/ops/op_rmsnorm.cuh:134-157; TensorF.rmsnorm, src/py_tensor_shim.hh:256-260)
+        -> bn_rmsnorm_f32.  weight is (1, hidden)."""
+        if weight.h != 1 or weight.w != self.w:
+            raise RuntimeError("RMSNorm: weight shape must be (1, hidden_dim)")
+        if not self.on_device or not weight.on_device:
+            raise RuntimeError("RMSNorm: only GPU implementation available")
+        out = TensorF(self.h, self.w, True)
+        _lib.check(_lib.load().bn_rmsnorm_f32(self._ptr(), self.stride_h, self.stride_w, weight._ptr(), weight.stride_w,
+                                              out._ptr(), out.stride_h, out.stride_w, self.h, self.w, float(eps),
+                                              _stream_ptr()))
+        return out
+
+    def add_rmsnorm(self, residual: "TensorF", weight: "TensorF", eps: float = 1e-6):
+        """(self + residual, rmsnorm(self + residual)) in one launch -> bn_add_rmsnorm_f32: the decoder layer's
+        `hidden = residual + hidden; hidden = norm(hidden)` (mygrad/llama/llama_layers.py:279-283), bit-identical to
+        the reference's two operators."""
+        if residual.h != self.h or residual.w != self.w:
+            raise RuntimeError("RMSNorm: input/output shape mismatch")
+        if weight.h != 1 or weight.w != self.w:
+            raise RuntimeError("RMSNorm: weight shape must be (1, hidden_dim)")
+        if not self.on_device or not residual.on_device or not weight.on_device:
+            raise RuntimeError("RMSNorm: only GPU implementation available")
+        total, out = TensorF(self.h, self.w, True), TensorF(self.h, self.w, True)
+        _lib.check(_lib.load().bn_add_rmsnorm_f32(
+            self._ptr(), self.stride_h, self.stride_w, residual._ptr(), residual.stride_h, residual.stride_w,
+            weight._ptr(), weight.stride_w, total._ptr(), total.stride_h, total.stride_w, out._ptr(), out.stride_h,
+            out.stride_w, self.h, self.w, float(eps), _stream_ptr()))
+        return total, out
+
     def attention_fused(self, key: "TensorF", value: "TensorF", scale: float, causal: bool = False,
                         seq_offset: int = 0, *, num_heads: int, num_kv_heads: int, head_dim: int,
                         theta: float = 10000.0, heads_mode: int = _lib.BN_HEADS_COLLAPSED,
@@ -212,6 +242,15 @@ class AGTensor:
 
     def rope(self, position_offset: int = 0, head_dim: int = 64, theta: float = 10000.0) -> "AGTensor":
         return AGTensor(self.data.rope(position_offset, head_dim, theta), (self,), "rope", requires_grad=False)
+
+    def rmsnorm(self, weight: "AGTensor", eps: float = 1e-6) -> "AGTensor":
+        """AGTensor.rmsnorm of the reference (forward only here)."""
+        return AGTensor(self.data.rmsnorm(weight.data, eps), (self, weight), "rmsnorm", requires_grad=False)
+
+    def add_rmsnorm(self, residual: "AGTensor", weight: "AGTensor", eps: float = 1e-6):
+        total, out = self.data.add_rmsnorm(residual.data, weight.data, eps)
+        return (AGTensor(total, (self, residual), "+", requires_grad=False),
+                AGTensor(out, (self, residual, weight), "add_rmsnorm", requires_grad=False))
 
     def numpy(self) -> np.ndarray:
         return self.data.to_numpy()

@@ -311,6 +311,65 @@ def measure_decode(torch, args, rank, world, dist, reduce_max, pk):
     }
 
 
+def measure_rmsnorm(torch, args, rank, world, dist, reduce_max, pk):
+    """Row N3 (the step either side of attention): residual add + RMSNorm over the tokens of config 2
+    (16384 rows x hidden 2048, fp32 like the reference).  One launch reads a and b and writes the sum and the normed
+    rows: 4 x 134 MB = 537 MB per step, every byte once; larger than L2, so no buffer rotation is needed."""
+    from baranet_bdml_b200 import _lib
+    rows, hidden = PREFILL["B"] * PREFILL["S"], 2048
+    g = torch.Generator(device="cuda").manual_seed(99 + rank)
+    a = torch.randn((rows, hidden), generator=g, device="cuda")
+    b = torch.randn((rows, hidden), generator=g, device="cuda")
+    w = torch.ones((hidden,), device="cuda")
+    s_out, y = torch.empty_like(a), torch.empty_like(a)
+    L = _lib.load()
+
+    def fused(i):
+        _lib.check(L.bn_add_rmsnorm_f32(a.data_ptr(), hidden, 1, b.data_ptr(), hidden, 1, w.data_ptr(), 1,
+                                        s_out.data_ptr(), hidden, 1, y.data_ptr(), hidden, 1, rows, hidden, 1e-6,
+                                        torch.cuda.current_stream().cuda_stream))
+
+    def plain(i):
+        _lib.check(L.bn_rmsnorm_f32(a.data_ptr(), hidden, 1, w.data_ptr(), 1, y.data_ptr(), hidden, 1, rows, hidden,
+                                    1e-6, torch.cuda.current_stream().cuda_stream))
+
+    steps = max(20, args.steps // 2)
+    ms_fused = reduce_max(time_loop(torch, fused, steps, 3, dist))
+    ms_plain = reduce_max(time_loop(torch, plain, steps, 3, dist))
+    bytes_fused, bytes_plain = 4 * rows * hidden * 4, 2 * rows * hidden * 4
+    gbs = bytes_fused * world / (ms_fused * 1e-3) / 1e9
+    out = {
+        "metric": "add_rmsnorm_hbm_gbs", "value": gbs, "unit": "GB/s", "ms_per_step": ms_fused, "steps": steps,
+        "n_gpus": world, "dtype": "f32",
+        "config": {"workload": "residual add + RMSNorm (row N3), 16384 rows x hidden 2048 fp32 = the tokens of "
+                               "BASELINE config 2; one launch, bit-identical to the reference's op_add + op_rmsnorm",
+                   "algorithmic_bytes_per_step": bytes_fused, "l2": "537 MB per step, larger than L2"},
+        "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": pk["hbm"], "unit": "GB/s",
+                     "frac": gbs / world / pk["hbm"], "traffic": None, "peak_source": pk["source"],
+                     "kernel": "rmsnorm_kernel"},
+        "rmsnorm_only": {"value": bytes_plain * world / (ms_plain * 1e-3) / 1e9, "unit": "GB/s",
+                         "ms_per_step": ms_plain, "algorithmic_bytes_per_step": bytes_plain},
+        "gpu_launches": 2 * steps,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        import numpy as np
+        from oracle import cref
+        cref.set_num_threads(len(os.sched_getaffinity(0)))
+        n = 2048
+        rng = np.random.default_rng(0)
+        xa, xb = rng.standard_normal((n, hidden), dtype=np.float32), rng.standard_normal((n, hidden), dtype=np.float32)
+        ww = np.ones(hidden, np.float32)
+        cref.add_rmsnorm(xa[:64], xb[:64], ww)
+        t0 = time.perf_counter()
+        reps = 5
+        for _ in range(reps):
+            cref.add_rmsnorm(xa, xb, ww)
+        dt = (time.perf_counter() - t0) / reps
+        out["cpu_baseline"] = {"value": 4 * n * hidden * 4 / dt / 1e9, "unit": "GB/s", "cores": cref.num_threads(),
+                               "kind": "port", "sample": f"{n} of {rows} rows, oracle/ref_attention.c with OpenMP"}
+    return out
+
+
 def measure_longctx(torch, args, rank, world, dist, reduce_max, pk):
     """BASELINE config 4: batch 4, one 262144-token sequence each, 32q/4kv heads.  The sequence is cut into
     contiguous page-aligned token ranges, one per GPU; each GPU decodes over its range (normalised partial
@@ -395,6 +454,10 @@ def run_ours(args):
                 result["decode_long"] = measure_longctx(torch, args, rank, world, dist, reduce_max, pk)
             except Exception as e:
                 result["decode_long"] = {"error": repr(e)}
+            try:
+                result["rmsnorm"] = measure_rmsnorm(torch, args, rank, world, dist, reduce_max, pk)
+            except Exception as e:
+                result["rmsnorm"] = {"error": repr(e)}
     if rank == 0:
         result["clocks"] = sampler.stop()
         if world == 1 and not args.no_cpu_baseline and not args.decode_only:

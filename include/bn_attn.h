@@ -92,6 +92,23 @@ BN_API int bn_mm_f32(const float* A, int64_t a_rs, int64_t a_cs, const float* B,
 BN_API int bn_rope_f32(const float* x, int64_t x_rs, int64_t x_cs, float* y, int64_t y_rs, int64_t y_cs, int rows,
                 int cols, int head_dim, float theta, int position_offset, bn_stream_t stream);
 
+/* y = x / sqrt(mean(x^2) + eps) * w, row by row; x, y (rows, hidden), w (hidden) with element strides.
+ * Same arithmetic order as the reference kernel (256 partial fused-multiply-add chains, its reduction tree, IEEE
+ * division and square root), so the result is the reference's bit for bit.
+ * Replaces op_rmsnorm (src/ops/op_rmsnorm.cuh:8-53, launcher :134-157; bound as TensorF.rmsnorm,
+ * src/py_tensor_shim.hh:256-260). */
+BN_API int bn_rmsnorm_f32(const float* x, int64_t x_rs, int64_t x_cs, const float* w, int64_t w_cs, float* y,
+                          int64_t y_rs, int64_t y_cs, int rows, int hidden, float eps, bn_stream_t stream);
+
+/* sum = a + b (fp32), y = rmsnorm(sum) in one pass; `sum` may be NULL when the caller does not need it.
+ * Replaces the pair op_add + op_rmsnorm that LLaMADecoderLayer runs around attention and the MLP
+ * (`hidden = residual + hidden; hidden = norm(hidden)`, mygrad/llama/llama_layers.py:279-283), which writes the
+ * sum and reads it back; bit-identical to that pair.  (The reference's own fused kernel, op_rmsnorm_residual,
+ * src/ops/op_mm_optimized.cuh:93-162, computes norm(x)*w + residual instead and is never called.) */
+BN_API int bn_add_rmsnorm_f32(const float* a, int64_t a_rs, int64_t a_cs, const float* b, int64_t b_rs, int64_t b_cs,
+                              const float* w, int64_t w_cs, float* sum, int64_t s_rs, int64_t s_cs, float* y,
+                              int64_t y_rs, int64_t y_cs, int rows, int hidden, float eps, bn_stream_t stream);
+
 /* Fused attention core, fp32:
  *   out = softmax_causal((rope(q) @ repeat(rope(k))^T) * scale) @ repeat(v)
  * q, out: (S, Hq*D); k, v: (S, Hkv*D); all with element strides.

@@ -76,6 +76,23 @@ def rope(x, head_dim=64, theta=10000.0, position_offset=0, inv_freq=None):
     return out
 
 
+def rmsnorm(x, w, eps=1e-6):
+    """Bit-faithful restatement of op_rmsnorm (src/ops/op_rmsnorm.cuh:8-53)."""
+    x, w = _f32(x), _f32(w).reshape(-1)
+    out = np.empty_like(x)
+    cpu().ref_rmsnorm_f32(_p(x), _p(w), C.c_int(x.shape[0]), C.c_int(x.shape[1]), C.c_float(eps), _p(out))
+    return out
+
+
+def add_rmsnorm(x, residual, w, eps=1e-6):
+    """s = x + residual (fp32), y = rmsnorm(s): returns (s, y)."""
+    x, residual, w = _f32(x), _f32(residual), _f32(w).reshape(-1)
+    s, y = np.empty_like(x), np.empty_like(x)
+    cpu().ref_add_rmsnorm_f32(_p(x), _p(residual), _p(w), C.c_int(x.shape[0]), C.c_int(x.shape[1]), C.c_float(eps),
+                              _p(s), _p(y))
+    return s, y
+
+
 def softmax(x, causal=False, seq_offset=0):
     x = _f32(x)
     out = np.empty_like(x)
@@ -181,6 +198,14 @@ def gpu_rope(x, head_dim=64, theta=10000.0, position_offset=0):
     out = np.empty_like(x)
     _gcheck(gpu().refgpu_rope(_p(x), C.c_int(x.shape[0]), C.c_int(x.shape[1]), C.c_int(head_dim),
                               C.c_float(theta), C.c_int(position_offset), _p(out)))
+    return out
+
+
+def gpu_rmsnorm(x, w, eps=1e-6):
+    """The reference's own op_rmsnorm on the GPU (needs oracle/_ref)."""
+    x, w = _f32(x), _f32(w).reshape(-1)
+    out = np.empty_like(x)
+    _gcheck(gpu().refgpu_rmsnorm(_p(x), _p(w), C.c_int(x.shape[0]), C.c_int(x.shape[1]), C.c_float(eps), _p(out)))
     return out
 
 

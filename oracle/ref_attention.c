@@ -325,3 +325,50 @@ REF_EXPORT int ref_decode_paged_f32(const float* q, const uint16_t* pool, const 
     }
     return 0;
 }
+
+/* ---------------------------------------------------------------------------
+ * RMSNorm, row-wise:  y = x / sqrt(mean(x^2) + eps) * w
+ * Restates op_rmsnorm_kernel (src/ops/op_rmsnorm.cuh:8-53, launched with 256
+ * threads per row, :134-157) in its own arithmetic order, so the result is the
+ * reference's bit for bit:
+ *   - thread t accumulates x[t], x[t+256], ... as a fused multiply-add chain
+ *     (`sum_sq += val * val` contracts to FFMA under nvcc's defaults);
+ *   - the 256 partial sums are reduced by the shared-memory tree
+ *     sh[t] += sh[t + stride], stride = 128, 64, ..., 1;
+ *   - mean = total / hidden (IEEE division), rms = sqrtf(mean + eps);
+ *   - y = (x / rms) * w  (division first, then the weight).
+ * `residual` (optional) is added to x first, in fp32, as the decoder layer's
+ * `residual + hidden_states` does before the next norm (op_add,
+ * mygrad/llama/llama_layers.py:279-283); the sum is returned in `sum_out`.
+ * ------------------------------------------------------------------------- */
+REF_EXPORT void ref_add_rmsnorm_f32(const float* x, const float* residual, const float* w, int rows, int hidden,
+                                    float eps, float* sum_out, float* y) {
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < rows; ++r) {
+        const float* xr = x + (size_t)r * hidden;
+        const float* rr = residual ? residual + (size_t)r * hidden : NULL;
+        float* sr = sum_out ? sum_out + (size_t)r * hidden : NULL;
+        float sh[256];
+        for (int t = 0; t < 256; ++t) {
+            float acc = 0.0f;
+            for (int i = t; i < hidden; i += 256) {
+                float v = rr ? xr[i] + rr[i] : xr[i];
+                acc = fmaf(v, v, acc);
+            }
+            sh[t] = acc;
+        }
+        for (int stride = 128; stride > 0; stride >>= 1)
+            for (int t = 0; t < stride; ++t) sh[t] += sh[t + stride];
+        float mean_sq = sh[0] / (float)hidden;
+        float rms = sqrtf(mean_sq + eps);
+        for (int i = 0; i < hidden; ++i) {
+            float v = rr ? xr[i] + rr[i] : xr[i];
+            if (sr) sr[i] = v;
+            y[(size_t)r * hidden + i] = (v / rms) * w[i];
+        }
+    }
+}
+
+REF_EXPORT void ref_rmsnorm_f32(const float* x, const float* w, int rows, int hidden, float eps, float* y) {
+    ref_add_rmsnorm_f32(x, NULL, w, rows, hidden, eps, NULL, y);
+}

@@ -320,3 +320,18 @@ def kv_append(pool_bits: np.ndarray, page_table: np.ndarray, positions: np.ndarr
         pool_bits[page, :, 0, slot, :] = f32_to_bf16_bits(kr.reshape(n_kv, head_dim))
         pool_bits[page, :, 1, slot, :] = f32_to_bf16_bits(v_new[t].astype(F32).reshape(n_kv, head_dim))
     return pool_bits
+
+
+def rmsnorm(x: np.ndarray, weight: np.ndarray, eps: float = 1e-6, residual: np.ndarray | None = None,
+            dtype=np.float64):
+    """RMSNorm, row-wise: y = x / sqrt(mean(x^2) + eps) * w  (op_rmsnorm_kernel,
+    src/ops/op_rmsnorm.cuh:8-53; `RMSNorm.__call__`, mygrad/llama/llama_layers.py:13-29).
+    With `residual`, x + residual is normalised (the decoder layer's residual add followed by the next norm,
+    llama_layers.py:279-283) and (sum, y) is returned.  This numpy form is the exact-math statement (float64 by
+    default); the bit-faithful fp32 order of the reference kernel lives in oracle/ref_attention.c."""
+    x = np.asarray(x, dtype=dtype)
+    w = np.asarray(weight, dtype=dtype).reshape(1, -1)
+    s = x if residual is None else (np.asarray(x, dtype=F32) + np.asarray(residual, dtype=F32)).astype(dtype)
+    rms = np.sqrt((s * s).mean(axis=1, keepdims=True) + dtype(eps))
+    y = s / rms * w
+    return y if residual is None else (s, y)

@@ -25,6 +25,7 @@
 #include "ops/op_elemwise.cuh"
 #include "ops/op_mm.cuh"
 #include "ops/op_mm_optimized.cuh"
+#include "ops/op_rmsnorm.cuh"
 #include "ops/op_rope.cuh"
 #include "ops/op_softmax.cuh"
 
@@ -102,6 +103,16 @@ int refgpu_inv_freq(int head_dim, float theta, float* out) {
         CUDA_OK(cudaDeviceSynchronize());
         CUDA_OK(cudaMemcpy(out, d, sizeof(float) * (head_dim / 2), cudaMemcpyDeviceToHost));
         cudaFree(d);
+        return 0;
+    } catch (const std::exception& e) { g_err = e.what(); return 1; }
+}
+
+// op_rmsnorm (src/ops/op_rmsnorm.cuh:134-157): weight is a (1, hidden) tensor
+int refgpu_rmsnorm(const float* x, const float* w, int rows, int hidden, float eps, float* out) {
+    try {
+        Tensor<float> in = upload(x, rows, hidden), wt = upload(w, 1, hidden), o(rows, hidden, true);
+        op_rmsnorm<float>(in, wt, o, eps);
+        download(o, out);
         return 0;
     } catch (const std::exception& e) { g_err = e.what(); return 1; }
 }

@@ -54,6 +54,13 @@ def main(out_dir):
                                       causal=bool(causal))
         save(f"core_s{S}_h{Hq}_{Hkv}_d{D}_off{off}_c{causal}", kind="core", q=q, k=k, v=v, out=out, Hq=Hq, Hkv=Hkv,
              D=D, offset=off, causal=causal, inv_freq=inv[D])
+    # op_rmsnorm (src/ops/op_rmsnorm.cuh): TinyLLaMA hidden size, a width that is not a multiple of the kernel's
+    # 256 threads, and a single column
+    for rows, hidden in ((6, 2048), (5, 300), (3, 1)):
+        x = (rng.standard_normal((rows, hidden), dtype=np.float32) * 2).astype(np.float32)
+        w = (1 + 0.1 * rng.standard_normal(hidden)).astype(np.float32)
+        save(f"rmsnorm_r{rows}_h{hidden}", kind="rmsnorm", x=x, w=w, eps=np.float32(1e-6),
+             out=cref.gpu_rmsnorm(x, w, 1e-6))
     # the reference's own decoder-layer test shape (test_llama.py:142-165): hidden 128, 4 heads / 2 KV heads
     S, hidden, Hq, Hkv, D = 4, 128, 4, 2, 32
     x, wq, wk, wv, wo = layer_inputs_from_seed(7, S, hidden, Hq, Hkv, D)

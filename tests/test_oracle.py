@@ -117,6 +117,11 @@ def test_oracle_matches_reference_cuda_golden(path, cref):
         pytest.skip("no golden fixtures generated yet")
     g = np.load(path)
     kind = str(g["kind"])
+    if kind == "rmsnorm":
+        # fp32 with the reference's own arithmetic order: bit for bit
+        got = cref.rmsnorm(g["x"], g["w"], float(g["eps"]))
+        assert np.array_equal(got, g["out"]), (path, nerr(got, g["out"]))
+        return
     kw = dict(num_heads=int(g["Hq"]), num_kv_heads=int(g["Hkv"]), head_dim=int(g["D"]),
               position_offset=int(g["offset"]), causal=bool(g["causal"]), inv_freq=g["inv_freq"])
     if kind == "layer":
@@ -140,3 +145,21 @@ def test_oracle_matches_reference_cuda_golden(path, cref):
     else:
         pytest.fail(kind)
     assert nerr(got, g["out"]) <= 1e-5, (path, nerr(got, g["out"]))
+
+
+def test_rmsnorm_restatements_agree(cref):
+    """The bit-faithful C restatement of op_rmsnorm against the exact-math numpy statement; residual form; hidden
+    sizes that are not a multiple of the reference's 256 threads; one element; a zero row (eps alone)."""
+    rng = np.random.default_rng(5)
+    for rows, hidden in ((4, 2048), (3, 300), (2, 1), (1, 5000), (5, 256)):
+        x = rng.standard_normal((rows, hidden), dtype=np.float32) * 3
+        w = (1 + 0.2 * rng.standard_normal(hidden)).astype(np.float32)
+        r = rng.standard_normal((rows, hidden), dtype=np.float32)
+        want = R.rmsnorm(x, w, 1e-6)
+        got = cref.rmsnorm(x, w, 1e-6)
+        assert np.abs(got - want).max() <= 2e-6 * np.abs(want).max() + 1e-12
+        s, y = cref.add_rmsnorm(x, r, w, 1e-6)
+        assert np.array_equal(s, x + r)
+        assert np.array_equal(y, cref.rmsnorm(x + r, w, 1e-6))      # the fused form IS add followed by norm
+    z = np.zeros((2, 64), dtype=np.float32)
+    assert np.array_equal(cref.rmsnorm(z, np.ones(64, np.float32), 1e-6), z)
