@@ -1,0 +1,222 @@
+// C (M,N) bf16 = A (M,K) bf16 @ Bt (N,K)^T bf16, fp32 accumulation in tensor memory, for sm_100a.
+//
+// This is the projection GEMM of the attention layer (q/k/v/o_proj: `hidden_states @ W`,
+// mygrad/llama/llama_layers.py:157-159,186; reference operator op_mm, src/ops/op_mm.cuh:39-57) on bf16 operands
+// with the weight stored transposed, (out_features, in_features), so that both operands are K-major: the same
+// operand form as Q K^T in the prefill kernel.
+//
+// Persistent kernel, one CTA per SM, 192 threads:
+//   warps 0-3  epilogue: TMEM -> registers -> bf16 -> global (thread = output row = TMEM lane)
+//   warp 4     MMA issuer: tcgen05.mma.cta_group::1.kind::f16, 128 x 256 x 16 per instruction
+//   warp 5     TMA producer: A tile 128 x 64 and Bt tile 256 x 64 per stage (48 KB), 4-stage mbarrier ring
+// Output tile 128 x 256; the fp32 accumulator (256 TMEM columns) is double buffered, so the epilogue of one tile
+// runs under the main loop of the next.  Tiles are walked N-panel by N-panel with M fastest, so the CTAs that run
+// together share their Bt panel in L2.  Edges: TMA zero-fills loads beyond M, N, K; stores are bounds-checked.
+// Every mbarrier wait is bounded; on expiry the kernel raises the caller's error word, frees TMEM and returns.
+#include "common.cuh"
+#include "ptx.cuh"
+#include "tcgen05.cuh"
+#include "tma.cuh"
+
+namespace bn {
+
+using namespace ptx;
+
+constexpr int GM_BM = 128, GM_BN = 256, GM_BK = 64;
+constexpr int GM_NSTAGE = 4;
+constexpr int GM_A_BYTES = GM_BM * GM_BK * 2;          // 16384
+constexpr int GM_B_BYTES = GM_BN * GM_BK * 2;          // 32768
+constexpr int GM_STAGE_BYTES = GM_A_BYTES + GM_B_BYTES;
+constexpr int GM_SMEM_BYTES = 1024 + GM_NSTAGE * GM_STAGE_BYTES;
+constexpr int GM_THREADS = 192;
+constexpr uint32_t GM_TMEM_COLS = 512;                 // two accumulators of 256 columns
+
+struct GemmParams {
+    __nv_bfloat16* c;
+    int* error_word;       // optional
+    int M, N, K;
+};
+
+__global__ void __launch_bounds__(GM_THREADS, 1)
+gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar_full[GM_NSTAGE], bar_empty[GM_NSTAGE], bar_acc_full[2], bar_acc_empty[2];
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort;
+
+    const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int tiles_m = (p.M + GM_BM - 1) / GM_BM, tiles_n = (p.N + GM_BN - 1) / GM_BN;
+    const int n_tiles = tiles_m * tiles_n;
+    const int k_steps = (p.K + GM_BK - 1) / GM_BK;
+
+    if (tid == 0) {
+        for (int s = 0; s < GM_NSTAGE; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&bar_acc_full[i]), 1);
+            mbar_init(smem_u32(&bar_acc_empty[i]), 4);      // one arrive per epilogue warp
+        }
+        s_abort = 0;
+        fence_mbar_init();
+    }
+    if (warp == 4) {
+        tc::tmem_alloc(smem_u32(&s_tmem_base), GM_TMEM_COLS);
+        tc::tmem_relinquish();
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem = s_tmem_base;
+
+    if (warp == 5) {
+        // ---------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            prefetch_tensormap(&tmap_a);
+            prefetch_tensormap(&tmap_b);
+            uint32_t it = 0;      // ring steps issued
+            bool ok = true;
+            for (int t = blockIdx.x; ok && t < n_tiles; t += gridDim.x) {
+                const int m0 = (t % tiles_m) * GM_BM, n0 = (t / tiles_m) * GM_BN;
+                for (int ks = 0; ks < k_steps; ++ks, ++it) {
+                    const int stage = it % GM_NSTAGE;
+                    ok = mbar_wait(smem_u32(&bar_empty[stage]), ((it / GM_NSTAGE) & 1u) ^ 1u, &s_abort);
+                    if (!ok) break;
+                    const uint32_t sA = smem0 + stage * GM_STAGE_BYTES, sB = sA + GM_A_BYTES;
+                    mbar_arrive_expect_tx(smem_u32(&bar_full[stage]), GM_STAGE_BYTES);
+                    tma_load_2d(sA, &tmap_a, ks * GM_BK, m0, smem_u32(&bar_full[stage]));
+                    tma_load_2d(sB, &tmap_b, ks * GM_BK, n0, smem_u32(&bar_full[stage]));
+                }
+            }
+        }
+    } else if (warp == 4) {
+        // ------------------------------------------------------------ MMA issuer
+        constexpr uint32_t IDESC = tc::idesc_bf16(GM_BM, GM_BN, 0);
+        const uint64_t dZero = tc::smem_desc_sw128(0);   // descriptor = this + (address >> 4)
+        uint32_t it = 0, local = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; ok && t < n_tiles; t += gridDim.x, ++local) {
+            const uint32_t acc = local & 1u;
+            // the epilogue must have drained this accumulator (two tiles ago)
+            ok = mbar_wait(smem_u32(&bar_acc_empty[acc]), ((local >> 1) & 1u) ^ 1u, &s_abort);
+            if (!ok) break;
+            tc::fence_after_sync();
+            for (int ks = 0; ks < k_steps; ++ks, ++it) {
+                const int stage = it % GM_NSTAGE;
+                ok = mbar_wait(smem_u32(&bar_full[stage]), (it / GM_NSTAGE) & 1u, &s_abort);
+                if (!ok) break;
+                if (elect_one()) {
+                    tc::fence_after_sync();
+                    const uint32_t sA = smem0 + stage * GM_STAGE_BYTES, sB = sA + GM_A_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < GM_BK / 16; ++kk)
+                        tc::mma_ss(tmem + acc * GM_BN, dZero + (uint64_t)((sA >> 4) + kk * 2),
+                                   dZero + (uint64_t)((sB >> 4) + kk * 2), IDESC, (ks > 0) || (kk > 0));
+                    tc::commit(smem_u32(&bar_empty[stage]));                       // the stage may be refilled
+                    if (ks == k_steps - 1) tc::commit(smem_u32(&bar_acc_full[acc]));  // the tile is complete
+                }
+                __syncwarp();
+            }
+        }
+    } else {
+        // ------------------------------------------------------ epilogue (warps 0..3)
+        const int row = tid;                                   // TMEM lane = output row inside the tile
+        const uint32_t lane_base = ((uint32_t)(warp * 32)) << 16;
+        uint32_t local = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; ok && t < n_tiles; t += gridDim.x, ++local) {
+            const uint32_t acc = local & 1u;
+            const int m0 = (t % tiles_m) * GM_BM, n0 = (t / tiles_m) * GM_BN;
+            ok = mbar_wait(smem_u32(&bar_acc_full[acc]), (local >> 1) & 1u, &s_abort);
+            if (!ok) break;
+            tc::fence_after_sync();
+            const int gm = m0 + row;
+            __nv_bfloat16* crow = p.c + (size_t)gm * p.N + n0;
+#pragma unroll 1
+            for (int c = 0; c < GM_BN / 32; ++c) {
+                uint32_t r[32];
+                tc::ld32(tmem + lane_base + acc * GM_BN + c * 32, r);
+                tc::wait_ld(r);
+                if (gm < p.M) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        const int col = n0 + c * 32 + v * 8;
+                        if (col < p.N) {        // N is a multiple of 8: a group of 8 columns is all in or all out
+                            uint4 o4;
+                            o4.x = pack_bf16(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+                            o4.y = pack_bf16(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+                            o4.z = pack_bf16(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+                            o4.w = pack_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+                            *reinterpret_cast<uint4*>(crow + c * 32 + v * 8) = o4;
+                        }
+                    }
+                }
+            }
+            // this warp has read its lanes of the accumulator
+            tc::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[acc]));
+        }
+    }
+
+    // common exit: everybody arrives here (all waits are bounded), then TMEM is freed
+    tc::fence_before_sync();
+    __syncthreads();
+    if (tid == 0 && s_abort && p.error_word) atomicExch(p.error_word, BN_ERR_TIMEOUT);
+    if (warp == 4) {
+        tc::fence_after_sync();
+        tc::tmem_dealloc(tmem, GM_TMEM_COLS);
+    }
+}
+
+}  // namespace bn
+
+using namespace bn;
+
+extern "C" int bn_gemm_bf16_nt(const void* a, const void* bt, void* c, int M, int N, int K, int* error_word,
+                               bn_stream_t stream) {
+    if (!a || !bt || !c) return fail(BN_ERR_INVALID_ARG, "bn_gemm_bf16_nt: null pointer");
+    if (M < 0 || N < 0 || K < 0) return fail(BN_ERR_INVALID_ARG, "bn_gemm_bf16_nt: bad shape M=%d N=%d K=%d", M, N, K);
+    if (N % 8 || K % 8)
+        return fail(BN_ERR_UNSUPPORTED, "bn_gemm_bf16_nt: N=%d and K=%d must be multiples of 8 (16-byte rows)", N, K);
+    if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(bt) | reinterpret_cast<uintptr_t>(c)) & 15)
+        return fail(BN_ERR_INVALID_ARG, "bn_gemm_bf16_nt: a/bt/c must be 16-byte aligned");
+    if (int rc = require_sm100()) return rc;
+    if (M == 0 || N == 0) return BN_OK;
+    if (K == 0) {
+        cudaError_t e = cudaMemsetAsync(c, 0, (size_t)M * N * 2, as_stream(stream));
+        return e == cudaSuccess ? BN_OK : fail(BN_ERR_CUDA, "bn_gemm_bf16_nt: %s", cudaGetErrorString(e));
+    }
+    CUtensorMap tmap_a, tmap_b;
+    {
+        const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M}, strides[1] = {(uint64_t)K * 2};
+        const uint32_t box[2] = {GM_BK, GM_BM};
+        if (int rc = make_tensor_map(&tmap_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a, dims, strides, box,
+                                     CU_TENSOR_MAP_SWIZZLE_128B))
+            return rc;
+    }
+    {
+        const uint64_t dims[2] = {(uint64_t)K, (uint64_t)N}, strides[1] = {(uint64_t)K * 2};
+        const uint32_t box[2] = {GM_BK, GM_BN};
+        if (int rc = make_tensor_map(&tmap_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, bt, dims, strides, box,
+                                     CU_TENSOR_MAP_SWIZZLE_128B))
+            return rc;
+    }
+    static thread_local int configured_dev = -1;
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    if (configured_dev != dev) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_nt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GM_SMEM_BYTES);
+        if (e != cudaSuccess) return fail(BN_ERR_CUDA, "cudaFuncSetAttribute(gemm): %s", cudaGetErrorString(e));
+        configured_dev = dev;
+    }
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long n_tiles = (long long)((M + GM_BM - 1) / GM_BM) * ((N + GM_BN - 1) / GM_BN);
+    GemmParams p{static_cast<__nv_bfloat16*>(c), error_word, M, N, K};
+    const unsigned grid = (unsigned)(n_tiles < sms ? n_tiles : sms);
+    gemm_bf16_nt_kernel<<<grid, GM_THREADS, GM_SMEM_BYTES, as_stream(stream)>>>(tmap_a, tmap_b, p);
+    return launch_status("bn_gemm_bf16_nt");
+}

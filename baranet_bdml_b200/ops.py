@@ -70,6 +70,24 @@ def attn_prefill_bf16(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scal
     return out
 
 
+def gemm_bf16_nt(a: torch.Tensor, bt: torch.Tensor, *, out: Optional[torch.Tensor] = None,
+                 error_word: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a (M,K) bf16 @ bt (N,K)^T bf16 -> (M,N) bf16, fp32 accumulation: the layer's projections `x @ W` with the weight
+    stored as (out_features, in_features)."""
+    _need(a, torch.bfloat16, "gemm_bf16_nt(a)")
+    _need(bt, torch.bfloat16, "gemm_bf16_nt(bt)")
+    if a.dim() != 2 or bt.dim() != 2 or a.shape[1] != bt.shape[1]:
+        raise RuntimeError(f"MatMul: inner dimensions mismatch {tuple(a.shape)} x {tuple(bt.shape)}^T")
+    M, K = a.shape
+    N = bt.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    _need(out, torch.bfloat16, "gemm_bf16_nt(out)")
+    _lib.check(_lib.load().bn_gemm_bf16_nt(a.data_ptr(), bt.data_ptr(), out.data_ptr(), M, N, K,
+                                           error_word.data_ptr() if error_word is not None else None, _stream()))
+    return out
+
+
 class HostPrefillPipeline:
     """Prefill attention for callers whose q/k/v/out live in (pinned) HOST memory, as the reference's tensors do
     before `to_device()` (mygrad tensors are created on the host and copied per call).  Every `submit` copies that

@@ -92,6 +92,16 @@ BN_API int bn_mm_f32(const float* A, int64_t a_rs, int64_t a_cs, const float* B,
 BN_API int bn_rope_f32(const float* x, int64_t x_rs, int64_t x_cs, float* y, int64_t y_rs, int64_t y_cs, int rows,
                 int cols, int head_dim, float theta, int position_offset, bn_stream_t stream);
 
+/* C (M,N) bf16 = A (M,K) bf16 @ Bt (N,K)^T bf16, fp32 accumulation (tcgen05 tensor cores, accumulators in tensor
+ * memory).  Dense row-major operands; Bt is the weight stored transposed, (out_features, in_features), so both
+ * operands are contiguous along K.  N and K multiples of 8, pointers 16-byte aligned; M, N, K otherwise free.
+ * `error_word` (device int, may be NULL) receives BN_ERR_TIMEOUT if a bounded device-side wait runs out.
+ * The projection GEMMs of the attention layer on bf16 operands: q/k/v/o_proj, `hidden_states @ W`
+ * (mygrad/llama/llama_layers.py:157-159,186), reference operator op_mm (src/ops/op_mm.cuh:39-57), whose fp32
+ * bit-compatible replacement is bn_mm_f32 above. */
+BN_API int bn_gemm_bf16_nt(const void* a, const void* bt, void* c, int M, int N, int K, int* error_word,
+                           bn_stream_t stream);
+
 /* y = x / sqrt(mean(x^2) + eps) * w, row by row; x, y (rows, hidden), w (hidden) with element strides.
  * Same arithmetic order as the reference kernel (256 partial fused-multiply-add chains, its reduction tree, IEEE
  * division and square root), so the result is the reference's bit for bit.
