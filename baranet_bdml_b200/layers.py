@@ -126,3 +126,55 @@ class GroupedQueryAttention:
 
     def parameters(self):
         return [self.q_proj, self.k_proj, self.v_proj, self.o_proj]
+
+
+class GroupedQueryAttentionBF16:
+    """The same layer on the bf16 tensor-core path, per-head grouped-query attention (BASELINE configs 2-4): the
+    four projections are `bn_gemm_bf16_nt` (weights held transposed, (out_features, in_features), bf16), the core is
+    `bn_attn_prefill_bf16` (RoPE, causal softmax, P V fused).  Same constructor arguments, attribute names and
+    `__call__(hidden_states, position_offset, use_causal_mask)` as mygrad/llama/llama_layers.py:46-191;
+    hidden_states is a torch bf16 tensor (B, S, hidden) or (S, hidden) on the GPU.  Inference only."""
+
+    def __init__(self, config, is_cuda: bool = True):
+        import torch
+        if not is_cuda:
+            raise RuntimeError("Attention: only GPU implementation available")
+        self.config = config
+        self.num_heads = config.num_attention_heads
+        self.num_kv_heads = config.num_key_value_heads
+        self.head_dim = config.head_dim
+        self.hidden_size = config.hidden_size
+        kv = self.num_kv_heads * self.head_dim
+
+        def init(in_features, out_features):     # Xavier/Glorot as llama_layers.py:80-85, stored transposed
+            std = np.sqrt(2.0 / (in_features + out_features))
+            w = np.random.randn(in_features, out_features).astype(np.float32) * std
+            return torch.from_numpy(np.ascontiguousarray(w.T)).cuda().to(torch.bfloat16)
+
+        self.q_proj, self.k_proj = init(self.hidden_size, self.hidden_size), init(self.hidden_size, kv)
+        self.v_proj, self.o_proj = init(self.hidden_size, kv), init(self.hidden_size, self.hidden_size)
+        self.rotary_emb = RotaryEmbedding(self.head_dim, max_position_embeddings=config.max_position_embeddings,
+                                          base=config.rope_theta)
+        self.scale = 1.0 / np.sqrt(self.head_dim)
+        self._ws = None
+
+    def __call__(self, hidden_states, position_offset: int = 0, use_causal_mask: bool = True):
+        from . import ops
+        x = hidden_states if hidden_states.dim() == 3 else hidden_states[None]
+        B, S, H = x.shape
+        if H != self.hidden_size:
+            raise RuntimeError("Attention: hidden size mismatch")
+        x2 = x.reshape(B * S, H)
+        q = ops.gemm_bf16_nt(x2, self.q_proj).view(B, S, self.num_heads, self.head_dim)
+        k = ops.gemm_bf16_nt(x2, self.k_proj).view(B, S, self.num_kv_heads, self.head_dim)
+        v = ops.gemm_bf16_nt(x2, self.v_proj).view(B, S, self.num_kv_heads, self.head_dim)
+        key = (B, S)
+        if self._ws is None or self._ws[0] != key:
+            self._ws = (key, ops.prefill_workspace(B, S, self.num_heads, self.num_kv_heads, self.head_dim, x.device))
+        attn = ops.attn_prefill_bf16(q, k, v, scale=float(self.scale), theta=self.rotary_emb.base,
+                                     position_offset=position_offset, causal=use_causal_mask, workspace=self._ws[1])
+        out = ops.gemm_bf16_nt(attn.view(B * S, self.num_heads * self.head_dim), self.o_proj).view(B, S, H)
+        return out if hidden_states.dim() == 3 else out[0]
+
+    def parameters(self):
+        return [self.q_proj, self.k_proj, self.v_proj, self.o_proj]

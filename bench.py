@@ -370,6 +370,38 @@ def measure_rmsnorm(torch, args, rank, world, dist, reduce_max, pk):
     return out
 
 
+def measure_gemm(torch, ops, args, rank, world, dist, reduce_max, pk):
+    """Row N1: the q_proj / o_proj GEMM of the layer at the token count of config 2: (16384, 2048) @ (2048, 2048)^T,
+    bf16 operands, fp32 accumulation.  Inputs rotate over 3 activation buffers (3 x 67 MB + weights > L2)."""
+    M, N, K = PREFILL["B"] * PREFILL["S"], 2048, 2048
+    g = torch.Generator(device="cuda").manual_seed(7 + rank)
+    xs = [torch.randn((M, K), generator=g, device="cuda").to(torch.bfloat16) for _ in range(3)]
+    w = (torch.randn((N, K), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def step(i):
+        ops.gemm_bf16_nt(xs[i % 3], w, out=out, error_word=err)
+
+    steps = max(20, args.steps // 2)
+    ms = reduce_max(time_loop(torch, step, steps, 3, dist))
+    if int(err.item()) != 0:
+        raise RuntimeError("gemm: a bounded device-side wait ran out")
+    flops = 2.0 * M * N * K
+    tf = flops * world / (ms * 1e-3) / 1e12
+    return {
+        "metric": "projection_gemm_tflops", "value": tf, "unit": "TFLOP/s", "ms_per_step": ms, "steps": steps,
+        "n_gpus": world, "dtype": "bf16",
+        "config": {"workload": "q_proj / o_proj GEMM of the layer (row N1): (16384, 2048) @ (2048, 2048)^T, bf16 in, "
+                               "fp32 accumulate, bf16 out", "flops_per_step_per_gpu": flops,
+                   "l2": "activations rotate over 3 buffers of 67 MB"},
+        "roofline": {"bound": "tensor", "achieved": tf / world, "peak": pk["tensor"], "unit": "TFLOP/s",
+                     "frac": tf / world / pk["tensor"], "traffic": None,
+                     "peak_source": pk["source"] + " (bf16 burst)", "kernel": "gemm_bf16_nt_kernel"},
+        "gpu_launches": steps,
+    }
+
+
 def measure_longctx(torch, args, rank, world, dist, reduce_max, pk):
     """BASELINE config 4: batch 4, one 262144-token sequence each, 32q/4kv heads.  The sequence is cut into
     contiguous page-aligned token ranges, one per GPU; each GPU decodes over its range (normalised partial
@@ -458,6 +490,10 @@ def run_ours(args):
                 result["rmsnorm"] = measure_rmsnorm(torch, args, rank, world, dist, reduce_max, pk)
             except Exception as e:
                 result["rmsnorm"] = {"error": repr(e)}
+            try:
+                result["gemm"] = measure_gemm(torch, ops, args, rank, world, dist, reduce_max, pk)
+            except Exception as e:
+                result["gemm"] = {"error": repr(e)}
     if rank == 0:
         result["clocks"] = sampler.stop()
         if world == 1 and not args.no_cpu_baseline and not args.decode_only:

@@ -59,3 +59,28 @@ def test_gemm_rejects_bad_arguments(lib):
                          torch.zeros((8, 8), dtype=torch.bfloat16, device="cuda"))
     with pytest.raises(RuntimeError, match="only GPU implementation available"):
         ops.gemm_bf16_nt(torch.zeros((16, 16), dtype=torch.bfloat16), torch.zeros((8, 16), dtype=torch.bfloat16))
+
+
+def test_bf16_layer_against_staged_fp64_restatement(lib):
+    """The whole attention layer on the bf16 path (4 tcgen05 GEMMs + the fused attention core) against the oracle's
+    per-head attention with fp64 arithmetic and a bf16 rounding wherever the kernels round (q, k, v, attention output,
+    layer output).  Gate 2e-2 absolute, the bf16 tolerance of the path."""
+    import torch
+    from baranet_bdml_b200.layers import GroupedQueryAttentionBF16, LLaMAConfig
+    cfg = LLaMAConfig(hidden_size=512, num_attention_heads=8, num_key_value_heads=2, intermediate_size=1024,
+                      num_hidden_layers=1)
+    np.random.seed(5)
+    layer = GroupedQueryAttentionBF16(cfg)
+    B, S = 2, 300
+    rng = np.random.default_rng(8)
+    x = R.round_bf16(rng.standard_normal((B, S, cfg.hidden_size), dtype=np.float32))
+    got = layer(torch.from_numpy(x).cuda().to(torch.bfloat16), position_offset=2).float().cpu().numpy()
+    wq, wk, wv, wo = (w.float().cpu().numpy().astype(np.float64) for w in (layer.q_proj, layer.k_proj, layer.v_proj,
+                                                                          layer.o_proj))
+    for b in range(B):
+        xb = x[b].astype(np.float64)
+        q, k, v = (R.round_bf16((xb @ w.T).astype(np.float32)) for w in (wq, wk, wv))
+        attn = R.attention_per_head(q, k, v, num_heads=8, num_kv_heads=2, head_dim=64, position_offset=2, causal=True,
+                                    dtype=np.float64, round_rope_bf16=True)
+        ref = R.round_bf16(attn.astype(np.float32)).astype(np.float64) @ wo.T
+        assert np.abs(got[b] - ref).max() <= 2e-2, np.abs(got[b] - ref).max()
