@@ -38,7 +38,8 @@ _emit = print
 PREFILL = dict(B=8, S=2048, Hq=32, Hkv=4, D=64)
 DECODE = dict(B=64, Hq=32, Hkv=4, D=64, Lmin=1024, Lmax=4096, page=16)
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
-NCU_TRAFFIC = {"prefill_kernel": 85.555e6 + 27.917e6, "decode_paged_kernel": 163.424e6 + 3.766e6}
+NCU_TRAFFIC = {"prefill_kernel": 85.475e6 + 27.995e6, "decode_paged_kernel": 163.426e6 + 3.645e6,
+               "rmsnorm_kernel": 268.471e6 + 224.065e6, "gemm_bf16_nt_kernel": 121.810e6 + 46.803e6}
 
 
 def peaks():
@@ -345,8 +346,9 @@ def measure_rmsnorm(torch, args, rank, world, dist, reduce_max, pk):
                                "BASELINE config 2; one launch, bit-identical to the reference's op_add + op_rmsnorm",
                    "algorithmic_bytes_per_step": bytes_fused, "l2": "537 MB per step, larger than L2"},
         "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": pk["hbm"], "unit": "GB/s",
-                     "frac": gbs / world / pk["hbm"], "traffic": None, "peak_source": pk["source"],
-                     "kernel": "rmsnorm_kernel"},
+                     "frac": gbs / world / pk["hbm"], "traffic": NCU_TRAFFIC["rmsnorm_kernel"],
+                     "traffic_unit": "bytes of DRAM traffic per launch (ncu capture, profiles/rmsnorm_kernel_16384x2048.md)",
+                     "peak_source": pk["source"], "kernel": "rmsnorm_regs_kernel"},
         "rmsnorm_only": {"value": bytes_plain * world / (ms_plain * 1e-3) / 1e9, "unit": "GB/s",
                          "ms_per_step": ms_plain, "algorithmic_bytes_per_step": bytes_plain},
         "gpu_launches": 2 * steps,
@@ -396,7 +398,9 @@ def measure_gemm(torch, ops, args, rank, world, dist, reduce_max, pk):
                                "fp32 accumulate, bf16 out", "flops_per_step_per_gpu": flops,
                    "l2": "activations rotate over 3 buffers of 67 MB"},
         "roofline": {"bound": "tensor", "achieved": tf / world, "peak": pk["tensor"], "unit": "TFLOP/s",
-                     "frac": tf / world / pk["tensor"], "traffic": None,
+                     "frac": tf / world / pk["tensor"], "traffic": NCU_TRAFFIC["gemm_bf16_nt_kernel"],
+                     "traffic_unit": "bytes of DRAM traffic per launch (ncu capture, "
+                                     "profiles/gemm_bf16_nt_kernel_16384x2048x2048.md)",
                      "peak_source": pk["source"] + " (bf16 burst)", "kernel": "gemm_bf16_nt_kernel"},
         "gpu_launches": steps,
     }
