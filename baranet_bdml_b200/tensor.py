@@ -153,6 +153,36 @@ class TensorF:
                                    self.h, self.w, head_dim, theta, position_offset, _stream_ptr()))
         return out
 
+    def argmax(self) -> "TensorU32":
+        """Per-row argmax, shape (h, 1): op_argmax (src/ops/op_reduction.cuh:196-210; TensorF.argmax,
+        src/py_tensor_shim.hh:220-224) -> bn_argmax_rows_f32.  Ties keep the first index."""
+        self._require_device("argmax")
+        out = TensorU32(self.h, 1)
+        _lib.check(_lib.load().bn_argmax_rows_f32(self._ptr(), self.stride_h, self.stride_w, out.data.data_ptr(),
+                                                  self.h, self.w, _stream_ptr()))
+        return out
+
+    def gather_rows(self, ids) -> "TensorF":
+        """self[ids[i], :] for every i, on the device -> bn_embedding_gather_f32: the device-side form of
+        LLaMAModel.embed (mygrad/llama/llama_model.py:58-78).  ids: uint32 numpy array, TensorU32 or torch int tensor."""
+        self._require_device("embed")
+        if self.stride_w != 1:
+            raise RuntimeError("embed: the table must have contiguous rows")
+        if isinstance(ids, TensorU32):
+            dev_ids = ids.data.reshape(-1)
+        elif isinstance(ids, torch.Tensor):
+            dev_ids = ids.to(device=self.base.device, dtype=torch.int32).reshape(-1).contiguous()
+        else:
+            dev_ids = torch.from_numpy(np.ascontiguousarray(ids, dtype=np.uint32).view(np.int32)).to(self.base.device)
+        n = int(dev_ids.numel())
+        out = TensorF(n, self.w, True)
+        err = torch.zeros(1, dtype=torch.int32, device=self.base.device)
+        _lib.check(_lib.load().bn_embedding_gather_f32(self._ptr(), self.stride_h, dev_ids.data_ptr(), out._ptr(),
+                                                       out.stride_h, n, self.w, self.h, err.data_ptr(), _stream_ptr()))
+        if int(err.item()) != 0:
+            raise IndexError("index out of range in embedding gather")
+        return out
+
     def rmsnorm(self, weight: "TensorF", eps: float = 1e-6) -> "TensorF":
         """op_rmsnorm (src/ops/op_rmsnorm.cuh:134-157; TensorF.rmsnorm, src/py_tensor_shim.hh:256-260)
         -> bn_rmsnorm_f32.  weight is (1, hidden)."""
@@ -207,6 +237,22 @@ class TensorF:
         return out
 
 
+class TensorU32:
+    """Dense (h, w) uint32 tensor on the device (bten.TensorU32): what argmax returns."""
+
+    def __init__(self, h: int, w: int):
+        self.h, self.w = int(h), int(w)
+        self.data = torch.zeros((self.h, self.w), dtype=torch.int32, device="cuda")   # same bits as uint32
+        self.on_device = True
+
+    @property
+    def shape(self) -> Tuple[int, int]:
+        return (self.h, self.w)
+
+    def to_numpy(self) -> np.ndarray:
+        return self.data.cpu().numpy().view(np.uint32).copy()
+
+
 class AGTensor:
     """Mirror of mygrad.engine.AGTensor for the (inference-only) attention path."""
 
@@ -242,6 +288,10 @@ class AGTensor:
 
     def rope(self, position_offset: int = 0, head_dim: int = 64, theta: float = 10000.0) -> "AGTensor":
         return AGTensor(self.data.rope(position_offset, head_dim, theta), (self,), "rope", requires_grad=False)
+
+    def argmax(self):
+        """AGTensor.argmax (mygrad/engine.py:355-361): per-row argmax, shape (N, 1), not differentiable."""
+        return self.data.argmax()
 
     def rmsnorm(self, weight: "AGTensor", eps: float = 1e-6) -> "AGTensor":
         """AGTensor.rmsnorm of the reference (forward only here)."""

@@ -372,6 +372,47 @@ def measure_rmsnorm(torch, args, rank, world, dist, reduce_max, pk):
     return out
 
 
+def measure_embed_argmax(torch, args, rank, world, dist, reduce_max, pk):
+    """Row N2: greedy argmax over a prefill's logits (2048 rows x 32000, 262 MB read) and the embedding gather of
+    config 2's 16384 tokens (134 MB read + 134 MB written), both on the device."""
+    from baranet_bdml_b200 import _lib
+    L = _lib.load()
+    rows, vocab, hidden, n_tok = PREFILL["S"], 32000, 2048, PREFILL["B"] * PREFILL["S"]
+    g = torch.Generator(device="cuda").manual_seed(5 + rank)
+    logits = torch.randn((rows, vocab), generator=g, device="cuda")
+    idx = torch.zeros((rows,), dtype=torch.int32, device="cuda")
+    table = torch.randn((vocab, hidden), generator=g, device="cuda")
+    ids = torch.randint(0, vocab, (n_tok,), generator=g, device="cuda", dtype=torch.int32)
+    emb = torch.empty((n_tok, hidden), device="cuda")
+
+    def amax(i):
+        _lib.check(L.bn_argmax_rows_f32(logits.data_ptr(), vocab, 1, idx.data_ptr(), rows, vocab,
+                                        torch.cuda.current_stream().cuda_stream))
+
+    def gather(i):
+        _lib.check(L.bn_embedding_gather_f32(table.data_ptr(), hidden, ids.data_ptr(), emb.data_ptr(), hidden, n_tok,
+                                             hidden, vocab, None, torch.cuda.current_stream().cuda_stream))
+
+    steps = max(20, args.steps // 2)
+    ms_a = reduce_max(time_loop(torch, amax, steps, 3, dist))
+    ms_g = reduce_max(time_loop(torch, gather, steps, 3, dist))
+    b_a, b_g = rows * vocab * 4, 2 * n_tok * hidden * 4
+    gbs = b_a * world / (ms_a * 1e-3) / 1e9
+    return {
+        "metric": "argmax_hbm_gbs", "value": gbs, "unit": "GB/s", "ms_per_step": ms_a, "steps": steps, "n_gpus": world,
+        "dtype": "f32",
+        "config": {"workload": "per-row argmax of 2048 x 32000 fp32 logits (row N2), first maximum as op_argmax",
+                   "algorithmic_bytes_per_step": b_a, "l2": "262 MB per step, larger than L2"},
+        "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": pk["hbm"], "unit": "GB/s",
+                     "frac": gbs / world / pk["hbm"], "traffic": None, "peak_source": pk["source"],
+                     "kernel": "argmax_rows_kernel"},
+        "embedding_gather": {"value": b_g * world / (ms_g * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_g,
+                             "algorithmic_bytes_per_step": b_g,
+                             "workload": "16384 token rows of 2048 fp32 from a 32000-row table"},
+        "gpu_launches": 2 * steps,
+    }
+
+
 def measure_gemm(torch, ops, args, rank, world, dist, reduce_max, pk):
     """Row N1: the q_proj / o_proj GEMM of the layer at the token count of config 2: (16384, 2048) @ (2048, 2048)^T,
     bf16 operands, fp32 accumulation.  Inputs rotate over 3 activation buffers (3 x 67 MB + weights > L2)."""
@@ -494,6 +535,10 @@ def run_ours(args):
                 result["rmsnorm"] = measure_rmsnorm(torch, args, rank, world, dist, reduce_max, pk)
             except Exception as e:
                 result["rmsnorm"] = {"error": repr(e)}
+            try:
+                result["embed_argmax"] = measure_embed_argmax(torch, args, rank, world, dist, reduce_max, pk)
+            except Exception as e:
+                result["embed_argmax"] = {"error": repr(e)}
             try:
                 result["gemm"] = measure_gemm(torch, ops, args, rank, world, dist, reduce_max, pk)
             except Exception as e:

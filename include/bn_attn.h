@@ -92,6 +92,22 @@ BN_API int bn_mm_f32(const float* A, int64_t a_rs, int64_t a_cs, const float* B,
 BN_API int bn_rope_f32(const float* x, int64_t x_rs, int64_t x_cs, float* y, int64_t y_rs, int64_t y_cs, int rows,
                 int cols, int head_dim, float theta, int position_offset, bn_stream_t stream);
 
+/* out[i, :] = table[ids[i], :] on the device (fp32 rows, element row strides).  An id >= vocab yields a zero row
+ * and BN_ERR_INVALID_ARG in *error_word (device int, may be NULL).
+ * Replaces LLaMAModel.embed (mygrad/llama/llama_model.py:58-78), which copies the whole table to the host, gathers
+ * there row by row and uploads the result. */
+BN_API int bn_embedding_gather_f32(const float* table, int64_t table_rs, const uint32_t* ids, float* out,
+                                   int64_t out_rs, int n_ids, int hidden, int vocab, int* error_word,
+                                   bn_stream_t stream);
+
+/* out[r] = index of the first maximum of row r of x (rows, cols) fp32 with element strides: element 0 stands unless
+ * a later element is strictly greater, so ties keep the first index and a NaN wins only at index 0.
+ * Replaces op_argmax (src/ops/op_reduction.cuh:196-210, MaxAccumFunc :5-19; TensorF.argmax,
+ * src/py_tensor_shim.hh:220-224), for greedy decoding on the device instead of downloading the logits
+ * (mygrad/llama/llama_model.py:136-160). */
+BN_API int bn_argmax_rows_f32(const float* x, int64_t x_rs, int64_t x_cs, uint32_t* out, int rows, int cols,
+                              bn_stream_t stream);
+
 /* C (M,N) bf16 = A (M,K) bf16 @ Bt (N,K)^T bf16, fp32 accumulation (tcgen05 tensor cores, accumulators in tensor
  * memory).  Dense row-major operands; Bt is the weight stored transposed, (out_features, in_features), so both
  * operands are contiguous along K.  N and K multiples of 8, pointers 16-byte aligned; M, N, K otherwise free.

@@ -201,6 +201,15 @@ def gpu_rope(x, head_dim=64, theta=10000.0, position_offset=0):
     return out
 
 
+def gpu_argmax(x):
+    """The reference's own op_argmax on the GPU (needs oracle/_ref): (rows, 1) uint32."""
+    x = _f32(x)
+    out = np.zeros((x.shape[0], 1), dtype=np.uint32)
+    _gcheck(gpu().refgpu_argmax(_p(x), C.c_int(x.shape[0]), C.c_int(x.shape[1]),
+                                out.ctypes.data_as(C.POINTER(C.c_uint32))))
+    return out
+
+
 def gpu_rmsnorm(x, w, eps=1e-6):
     """The reference's own op_rmsnorm on the GPU (needs oracle/_ref)."""
     x, w = _f32(x), _f32(w).reshape(-1)

@@ -335,3 +335,29 @@ def rmsnorm(x: np.ndarray, weight: np.ndarray, eps: float = 1e-6, residual: np.n
     rms = np.sqrt((s * s).mean(axis=1, keepdims=True) + dtype(eps))
     y = s / rms * w
     return y if residual is None else (s, y)
+
+
+def argmax_rows(x: np.ndarray) -> np.ndarray:
+    """Per-row argmax with the reference's sequential rule: op_argmax (src/ops/op_reduction.cuh:196-210) runs
+    MaxAccumFunc (:5-19) over the columns of a row in order -- accum starts as element 0 and is replaced only by a
+    strictly greater value, so ties keep the first index and a NaN wins only at index 0.  Returns (rows, 1) uint32
+    like TensorF.argmax (src/py_tensor_shim.hh:220-224)."""
+    x = np.asarray(x, dtype=F32)
+    out = np.zeros((x.shape[0], 1), dtype=np.uint32)
+    for r in range(x.shape[0]):
+        acc, ind = x[r, 0], 0
+        for c in range(1, x.shape[1]):
+            if x[r, c] > acc:
+                acc, ind = x[r, c], c
+        out[r, 0] = ind
+    return out
+
+
+def embed(table: np.ndarray, input_ids: np.ndarray) -> np.ndarray:
+    """LLaMAModel.embed (mygrad/llama/llama_model.py:58-78): row i of the result is row input_ids[i] of the
+    embedding table (the reference gathers on the host and uploads)."""
+    table = np.asarray(table, dtype=F32)
+    out = np.zeros((len(input_ids), table.shape[1]), dtype=F32)
+    for i, token_id in enumerate(input_ids):
+        out[i] = table[int(token_id)]
+    return out

@@ -25,6 +25,7 @@
 #include "ops/op_elemwise.cuh"
 #include "ops/op_mm.cuh"
 #include "ops/op_mm_optimized.cuh"
+#include "ops/op_reduction.cuh"
 #include "ops/op_rmsnorm.cuh"
 #include "ops/op_rope.cuh"
 #include "ops/op_softmax.cuh"
@@ -103,6 +104,18 @@ int refgpu_inv_freq(int head_dim, float theta, float* out) {
         CUDA_OK(cudaDeviceSynchronize());
         CUDA_OK(cudaMemcpy(out, d, sizeof(float) * (head_dim / 2), cudaMemcpyDeviceToHost));
         cudaFree(d);
+        return 0;
+    } catch (const std::exception& e) { g_err = e.what(); return 1; }
+}
+
+// op_argmax (src/ops/op_reduction.cuh:196-210): per-row index of the first maximum, (rows, 1) uint32
+int refgpu_argmax(const float* x, int rows, int cols, unsigned int* out) {
+    try {
+        Tensor<float> in = upload(x, rows, cols);
+        Tensor<unsigned int> idx(rows, 1, true);
+        op_argmax<float, unsigned int>(in, idx);
+        CUDA_OK(cudaDeviceSynchronize());
+        CUDA_OK(cudaMemcpy(out, idx.rawp, sizeof(unsigned int) * rows, cudaMemcpyDeviceToHost));
         return 0;
     } catch (const std::exception& e) { g_err = e.what(); return 1; }
 }

@@ -61,6 +61,14 @@ def main(out_dir):
         w = (1 + 0.1 * rng.standard_normal(hidden)).astype(np.float32)
         save(f"rmsnorm_r{rows}_h{hidden}", kind="rmsnorm", x=x, w=w, eps=np.float32(1e-6),
              out=cref.gpu_rmsnorm(x, w, 1e-6))
+    # op_argmax (src/ops/op_reduction.cuh): random rows, ties, NaN at and after element 0, a row of -inf
+    x = rng.standard_normal((12, 97), dtype=np.float32)
+    x[1, [4, 40, 90]] = 7.0
+    x[2, 10] = np.nan
+    x[3, 0] = np.nan
+    x[4, :] = -np.inf
+    x[5, 96] = 9.0
+    save("argmax_r12_c97", kind="argmax", x=x, out=cref.gpu_argmax(x))
     # the reference's own decoder-layer test shape (test_llama.py:142-165): hidden 128, 4 heads / 2 KV heads
     S, hidden, Hq, Hkv, D = 4, 128, 4, 2, 32
     x, wq, wk, wv, wo = layer_inputs_from_seed(7, S, hidden, Hq, Hkv, D)

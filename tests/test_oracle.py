@@ -117,6 +117,9 @@ def test_oracle_matches_reference_cuda_golden(path, cref):
         pytest.skip("no golden fixtures generated yet")
     g = np.load(path)
     kind = str(g["kind"])
+    if kind == "argmax":
+        assert np.array_equal(R.argmax_rows(g["x"]), g["out"]), path
+        return
     if kind == "rmsnorm":
         # fp32 with the reference's own arithmetic order: bit for bit
         got = cref.rmsnorm(g["x"], g["w"], float(g["eps"]))
@@ -163,3 +166,17 @@ def test_rmsnorm_restatements_agree(cref):
         assert np.array_equal(y, cref.rmsnorm(x + r, w, 1e-6))      # the fused form IS add followed by norm
     z = np.zeros((2, 64), dtype=np.float32)
     assert np.array_equal(cref.rmsnorm(z, np.ones(64, np.float32), 1e-6), z)
+
+
+def test_argmax_and_embed_restatements():
+    """The sequential first-maximum rule against numpy's argmax (the same rule on NaN-free data) and its NaN / tie
+    cases; the host gather."""
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((20, 300)).astype(np.float32)
+    x[3, [5, 9]] = 50.0
+    assert np.array_equal(R.argmax_rows(x)[:, 0], np.argmax(x, axis=1))
+    y = np.array([[np.nan, 3.0, 1.0], [1.0, np.nan, 2.0], [-np.inf, -np.inf, -np.inf]], dtype=np.float32)
+    assert list(R.argmax_rows(y)[:, 0]) == [0, 2, 0]
+    table = rng.standard_normal((11, 4)).astype(np.float32)
+    ids = np.array([10, 0, 3, 3], dtype=np.uint32)
+    assert np.array_equal(R.embed(table, ids), table[ids])
