@@ -12,6 +12,10 @@
 // Output tile 128 x 256; the fp32 accumulator (256 TMEM columns) is double buffered, so the epilogue of one tile
 // runs under the main loop of the next.  Tiles are walked N-panel by N-panel with M fastest, so the CTAs that run
 // together share their Bt panel in L2.  Edges: TMA zero-fills loads beyond M, N, K; stores are bounds-checked.
+// Epilogue variants: plain (C = the accumulator as bf16) and SwiGLU (`MLP.__call__`, mygrad/llama/llama_layers.py:217-232,
+// SiLU as op_silu.cuh:7-15): Bt holds, per 256-row tile, 128 rows of the gate weight followed by the 128 rows of the up
+// weight for the same intermediate indices, so one thread finds gate and up of an output element in the same
+// accumulator row and writes silu(gate) * up -- the two GEMMs, the activation and the product in one launch.
 // Every mbarrier wait is bounded; on expiry the kernel raises the caller's error word, frees TMEM and returns.
 #include "common.cuh"
 #include "ptx.cuh"
@@ -34,9 +38,13 @@ constexpr uint32_t GM_TMEM_COLS = 512;                 // two accumulators of 25
 struct GemmParams {
     __nv_bfloat16* c;
     int* error_word;       // optional
-    int M, N, K;
+    int M, N, K;           // N = rows of Bt
+    int n_out;             // columns of C: N (plain) or the intermediate size (SwiGLU)
 };
 
+constexpr int EPI_PLAIN = 0, EPI_SWIGLU = 1;
+
+template <int EPI>
 __global__ void __launch_bounds__(GM_THREADS, 1)
 gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const GemmParams p) {
@@ -134,23 +142,58 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             if (!ok) break;
             tc::fence_after_sync();
             const int gm = m0 + row;
-            __nv_bfloat16* crow = p.c + (size_t)gm * p.N + n0;
+            if (EPI == EPI_PLAIN) {
+                __nv_bfloat16* crow = p.c + (size_t)gm * p.n_out + n0;
 #pragma unroll 1
-            for (int c = 0; c < GM_BN / 32; ++c) {
-                uint32_t r[32];
-                tc::ld32(tmem + lane_base + acc * GM_BN + c * 32, r);
-                tc::wait_ld(r);
-                if (gm < p.M) {
+                for (int c = 0; c < GM_BN / 32; ++c) {
+                    uint32_t r[32];
+                    tc::ld32(tmem + lane_base + acc * GM_BN + c * 32, r);
+                    tc::wait_ld(r);
+                    if (gm < p.M) {
 #pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        const int col = n0 + c * 32 + v * 8;
-                        if (col < p.N) {        // N is a multiple of 8: a group of 8 columns is all in or all out
-                            uint4 o4;
-                            o4.x = pack_bf16(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
-                            o4.y = pack_bf16(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
-                            o4.z = pack_bf16(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
-                            o4.w = pack_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
-                            *reinterpret_cast<uint4*>(crow + c * 32 + v * 8) = o4;
+                        for (int v = 0; v < 4; ++v) {
+                            const int col = n0 + c * 32 + v * 8;
+                            if (col < p.n_out) {    // a multiple of 8: a group of 8 columns is all in or all out
+                                uint4 o4;
+                                o4.x = pack_bf16(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+                                o4.y = pack_bf16(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+                                o4.z = pack_bf16(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+                                o4.w = pack_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+                                *reinterpret_cast<uint4*>(crow + c * 32 + v * 8) = o4;
+                            }
+                        }
+                    }
+                }
+            } else {
+                // accumulator columns [0,128) = gate, [128,256) = up, of intermediate indices n0/2 .. n0/2 + 127
+                const int i0 = n0 / 2;
+                __nv_bfloat16* crow = p.c + (size_t)gm * p.n_out + i0;
+#pragma unroll 1
+                for (int c = 0; c < GM_BN / 64; ++c) {
+                    uint32_t g[32], u[32];
+                    tc::ld32(tmem + lane_base + acc * GM_BN + c * 32, g);
+                    tc::ld32(tmem + lane_base + acc * GM_BN + GM_BN / 2 + c * 32, u);
+                    tc::wait_ld(g);
+                    tc::wait_ld(u);
+                    if (gm < p.M) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            const int col = i0 + c * 32 + v * 8;
+                            if (col < p.n_out) {
+                                float h[8];
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) {
+                                    const float gv = __uint_as_float(g[v * 8 + e]);
+                                    // silu(g) * up, silu(g) = g / (1 + exp(-g))
+                                    h[e] = __fdividef(gv, 1.f + __expf(-gv)) * __uint_as_float(u[v * 8 + e]);
+                                }
+                                uint4 o4;
+                                o4.x = pack_bf16(h[0], h[1]);
+                                o4.y = pack_bf16(h[2], h[3]);
+                                o4.z = pack_bf16(h[4], h[5]);
+                                o4.w = pack_bf16(h[6], h[7]);
+                                *reinterpret_cast<uint4*>(crow + c * 32 + v * 8) = o4;
+                            }
                         }
                     }
                 }
@@ -176,19 +219,19 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
 using namespace bn;
 
-extern "C" int bn_gemm_bf16_nt(const void* a, const void* bt, void* c, int M, int N, int K, int* error_word,
-                               bn_stream_t stream) {
-    if (!a || !bt || !c) return fail(BN_ERR_INVALID_ARG, "bn_gemm_bf16_nt: null pointer");
-    if (M < 0 || N < 0 || K < 0) return fail(BN_ERR_INVALID_ARG, "bn_gemm_bf16_nt: bad shape M=%d N=%d K=%d", M, N, K);
-    if (N % 8 || K % 8)
-        return fail(BN_ERR_UNSUPPORTED, "bn_gemm_bf16_nt: N=%d and K=%d must be multiples of 8 (16-byte rows)", N, K);
+static int gemm_launch(const void* a, const void* bt, void* c, int M, int N, int K, int n_out, int epi, int* error_word,
+                       bn_stream_t stream, const char* what) {
+    if (!a || !bt || !c) return fail(BN_ERR_INVALID_ARG, "%s: null pointer", what);
+    if (M < 0 || N < 0 || K < 0 || n_out < 0) return fail(BN_ERR_INVALID_ARG, "%s: bad shape M=%d N=%d K=%d", what, M, N, K);
+    if (n_out % 8 || K % 8)
+        return fail(BN_ERR_UNSUPPORTED, "%s: N=%d and K=%d must be multiples of 8 (16-byte rows)", what, n_out, K);
     if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(bt) | reinterpret_cast<uintptr_t>(c)) & 15)
-        return fail(BN_ERR_INVALID_ARG, "bn_gemm_bf16_nt: a/bt/c must be 16-byte aligned");
+        return fail(BN_ERR_INVALID_ARG, "%s: a/bt/c must be 16-byte aligned", what);
     if (int rc = require_sm100()) return rc;
-    if (M == 0 || N == 0) return BN_OK;
+    if (M == 0 || n_out == 0) return BN_OK;
     if (K == 0) {
-        cudaError_t e = cudaMemsetAsync(c, 0, (size_t)M * N * 2, as_stream(stream));
-        return e == cudaSuccess ? BN_OK : fail(BN_ERR_CUDA, "bn_gemm_bf16_nt: %s", cudaGetErrorString(e));
+        cudaError_t e = cudaMemsetAsync(c, 0, (size_t)M * n_out * 2, as_stream(stream));
+        return e == cudaSuccess ? BN_OK : fail(BN_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
     }
     CUtensorMap tmap_a, tmap_b;
     {
@@ -209,14 +252,33 @@ extern "C" int bn_gemm_bf16_nt(const void* a, const void* bt, void* c, int M, in
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     if (configured_dev != dev) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_nt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GM_SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_nt_kernel<EPI_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             GM_SMEM_BYTES);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(gemm_bf16_nt_kernel<EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     GM_SMEM_BYTES);
         if (e != cudaSuccess) return fail(BN_ERR_CUDA, "cudaFuncSetAttribute(gemm): %s", cudaGetErrorString(e));
         configured_dev = dev;
     }
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const long long n_tiles = (long long)((M + GM_BM - 1) / GM_BM) * ((N + GM_BN - 1) / GM_BN);
-    GemmParams p{static_cast<__nv_bfloat16*>(c), error_word, M, N, K};
+    GemmParams p{static_cast<__nv_bfloat16*>(c), error_word, M, N, K, n_out};
     const unsigned grid = (unsigned)(n_tiles < sms ? n_tiles : sms);
-    gemm_bf16_nt_kernel<<<grid, GM_THREADS, GM_SMEM_BYTES, as_stream(stream)>>>(tmap_a, tmap_b, p);
-    return launch_status("bn_gemm_bf16_nt");
+    if (epi == EPI_PLAIN)
+        gemm_bf16_nt_kernel<EPI_PLAIN><<<grid, GM_THREADS, GM_SMEM_BYTES, as_stream(stream)>>>(tmap_a, tmap_b, p);
+    else
+        gemm_bf16_nt_kernel<EPI_SWIGLU><<<grid, GM_THREADS, GM_SMEM_BYTES, as_stream(stream)>>>(tmap_a, tmap_b, p);
+    return launch_status(what);
+}
+
+extern "C" int bn_gemm_bf16_nt(const void* a, const void* bt, void* c, int M, int N, int K, int* error_word,
+                               bn_stream_t stream) {
+    return gemm_launch(a, bt, c, M, N, K, N, EPI_PLAIN, error_word, stream, "bn_gemm_bf16_nt");
+}
+
+extern "C" int bn_gemm_swiglu_bf16_nt(const void* x, const void* gate_up_t, void* h, int M, int inter, int K,
+                                      int* error_word, bn_stream_t stream) {
+    if (inter < 0) return fail(BN_ERR_INVALID_ARG, "bn_gemm_swiglu_bf16_nt: bad shape inter=%d", inter);
+    const int n_rows = (inter + 127) / 128 * 256;      // rows of the packed gate/up weight
+    return gemm_launch(x, gate_up_t, h, M, n_rows, K, inter, EPI_SWIGLU, error_word, stream, "bn_gemm_swiglu_bf16_nt");
 }

@@ -178,3 +178,35 @@ class GroupedQueryAttentionBF16:
 
     def parameters(self):
         return [self.q_proj, self.k_proj, self.v_proj, self.o_proj]
+
+
+class MLPBF16:
+    """The SwiGLU feed-forward block (mygrad/llama/llama_layers.py:194-235: gate_proj, up_proj, down_proj;
+    `(SiLU(x @ gate) * (x @ up)) @ down`) on the tensor-core path: one fused gate/up GEMM with the SiLU * mul epilogue
+    and one down GEMM.  Weights are held transposed in bf16; `gate_proj` / `up_proj` / `down_proj` keep the reference's
+    names.  x: torch bf16 (tokens, hidden) on the GPU.  Inference only."""
+
+    def __init__(self, config, is_cuda: bool = True):
+        import torch
+        from . import ops
+        if not is_cuda:
+            raise RuntimeError("MatMul: only GPU implementation available")
+        self.config = config
+        hidden, inter = config.hidden_size, config.intermediate_size
+
+        def init(in_features, out_features):
+            std = np.sqrt(2.0 / (in_features + out_features))
+            w = np.random.randn(in_features, out_features).astype(np.float32) * std
+            return torch.from_numpy(np.ascontiguousarray(w.T)).cuda().to(torch.bfloat16)
+
+        self.gate_proj, self.up_proj, self.down_proj = init(hidden, inter), init(hidden, inter), init(inter, hidden)
+        self.intermediate_size = inter
+        self._gate_up = ops.pack_gate_up(self.gate_proj, self.up_proj)
+
+    def __call__(self, x):
+        from . import ops
+        h = ops.gemm_swiglu_bf16_nt(x, self._gate_up, self.intermediate_size)
+        return ops.gemm_bf16_nt(h, self.down_proj)
+
+    def parameters(self):
+        return [self.gate_proj, self.up_proj, self.down_proj]

@@ -88,6 +88,38 @@ def gemm_bf16_nt(a: torch.Tensor, bt: torch.Tensor, *, out: Optional[torch.Tenso
     return out
 
 
+def pack_gate_up(gate_t: torch.Tensor, up_t: torch.Tensor) -> torch.Tensor:
+    """Packs Wgate^T and Wup^T, each (inter, K) bf16, into the weight layout of `gemm_swiglu_bf16_nt`: for every
+    block of 128 intermediate indices the 128 gate rows, then the 128 up rows (zero rows beyond inter)."""
+    _need(gate_t, torch.bfloat16, "pack_gate_up(gate_t)")
+    _need(up_t, torch.bfloat16, "pack_gate_up(up_t)")
+    if gate_t.shape != up_t.shape or gate_t.dim() != 2:
+        raise RuntimeError("pack_gate_up: gate and up weights must have the same (inter, K) shape")
+    inter, K = gate_t.shape
+    blocks = (inter + 127) // 128
+    packed = torch.zeros((blocks, 2, 128, K), dtype=torch.bfloat16, device=gate_t.device)
+    padded = torch.zeros((2, blocks * 128, K), dtype=torch.bfloat16, device=gate_t.device)
+    padded[0, :inter], padded[1, :inter] = gate_t, up_t
+    packed[:, 0], packed[:, 1] = padded[0].view(blocks, 128, K), padded[1].view(blocks, 128, K)
+    return packed.view(blocks * 256, K)
+
+
+def gemm_swiglu_bf16_nt(x: torch.Tensor, gate_up_t: torch.Tensor, inter: int, *, out: Optional[torch.Tensor] = None,
+                        error_word: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """silu(x @ Wgate) * (x @ Wup) -> (M, inter) bf16 in one launch; gate_up_t from `pack_gate_up`."""
+    _need(x, torch.bfloat16, "gemm_swiglu_bf16_nt(x)")
+    _need(gate_up_t, torch.bfloat16, "gemm_swiglu_bf16_nt(gate_up_t)")
+    M, K = x.shape
+    if gate_up_t.shape != ((inter + 127) // 128 * 256, K):
+        raise RuntimeError("gemm_swiglu_bf16_nt: packed weight has the wrong shape for this inter / K")
+    if out is None:
+        out = torch.empty((M, inter), dtype=torch.bfloat16, device=x.device)
+    _need(out, torch.bfloat16, "gemm_swiglu_bf16_nt(out)")
+    _lib.check(_lib.load().bn_gemm_swiglu_bf16_nt(x.data_ptr(), gate_up_t.data_ptr(), out.data_ptr(), M, int(inter), K,
+                                                  error_word.data_ptr() if error_word is not None else None, _stream()))
+    return out
+
+
 class HostPrefillPipeline:
     """Prefill attention for callers whose q/k/v/out live in (pinned) HOST memory, as the reference's tensors do
     before `to_device()` (mygrad tensors are created on the host and copied per call).  Every `submit` copies that

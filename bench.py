@@ -447,6 +447,42 @@ def measure_gemm(torch, ops, args, rank, world, dist, reduce_max, pk):
     }
 
 
+def measure_mlp(torch, ops, args, rank, world, dist, reduce_max, pk):
+    """Row N4: the SwiGLU MLP of TinyLLaMA at config 2's token count: fused gate/up GEMM with the SiLU * mul epilogue
+    (16384 x 2048 -> 5632, 756 GFLOP) and the down GEMM (5632 -> 2048, 378 GFLOP), two launches."""
+    M, K, I = PREFILL["B"] * PREFILL["S"], 2048, 5632
+    g = torch.Generator(device="cuda").manual_seed(17 + rank)
+    xs = [torch.randn((M, K), generator=g, device="cuda").to(torch.bfloat16) for _ in range(2)]
+    wg = (torch.randn((I, K), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    wu = (torch.randn((I, K), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    wd = (torch.randn((K, I), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    gu = ops.pack_gate_up(wg, wu)
+    h = torch.empty((M, I), dtype=torch.bfloat16, device="cuda")
+    y = torch.empty((M, K), dtype=torch.bfloat16, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def step(i):
+        ops.gemm_swiglu_bf16_nt(xs[i % 2], gu, I, out=h, error_word=err)
+        ops.gemm_bf16_nt(h, wd, out=y, error_word=err)
+
+    steps = max(10, args.steps // 5)
+    ms = reduce_max(time_loop(torch, step, steps, 3, dist))
+    if int(err.item()) != 0:
+        raise RuntimeError("mlp: a bounded device-side wait ran out")
+    flops = 2.0 * M * K * (2 * I) + 2.0 * M * I * K
+    tf = flops * world / (ms * 1e-3) / 1e12
+    return {
+        "metric": "swiglu_mlp_tflops", "value": tf, "unit": "TFLOP/s", "ms_per_step": ms, "steps": steps,
+        "n_gpus": world, "dtype": "bf16",
+        "config": {"workload": "SwiGLU MLP (row N4): 16384 tokens, hidden 2048, intermediate 5632; fused gate/up GEMM "
+                               "with SiLU*mul epilogue + down GEMM", "flops_per_step_per_gpu": flops},
+        "roofline": {"bound": "tensor", "achieved": tf / world, "peak": pk["tensor"], "unit": "TFLOP/s",
+                     "frac": tf / world / pk["tensor"], "traffic": None,
+                     "peak_source": pk["source"] + " (bf16 burst)", "kernel": "gemm_bf16_nt_kernel"},
+        "gpu_launches": 2 * steps,
+    }
+
+
 def measure_longctx(torch, args, rank, world, dist, reduce_max, pk):
     """BASELINE config 4: batch 4, one 262144-token sequence each, 32q/4kv heads.  The sequence is cut into
     contiguous page-aligned token ranges, one per GPU; each GPU decodes over its range (normalised partial
@@ -543,6 +579,10 @@ def run_ours(args):
                 result["gemm"] = measure_gemm(torch, ops, args, rank, world, dist, reduce_max, pk)
             except Exception as e:
                 result["gemm"] = {"error": repr(e)}
+            try:
+                result["mlp"] = measure_mlp(torch, ops, args, rank, world, dist, reduce_max, pk)
+            except Exception as e:
+                result["mlp"] = {"error": repr(e)}
     if rank == 0:
         result["clocks"] = sampler.stop()
         if world == 1 and not args.no_cpu_baseline and not args.decode_only:

@@ -118,6 +118,16 @@ BN_API int bn_argmax_rows_f32(const float* x, int64_t x_rs, int64_t x_cs, uint32
 BN_API int bn_gemm_bf16_nt(const void* a, const void* bt, void* c, int M, int N, int K, int* error_word,
                            bn_stream_t stream);
 
+/* h (M, inter) bf16 = silu(x @ Wgate) * (x @ Wup): both GEMMs of the SwiGLU MLP, the activation and the product in
+ * one launch of the tensor-core GEMM.  x (M,K) bf16; gate_up_t is the PACKED weight, ceil(inter/128)*256 rows of K
+ * bf16: for every block of 128 intermediate indices, the 128 rows of Wgate^T followed by the 128 rows of Wup^T for
+ * the same indices (rows beyond `inter` zero).  inter and K multiples of 8.
+ * Replaces `gate = x @ gate_proj; gate = gate.silu(); up = x @ up_proj; inter = gate * up` of MLP.__call__
+ * (mygrad/llama/llama_layers.py:217-228; op_mm, op_silu src/ops/op_silu.cuh:7-15, op_multiply); the down projection
+ * that follows is bn_gemm_bf16_nt. */
+BN_API int bn_gemm_swiglu_bf16_nt(const void* x, const void* gate_up_t, void* h, int M, int inter, int K,
+                                  int* error_word, bn_stream_t stream);
+
 /* y = x / sqrt(mean(x^2) + eps) * w, row by row; x, y (rows, hidden), w (hidden) with element strides.
  * Same arithmetic order as the reference kernel (256 partial fused-multiply-add chains, its reduction tree, IEEE
  * division and square root), so the result is the reference's bit for bit.

@@ -84,3 +84,40 @@ def test_bf16_layer_against_staged_fp64_restatement(lib):
                                     dtype=np.float64, round_rope_bf16=True)
         ref = R.round_bf16(attn.astype(np.float32)).astype(np.float64) @ wo.T
         assert np.abs(got[b] - ref).max() <= 2e-2, np.abs(got[b] - ref).max()
+
+
+@pytest.mark.parametrize("M,inter,K", [(128, 128, 64), (200, 256, 128), (64, 5632, 2048), (300, 136, 72), (1000, 1000, 512)])
+def test_swiglu_gemm_against_fp64(lib, M, inter, K):
+    """silu(x Wg) * (x Wu) from one launch against fp64 on the same bf16 operands; the kernel applies the activation
+    to its fp32 accumulators and rounds once, so the gate is one bf16 ulp at the largest magnitude."""
+    from baranet_bdml_b200 import ops
+    rng = np.random.default_rng(M + inter + K)
+    x = R.round_bf16(rng.standard_normal((M, K), dtype=np.float32))
+    wg = R.round_bf16((rng.standard_normal((inter, K)) * 0.05).astype(np.float32))
+    wu = R.round_bf16((rng.standard_normal((inter, K)) * 0.05).astype(np.float32))
+    tx, tg, tu = (torch.from_numpy(a).cuda().to(torch.bfloat16) for a in (x, wg, wu))
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = ops.gemm_swiglu_bf16_nt(tx, ops.pack_gate_up(tg, tu), inter, error_word=err).float().cpu().numpy()
+    assert int(err.item()) == 0
+    g = x.astype(np.float64) @ wg.astype(np.float64).T
+    u = x.astype(np.float64) @ wu.astype(np.float64).T
+    ref = g / (1.0 + np.exp(-g)) * u
+    assert np.abs(got - ref).max() <= max(np.abs(ref).max(), 1e-30) * 2.0 ** -8
+
+
+def test_bf16_mlp_against_staged_fp64(lib):
+    """MLPBF16 (fused gate/up GEMM + down GEMM) against fp64 with a bf16 rounding of the intermediate, where the
+    kernels round."""
+    from baranet_bdml_b200.layers import LLaMAConfig, MLPBF16
+    cfg = LLaMAConfig(hidden_size=512, num_attention_heads=8, num_key_value_heads=2, intermediate_size=1408,
+                      num_hidden_layers=1)
+    np.random.seed(2)
+    mlp = MLPBF16(cfg)
+    rng = np.random.default_rng(4)
+    x = R.round_bf16(rng.standard_normal((333, 512), dtype=np.float32))
+    got = mlp(torch.from_numpy(x).cuda().to(torch.bfloat16)).float().cpu().numpy()
+    wg, wu, wd = (w.float().cpu().numpy().astype(np.float64) for w in (mlp.gate_proj, mlp.up_proj, mlp.down_proj))
+    g, u = x.astype(np.float64) @ wg.T, x.astype(np.float64) @ wu.T
+    inter = R.round_bf16((g / (1.0 + np.exp(-g)) * u).astype(np.float32)).astype(np.float64)
+    ref = inter @ wd.T
+    assert np.abs(got - ref).max() <= np.abs(ref).max() * 2.0 ** -7
