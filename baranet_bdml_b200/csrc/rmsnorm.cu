@@ -176,3 +176,119 @@ extern "C" int bn_add_rmsnorm_f32(const float* a, int64_t a_rs, int64_t a_cs, co
     RmsParams p{a, a_rs, a_cs, b, b_rs, b_cs, w, w_cs, sum, s_rs, s_cs, y, y_rs, y_cs, rows, hidden, eps};
     return rmsnorm_launch(p, stream, "bn_add_rmsnorm_f32");
 }
+
+// ---------------------------------------------------------------------------
+// bf16 residual stream: s = a + b rounded to bf16 (the model dtype), y = s / sqrt(mean(s^2) + eps) * w with fp32
+// arithmetic and one rounding of y.  Used by the bf16 decoder layer; no bit-compatibility constraint here, so the
+// row is moved in 16-byte pieces and reduced with shuffles.
+// ---------------------------------------------------------------------------
+namespace bn {
+
+struct RmsBf16Params {
+    const __nv_bfloat16 *a, *b, *w;    // b may be null
+    __nv_bfloat16 *s, *y;              // s may be null
+    int rows, hidden;
+    float eps;
+};
+
+constexpr int RB_MAXV = 2;             // 16-byte pieces per thread kept in registers: hidden <= 256 * 8 * 2 = 4096
+
+__device__ __forceinline__ float bf16lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+__device__ __forceinline__ uint32_t packbf(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+__global__ void __launch_bounds__(256)
+rmsnorm_bf16_kernel(const RmsBf16Params p) {
+    __shared__ float s_part[8];
+    const int tid = threadIdx.x, lane = tid % 32, warp = tid / 32;
+    const int pieces = p.hidden / 8;
+    for (int row = blockIdx.x; row < p.rows; row += gridDim.x) {
+        const uint4* ar = reinterpret_cast<const uint4*>(p.a + (size_t)row * p.hidden);
+        const uint4* br = p.b ? reinterpret_cast<const uint4*>(p.b + (size_t)row * p.hidden) : nullptr;
+        uint4* sr = p.s ? reinterpret_cast<uint4*>(p.s + (size_t)row * p.hidden) : nullptr;
+        uint4* yr = reinterpret_cast<uint4*>(p.y + (size_t)row * p.hidden);
+        uint4 v[RB_MAXV];
+        float acc = 0.f;
+        auto fetch = [&](int c) {
+            uint4 x = __ldg(ar + c);
+            if (br) {
+                const uint4 y4 = __ldg(br + c);
+                uint32_t* xs = reinterpret_cast<uint32_t*>(&x);
+                const uint32_t* ys = reinterpret_cast<const uint32_t*>(&y4);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) xs[e] = packbf(bf16lo(xs[e]) + bf16lo(ys[e]), bf16hi(xs[e]) + bf16hi(ys[e]));
+            }
+            return x;
+        };
+        auto sq = [&](const uint4& x) {
+            const uint32_t* xs = reinterpret_cast<const uint32_t*>(&x);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float lo = bf16lo(xs[e]), hi = bf16hi(xs[e]);
+                acc = fmaf(lo, lo, acc);
+                acc = fmaf(hi, hi, acc);
+            }
+        };
+#pragma unroll
+        for (int k = 0; k < RB_MAXV; ++k) {
+            const int c = tid + k * 256;
+            if (c < pieces) { v[k] = fetch(c); sq(v[k]); }
+        }
+        for (int c = tid + RB_MAXV * 256; c < pieces; c += 256) { const uint4 x = fetch(c); sq(x); }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) s_part[warp] = acc;
+        __syncthreads();
+        float total = 0.f;
+#pragma unroll
+        for (int w8 = 0; w8 < 8; ++w8) total += s_part[w8];
+        const float inv = rsqrtf(total / (float)p.hidden + p.eps);
+        auto emit = [&](int c, const uint4& x) {
+            if (sr) sr[c] = x;
+            const uint4 w4 = __ldg(reinterpret_cast<const uint4*>(p.w) + c);
+            const uint32_t* xs = reinterpret_cast<const uint32_t*>(&x);
+            const uint32_t* ws = reinterpret_cast<const uint32_t*>(&w4);
+            uint4 o4;
+            uint32_t* os = reinterpret_cast<uint32_t*>(&o4);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                os[e] = packbf(bf16lo(xs[e]) * inv * bf16lo(ws[e]), bf16hi(xs[e]) * inv * bf16hi(ws[e]));
+            yr[c] = o4;
+        };
+#pragma unroll
+        for (int k = 0; k < RB_MAXV; ++k) {
+            const int c = tid + k * 256;
+            if (c < pieces) emit(c, v[k]);
+        }
+        for (int c = tid + RB_MAXV * 256; c < pieces; c += 256) emit(c, fetch(c));
+        __syncthreads();     // s_part is rewritten by the next row
+    }
+}
+
+}  // namespace bn
+
+extern "C" int bn_add_rmsnorm_bf16(const void* a, const void* b, const void* w, void* sum, void* y, int rows, int hidden,
+                                   float eps, bn_stream_t stream) {
+    if (!a || !w || !y) return fail(BN_ERR_INVALID_ARG, "bn_add_rmsnorm_bf16: null pointer");
+    if (rows < 0 || hidden < 0 || hidden % 8)
+        return fail(BN_ERR_INVALID_ARG, "bn_add_rmsnorm_bf16: bad shape rows=%d hidden=%d (hidden must be a multiple of 8)",
+                    rows, hidden);
+    if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(w) |
+         reinterpret_cast<uintptr_t>(sum) | reinterpret_cast<uintptr_t>(y)) & 15)
+        return fail(BN_ERR_INVALID_ARG, "bn_add_rmsnorm_bf16: pointers must be 16-byte aligned");
+    if (int rc = require_sm100()) return rc;
+    if (rows == 0 || hidden == 0) return BN_OK;
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long cap = (long long)sms * 8;
+    RmsBf16Params p{static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b),
+                    static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(sum),
+                    static_cast<__nv_bfloat16*>(y), rows, hidden, eps};
+    rmsnorm_bf16_kernel<<<(unsigned)(rows < cap ? rows : cap), 256, 0, as_stream(stream)>>>(p);
+    return launch_status("bn_add_rmsnorm_bf16");
+}

@@ -210,3 +210,41 @@ class MLPBF16:
 
     def parameters(self):
         return [self.gate_proj, self.up_proj, self.down_proj]
+
+
+class LLaMADecoderLayerBF16:
+    """mygrad/llama/llama_layers.py:238-296 (pre-norm decoder block: input_layernorm -> self_attn -> residual add ->
+    post_attention_layernorm -> mlp -> residual add) on the bf16 tensor-core path, 10 launches per call:
+    norm, 3 projection GEMMs, K rotation, fused attention, o_proj GEMM, fused residual add + norm, fused gate/up GEMM,
+    down GEMM; the last residual add is returned un-added together with the MLP output by `forward_parts`, so that
+    the NEXT layer's fused add + norm performs it (`__call__` adds it for a stand-alone layer).
+    hidden_states: torch bf16 (B, S, hidden) on the GPU.  Inference only."""
+
+    def __init__(self, config, is_cuda: bool = True):
+        import torch
+        self.config = config
+        self.self_attn = GroupedQueryAttentionBF16(config, is_cuda)
+        self.mlp = MLPBF16(config, is_cuda)
+        self.input_layernorm_weight = torch.ones(config.hidden_size, dtype=torch.bfloat16, device="cuda")
+        self.post_attention_layernorm_weight = torch.ones(config.hidden_size, dtype=torch.bfloat16, device="cuda")
+        self.eps = config.rms_norm_eps
+
+    def forward_parts(self, hidden_states, position_offset: int = 0, use_causal_mask: bool = True, pending=None):
+        """Returns (residual, mlp_out) with the layer output = residual + mlp_out.  `pending` is the previous layer's
+        not-yet-added MLP output: it is added to hidden_states by this layer's first (fused) norm."""
+        from . import ops
+        B, S, H = hidden_states.shape
+        x2 = hidden_states.reshape(B * S, H)
+        residual, normed = ops.add_rmsnorm_bf16(x2, None if pending is None else pending.reshape(B * S, H),
+                                                self.input_layernorm_weight, self.eps)
+        attn = self.self_attn(normed.view(B, S, H), position_offset, use_causal_mask).reshape(B * S, H)
+        residual, normed = ops.add_rmsnorm_bf16(residual, attn, self.post_attention_layernorm_weight, self.eps)
+        return residual.view(B, S, H), self.mlp(normed).view(B, S, H)
+
+    def __call__(self, hidden_states, position_offset: int = 0, use_causal_mask: bool = True):
+        residual, mlp_out = self.forward_parts(hidden_states, position_offset, use_causal_mask)
+        return residual + mlp_out
+
+    def parameters(self):
+        return ([self.input_layernorm_weight] + self.self_attn.parameters() + [self.post_attention_layernorm_weight] +
+                self.mlp.parameters())

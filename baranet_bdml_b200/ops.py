@@ -88,6 +88,26 @@ def gemm_bf16_nt(a: torch.Tensor, bt: torch.Tensor, *, out: Optional[torch.Tenso
     return out
 
 
+def add_rmsnorm_bf16(a: torch.Tensor, b: Optional[torch.Tensor], weight: torch.Tensor, eps: float = 1e-6, *,
+                     want_sum: bool = True) -> Tuple[Optional[torch.Tensor], torch.Tensor]:
+    """(a + b rounded to bf16, rmsnorm of that sum) for a bf16 residual stream (tokens, hidden); b None: plain norm."""
+    _need(a, torch.bfloat16, "add_rmsnorm_bf16(a)")
+    _need(weight, torch.bfloat16, "add_rmsnorm_bf16(weight)")
+    if b is not None:
+        _need(b, torch.bfloat16, "add_rmsnorm_bf16(b)")
+        if b.shape != a.shape:
+            raise RuntimeError("RMSNorm: input/output shape mismatch")
+    rows, hidden = a.shape
+    if weight.numel() != hidden:
+        raise RuntimeError("RMSNorm: weight shape must be (1, hidden_dim)")
+    total = torch.empty_like(a) if (want_sum and b is not None) else None
+    y = torch.empty_like(a)
+    _lib.check(_lib.load().bn_add_rmsnorm_bf16(a.data_ptr(), b.data_ptr() if b is not None else None, weight.data_ptr(),
+                                               total.data_ptr() if total is not None else None, y.data_ptr(), rows,
+                                               hidden, float(eps), _stream()))
+    return (total if b is not None else a), y
+
+
 def pack_gate_up(gate_t: torch.Tensor, up_t: torch.Tensor) -> torch.Tensor:
     """Packs Wgate^T and Wup^T, each (inter, K) bf16, into the weight layout of `gemm_swiglu_bf16_nt`: for every
     block of 128 intermediate indices the 128 gate rows, then the 128 up rows (zero rows beyond inter)."""

@@ -483,6 +483,39 @@ def measure_mlp(torch, ops, args, rank, world, dist, reduce_max, pk):
     }
 
 
+def measure_decoder_layer(torch, args, rank, world, dist, reduce_max, pk):
+    """One TinyLLaMA decoder block (hidden 2048, 32q/4kv heads, intermediate 5632) on the bf16 path over config 2's
+    tokens (B=8, S=2048): norm, q/k/v GEMMs, K rotation, fused attention, o GEMM, add+norm, fused gate/up GEMM,
+    down GEMM = 10 launches (`layers.LLaMADecoderLayerBF16.forward_parts`)."""
+    from baranet_bdml_b200.layers import LLaMAConfig, LLaMADecoderLayerBF16
+    import numpy as np
+    np.random.seed(1 + rank)
+    cfg = LLaMAConfig()
+    layer = LLaMADecoderLayerBF16(cfg)
+    B, S, H = PREFILL["B"], PREFILL["S"], cfg.hidden_size
+    g = torch.Generator(device="cuda").manual_seed(3 + rank)
+    xs = [torch.randn((B, S, H), generator=g, device="cuda").to(torch.bfloat16) for _ in range(2)]
+
+    def step(i):
+        layer.forward_parts(xs[i % 2])
+
+    steps = max(10, args.steps // 10)
+    ms = reduce_max(time_loop(torch, step, steps, 3, dist))
+    T, I, kv = B * S, cfg.intermediate_size, cfg.num_key_value_heads * cfg.head_dim
+    flops = prefill_flops() + 2.0 * T * H * (2 * H + 2 * kv) + 2.0 * T * H * 3 * I
+    tf = flops * world / (ms * 1e-3) / 1e12
+    return {
+        "metric": "decoder_layer_tflops", "value": tf, "unit": "TFLOP/s", "ms_per_step": ms, "steps": steps,
+        "n_gpus": world, "dtype": "bf16", "tokens_per_s": T * world / (ms * 1e-3),
+        "config": {"workload": "one TinyLLaMA decoder block, bf16, 16384 tokens (B=8, S=2048), causal, 10 launches",
+                   "flops_per_step_per_gpu": flops},
+        "roofline": {"bound": "tensor", "achieved": tf / world, "peak": pk["tensor"], "unit": "TFLOP/s",
+                     "frac": tf / world / pk["tensor"], "traffic": None, "peak_source": pk["source"] + " (bf16 burst)",
+                     "kernel": "gemm_bf16_nt_kernel + prefill_kernel"},
+        "gpu_launches": 10 * steps,
+    }
+
+
 def measure_longctx(torch, args, rank, world, dist, reduce_max, pk):
     """BASELINE config 4: batch 4, one 262144-token sequence each, 32q/4kv heads.  The sequence is cut into
     contiguous page-aligned token ranges, one per GPU; each GPU decodes over its range (normalised partial
@@ -583,6 +616,10 @@ def run_ours(args):
                 result["mlp"] = measure_mlp(torch, ops, args, rank, world, dist, reduce_max, pk)
             except Exception as e:
                 result["mlp"] = {"error": repr(e)}
+            try:
+                result["decoder_layer"] = measure_decoder_layer(torch, args, rank, world, dist, reduce_max, pk)
+            except Exception as e:
+                result["decoder_layer"] = {"error": repr(e)}
     if rank == 0:
         result["clocks"] = sampler.stop()
         if world == 1 and not args.no_cpu_baseline and not args.decode_only:

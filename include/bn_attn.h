@@ -145,6 +145,13 @@ BN_API int bn_add_rmsnorm_f32(const float* a, int64_t a_rs, int64_t a_cs, const 
                               const float* w, int64_t w_cs, float* sum, int64_t s_rs, int64_t s_cs, float* y,
                               int64_t y_rs, int64_t y_cs, int rows, int hidden, float eps, bn_stream_t stream);
 
+/* The same pair on a bf16 residual stream (rows, hidden) bf16, dense: sum = a + b rounded to bf16 (b may be NULL:
+ * sum = a), y = sum / sqrt(mean(sum^2) + eps) * w computed in fp32 and rounded once.  `sum` may be NULL.  hidden a
+ * multiple of 8, pointers 16-byte aligned.  Used by the bf16 decoder layer (RMSNorm and the residual adds of
+ * LLaMADecoderLayer, mygrad/llama/llama_layers.py:262-287, on bf16 activations). */
+BN_API int bn_add_rmsnorm_bf16(const void* a, const void* b, const void* w, void* sum, void* y, int rows, int hidden,
+                               float eps, bn_stream_t stream);
+
 /* Fused attention core, fp32:
  *   out = softmax_causal((rope(q) @ repeat(rope(k))^T) * scale) @ repeat(v)
  * q, out: (S, Hq*D); k, v: (S, Hkv*D); all with element strides.

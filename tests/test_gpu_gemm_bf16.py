@@ -121,3 +121,50 @@ def test_bf16_mlp_against_staged_fp64(lib):
     inter = R.round_bf16((g / (1.0 + np.exp(-g)) * u).astype(np.float32)).astype(np.float64)
     ref = inter @ wd.T
     assert np.abs(got - ref).max() <= np.abs(ref).max() * 2.0 ** -7
+
+
+def test_bf16_decoder_layer_against_staged_fp64(lib):
+    """The whole pre-norm decoder block on the bf16 path (norm, attention layer, fused residual add + norm, SwiGLU MLP,
+    residual) against fp64 with a bf16 rounding wherever a kernel rounds; and two stacked layers with the deferred
+    residual add (`forward_parts(pending=...)`) equal to the plain composition."""
+    from baranet_bdml_b200.layers import LLaMAConfig, LLaMADecoderLayerBF16
+    cfg = LLaMAConfig(hidden_size=512, num_attention_heads=8, num_key_value_heads=2, intermediate_size=1408,
+                      num_hidden_layers=2)
+    np.random.seed(12)
+    layer = LLaMADecoderLayerBF16(cfg)
+    B, S, H = 2, 200, 512
+    rng = np.random.default_rng(3)
+    x = R.round_bf16(rng.standard_normal((B, S, H), dtype=np.float32))
+    tx = torch.from_numpy(x).cuda().to(torch.bfloat16)
+    got = layer(tx).float().cpu().numpy()
+
+    rb = lambda a: R.round_bf16(np.asarray(a, dtype=np.float32)).astype(np.float64)
+    f64 = lambda t: t.float().cpu().numpy().astype(np.float64)
+    at, ml = layer.self_attn, layer.mlp
+    wq, wk, wv, wo = f64(at.q_proj), f64(at.k_proj), f64(at.v_proj), f64(at.o_proj)
+    wg, wu, wd = f64(ml.gate_proj), f64(ml.up_proj), f64(ml.down_proj)
+
+    def norm(s):
+        return rb(s / np.sqrt((s * s).mean(axis=1, keepdims=True) + cfg.rms_norm_eps))
+
+    for b in range(B):
+        h0 = x[b].astype(np.float64)
+        n1 = norm(h0)
+        q, k, v = rb(n1 @ wq.T), rb(n1 @ wk.T), rb(n1 @ wv.T)
+        attn = rb(R.attention_per_head(q, k, v, num_heads=8, num_kv_heads=2, head_dim=64, causal=True, dtype=np.float64,
+                                       round_rope_bf16=True))
+        h1 = rb(h0 + rb(attn @ wo.T))
+        n2 = norm(h1)
+        g, u = n2 @ wg.T, n2 @ wu.T
+        m = rb(rb(g / (1.0 + np.exp(-g)) * u) @ wd.T)
+        ref = rb(h1 + m)
+        err = np.abs(got[b] - ref).max()
+        # the attention path's 2e-2 plus two bf16 ulps at the largest magnitude: a value that sits near a rounding
+        # boundary may round the other way in the kernel and its neighbours downstream
+        assert err <= 2e-2 + np.abs(ref).max() * 2.0 ** -7, (err, np.abs(ref).max())
+
+    layer2 = LLaMADecoderLayerBF16(cfg)
+    plain = layer2(layer(tx))
+    res, pend = layer.forward_parts(tx)
+    res2, pend2 = layer2.forward_parts(res, pending=pend)
+    assert torch.equal(res2 + pend2, plain)

@@ -90,3 +90,23 @@ def test_rmsnorm_full_size_properties(lib):
     rms = y.double().pow(2).mean(dim=1).sqrt()
     assert float((rms - 1).abs().max()) < 1e-6
     assert torch.equal(y, y4)
+
+
+@pytest.mark.parametrize("rows,hidden", [(1, 8), (5, 2048), (3, 4096), (4, 4104), (700, 512)])
+def test_bf16_add_rmsnorm(lib, rows, hidden):
+    """bf16 residual stream: the sum is the bf16 rounding of a + b (bit-exact against torch), the norm is within one
+    bf16 ulp of fp64 on that rounded sum, and the fused call equals add followed by the plain norm bit for bit."""
+    import torch
+    from baranet_bdml_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(rows + hidden)
+    a = torch.randn((rows, hidden), generator=g, device="cuda").to(torch.bfloat16)
+    b = torch.randn((rows, hidden), generator=g, device="cuda").to(torch.bfloat16)
+    w = (1 + 0.1 * torch.randn((hidden,), generator=g, device="cuda")).to(torch.bfloat16)
+    total, y = ops.add_rmsnorm_bf16(a, b, w, 1e-6)
+    want_sum = (a.float() + b.float()).to(torch.bfloat16)
+    assert torch.equal(total, want_sum)
+    s64 = want_sum.double()
+    ref = s64 / torch.sqrt((s64 * s64).mean(dim=1, keepdim=True) + 1e-6) * w.double()
+    assert float((y.double() - ref).abs().max()) <= float(ref.abs().max()) * 2.0 ** -8
+    _, y_plain = ops.add_rmsnorm_bf16(want_sum, None, w, 1e-6)
+    assert torch.equal(y, y_plain)
