@@ -39,7 +39,8 @@ PREFILL = dict(B=8, S=2048, Hq=32, Hkv=4, D=64)
 DECODE = dict(B=64, Hq=32, Hkv=4, D=64, Lmin=1024, Lmax=4096, page=16)
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
 NCU_TRAFFIC = {"prefill_kernel": 85.475e6 + 27.995e6, "decode_paged_kernel": 163.426e6 + 3.645e6,
-               "rmsnorm_kernel": 268.471e6 + 224.065e6, "gemm_bf16_nt_kernel": 121.810e6 + 46.803e6}
+               "rmsnorm_kernel": 268.471e6 + 224.065e6, "gemm_bf16_nt_kernel": 121.810e6 + 46.803e6,
+               "argmax_rows_kernel": 262.395e6 + 3.882e6}
 
 
 def peaks():
@@ -404,8 +405,10 @@ def measure_embed_argmax(torch, args, rank, world, dist, reduce_max, pk):
         "config": {"workload": "per-row argmax of 2048 x 32000 fp32 logits (row N2), first maximum as op_argmax",
                    "algorithmic_bytes_per_step": b_a, "l2": "262 MB per step, larger than L2"},
         "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": pk["hbm"], "unit": "GB/s",
-                     "frac": gbs / world / pk["hbm"], "traffic": None, "peak_source": pk["source"],
-                     "kernel": "argmax_rows_kernel"},
+                     "frac": gbs / world / pk["hbm"], "traffic": NCU_TRAFFIC["argmax_rows_kernel"],
+                     "traffic_unit": "bytes of DRAM traffic per launch (ncu capture, "
+                                     "profiles/argmax_and_embedding_gather_kernels.md)",
+                     "peak_source": pk["source"], "kernel": "argmax_rows_kernel"},
         "embedding_gather": {"value": b_g * world / (ms_g * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms_g,
                              "algorithmic_bytes_per_step": b_g,
                              "workload": "16384 token rows of 2048 fp32 from a 32000-row table"},
