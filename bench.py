@@ -15,9 +15,11 @@ batch of synthetic input:
       with this measurement.
 With N > 1 (torchrun, one rank per GPU) every rank processes its own copy of
 the workload (weak scaling, no data-path collective); the time is the max over
-ranks.  `--impl reference` times the CPU restatement of the reference's
-operators on the host cores (the reference has no CPU implementation of this
-path: its operators throw "only GPU implementation available").
+ranks.  `--impl reference` times the reference's OWN CUDA operators (its
+attention-layer core, through oracle/_ref, host arrays in and out) when that
+library was built, and the plain-C restatement of its operators on the host
+cores beside it (the reference has no CPU implementation of this path: its
+operators throw "only GPU implementation available").
 """
 from __future__ import annotations
 
@@ -130,20 +132,67 @@ def cpu_prefill_sample(n_batches: int, steps: int = 1, warmup: int = 0):
                        f"oracle/ref_attention.c with OpenMP")
 
 
+def reference_cuda_sample(n_batches: int, steps: int, warmup: int):
+    """Times the reference's OWN CUDA operators (oracle/_ref, compiled from the reference tree): per batch element
+    the operator sequence of its attention layer core -- op_rope on q and k, host-side head repeat, op_mm, op_multiply,
+    causal op_softmax, op_mm -- on fp32 host arrays, as its tensors require (upload and download are part of its call).
+    None when that library or a GPU is not there."""
+    import numpy as np
+    from oracle import cref
+    try:
+        import torch
+        if not torch.cuda.is_available() or not os.path.exists(cref._GPU_SO):
+            return None
+        cref.gpu()
+    except Exception:
+        return None
+    c = PREFILL
+    rng = np.random.default_rng(0)
+    q = rng.standard_normal((n_batches, c["S"], c["Hq"] * c["D"]), dtype=np.float32)
+    k = rng.standard_normal((n_batches, c["S"], c["Hkv"] * c["D"]), dtype=np.float32)
+    v = rng.standard_normal((n_batches, c["S"], c["Hkv"] * c["D"]), dtype=np.float32)
+
+    def one_step():
+        for b in range(n_batches):
+            cref.gpu_attention_core(q[b], k[b], v[b], num_heads=c["Hq"], num_kv_heads=c["Hkv"], head_dim=c["D"],
+                                    causal=True)
+
+    for _ in range(warmup):
+        one_step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one_step()
+    dt = (time.perf_counter() - t0) / steps
+    flops = prefill_flops() * n_batches / c["B"]
+    return dict(value=flops / dt / 1e12, seconds=dt,
+                sample=f"{n_batches} of {c['B']} batch elements of config 2 (S=2048, 32q/4kv, D=64), the reference's own "
+                       f"CUDA operators (fp32, heads collapsed as its layer computes them) via oracle/_ref, host arrays in "
+                       f"and out")
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    r = cpu_prefill_sample(n_batches=2, steps=max(1, args.steps), warmup=1 if args.warmup else 0)
+    cpu = cpu_prefill_sample(n_batches=2, steps=max(1, min(args.steps, 3)), warmup=1 if args.warmup else 0)
+    gpu = reference_cuda_sample(n_batches=2, steps=max(1, min(args.steps, 5)), warmup=1 if args.warmup else 0)
+    # The reference has no CPU implementation of this path (its operators throw "only GPU implementation
+    # available"), so its own code can only be timed on the GPU: that is the arm's value whenever the compiled
+    # reference is present; the plain-C restatement on the host cores is reported beside it.
+    r = gpu if gpu is not None else cpu
     line = {
         "impl": "reference", "metric": "prefill_attention_tflops", "value": r["value"], "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["seconds"] * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "prefill attention core, BASELINE config 2 (B=8 S=2048 32q/4kv D=64 causal, RoPE fused)",
                    "note": "the reference has no CPU implementation of this path (its operators throw 'only GPU "
-                           "implementation available'); this arm times the plain-C restatement of its operators"},
-        "cpu_baseline": {"value": r["value"], "unit": "TFLOP/s", "cores": r["cores"], "kind": "port",
-                         "sample": r["sample"]},
+                           "implementation available'); value = " +
+                           ("its own CUDA operators on this GPU through oracle/_ref" if gpu is not None else
+                            "the plain-C restatement of its operators on the host cores (oracle/_ref not present)")},
+        "cpu_baseline": {"value": r["value"], "unit": "TFLOP/s", "cores": 1 if gpu is not None else cpu["cores"],
+                         "kind": "reference" if gpu is not None else "port", "sample": r["sample"]},
+        "cpu_port": {"value": cpu["value"], "unit": "TFLOP/s", "cores": cpu["cores"], "kind": "port",
+                     "sample": cpu["sample"]},
         "e2e": {"value": r["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
