@@ -22,6 +22,11 @@ import numpy as np
 from . import _lib
 from .tensor import AGTensor, TensorF
 
+try:  # only for annotations
+    import torch  # noqa: F401
+except Exception:  # pragma: no cover
+    torch = None
+
 
 @dataclass
 class LLaMAConfig:
@@ -248,3 +253,30 @@ class LLaMADecoderLayerBF16:
     def parameters(self):
         return ([self.input_layernorm_weight] + self.self_attn.parameters() + [self.post_attention_layernorm_weight] +
                 self.mlp.parameters())
+
+
+class GraphedDecoderLayerBF16:
+    """`LLaMADecoderLayerBF16.forward_parts` for one fixed input shape, captured once into a CUDA graph and replayed:
+    the ten launches of a block go to the GPU as one submission, without the host-side work between them (tensor-map
+    encoding, argument checks, allocator calls).  `__call__(x)` copies x into the graph's static input and returns
+    the static outputs (residual, mlp_out); they are overwritten by the next call."""
+
+    def __init__(self, layer: "LLaMADecoderLayerBF16", example: "torch.Tensor", position_offset: int = 0,
+                 use_causal_mask: bool = True):
+        import torch
+        self.layer = layer
+        self.static_in = example.clone()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):              # warm-up outside the capture: attributes, workspaces, caches
+            for _ in range(2):
+                layer.forward_parts(self.static_in, position_offset, use_causal_mask)
+        torch.cuda.current_stream().wait_stream(side)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.static_out = layer.forward_parts(self.static_in, position_offset, use_causal_mask)
+
+    def __call__(self, hidden_states):
+        self.static_in.copy_(hidden_states)
+        self.graph.replay()
+        return self.static_out

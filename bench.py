@@ -553,12 +553,20 @@ def measure_decoder_layer(torch, args, rank, world, dist, reduce_max, pk):
 
     steps = max(10, args.steps // 10)
     ms = reduce_max(time_loop(torch, step, steps, 3, dist))
+    # the same ten launches replayed from one CUDA graph
+    ms_graph = None
+    try:
+        from baranet_bdml_b200.layers import GraphedDecoderLayerBF16
+        graphed = GraphedDecoderLayerBF16(layer, xs[0])
+        ms_graph = reduce_max(time_loop(torch, lambda i: graphed.graph.replay(), steps, 3, dist))
+    except Exception as e:      # the eager number stands
+        ms_graph = repr(e)
     T, I, kv = B * S, cfg.intermediate_size, cfg.num_key_value_heads * cfg.head_dim
     flops = prefill_flops() + 2.0 * T * H * (2 * H + 2 * kv) + 2.0 * T * H * 3 * I
     tf = flops * world / (ms * 1e-3) / 1e12
     return {
         "metric": "decoder_layer_tflops", "value": tf, "unit": "TFLOP/s", "ms_per_step": ms, "steps": steps,
-        "n_gpus": world, "dtype": "bf16", "tokens_per_s": T * world / (ms * 1e-3),
+        "n_gpus": world, "dtype": "bf16", "tokens_per_s": T * world / (ms * 1e-3), "ms_per_step_cuda_graph": ms_graph,
         "config": {"workload": "one TinyLLaMA decoder block, bf16, 16384 tokens (B=8, S=2048), causal, 10 launches",
                    "flops_per_step_per_gpu": flops},
         "roofline": {"bound": "tensor", "achieved": tf / world, "peak": pk["tensor"], "unit": "TFLOP/s",

@@ -168,3 +168,20 @@ def test_bf16_decoder_layer_against_staged_fp64(lib):
     res, pend = layer.forward_parts(tx)
     res2, pend2 = layer2.forward_parts(res, pending=pend)
     assert torch.equal(res2 + pend2, plain)
+
+
+def test_graphed_decoder_layer_equals_eager(lib):
+    """The block captured into a CUDA graph returns the bits of the eager block, call after call."""
+    from baranet_bdml_b200.layers import GraphedDecoderLayerBF16, LLaMAConfig, LLaMADecoderLayerBF16
+    cfg = LLaMAConfig(hidden_size=512, num_attention_heads=8, num_key_value_heads=2, intermediate_size=1408,
+                      num_hidden_layers=1)
+    np.random.seed(21)
+    layer = LLaMADecoderLayerBF16(cfg)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    xs = [torch.randn((2, 160, 512), generator=g, device="cuda").to(torch.bfloat16) for _ in range(3)]
+    graphed = GraphedDecoderLayerBF16(layer, xs[0])
+    for x in xs:
+        res_e, mlp_e = layer.forward_parts(x)
+        res_g, mlp_g = graphed(x)
+        torch.cuda.synchronize()
+        assert torch.equal(res_e, res_g) and torch.equal(mlp_e, mlp_g)
