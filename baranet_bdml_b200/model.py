@@ -1,0 +1,159 @@
+"""LLaMAModel on the bf16 path with a paged KV cache: `generate()` without whole-sequence recomputation.
+
+Mirror of mygrad/llama/llama_model.py (`LLaMAModel`: embed_tokens, layers, norm, lm_head; `__call__`, `generate`),
+composed from the rows of this package: device-side embedding gather, `LLaMADecoderLayerBF16` blocks for the prompt,
+and for every new token one row per sequence through the same weights with `bn_kv_append` + `bn_attn_decode_paged`
+instead of attention over the recomputed sequence (the reference recomputes the whole sequence for every token and
+keeps the last row, llama_model.py:136-144), then the final norm, the lm_head GEMM and a device-side argmax.
+Greedy decoding only (temperature / top-k sampling of the reference is host code).  Inference only.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import numpy as np
+import torch
+
+from . import _lib, ops
+from .kv_cache import PAGE_TOKENS, PagedKVCache
+from .layers import LLaMAConfig, LLaMADecoderLayerBF16
+
+
+class LLaMAModelBF16:
+    def __init__(self, config: LLaMAConfig, is_cuda: bool = True):
+        if not is_cuda:
+            raise RuntimeError("LLaMAModelBF16: only GPU implementation available")
+        self.config = config
+        # embed_tokens as the reference initialises it (llama_model.py:44-50: normal, std 0.02), fp32 table
+        self.embed_tokens = torch.from_numpy(
+            (np.random.randn(config.vocab_size, config.hidden_size) * 0.02).astype(np.float32)).cuda()
+        self.layers = [LLaMADecoderLayerBF16(config) for _ in range(config.num_hidden_layers)]
+        self.norm_weight = torch.ones(config.hidden_size, dtype=torch.bfloat16, device="cuda")
+        std = np.sqrt(2.0 / (config.hidden_size + config.vocab_size))
+        w = np.random.randn(config.hidden_size, config.vocab_size).astype(np.float32) * std
+        self.lm_head = torch.from_numpy(np.ascontiguousarray(w.T)).cuda().to(torch.bfloat16)    # (vocab, hidden)
+        self.caches: Optional[List[PagedKVCache]] = None
+
+    # ------------------------------------------------------------------ pieces
+    def embed(self, input_ids: torch.Tensor) -> torch.Tensor:
+        """(n,) int32 token ids on the device -> (n, hidden) bf16 (gather on the device)."""
+        ids = input_ids.to(torch.int32).contiguous()
+        n, H = ids.numel(), self.config.hidden_size
+        out = torch.empty((n, H), dtype=torch.float32, device="cuda")
+        err = torch.zeros(1, dtype=torch.int32, device="cuda")
+        _lib.check(_lib.load().bn_embedding_gather_f32(self.embed_tokens.data_ptr(), H, ids.data_ptr(), out.data_ptr(), H,
+                                                       n, H, self.config.vocab_size, err.data_ptr(),
+                                                       torch.cuda.current_stream().cuda_stream))
+        if int(err.item()) != 0:
+            raise IndexError("token id out of range")
+        return out.to(torch.bfloat16)
+
+    def _logits(self, residual: torch.Tensor, pending: torch.Tensor) -> torch.Tensor:
+        """final norm of (residual + pending), lm_head: (rows, hidden) -> (rows, vocab) fp32"""
+        _, normed = ops.add_rmsnorm_bf16(residual, pending, self.norm_weight, self.config.rms_norm_eps, want_sum=False)
+        return ops.gemm_bf16_nt(normed, self.lm_head).float()
+
+    def argmax(self, logits: torch.Tensor) -> torch.Tensor:
+        rows, cols = logits.shape
+        out = torch.zeros((rows,), dtype=torch.int32, device="cuda")
+        _lib.check(_lib.load().bn_argmax_rows_f32(logits.data_ptr(), logits.stride(0), logits.stride(1), out.data_ptr(),
+                                                  rows, cols, torch.cuda.current_stream().cuda_stream))
+        return out
+
+    # ----------------------------------------------------------------- forward
+    def __call__(self, input_ids: torch.Tensor, position_offset: int = 0, use_causal_mask: bool = True) -> torch.Tensor:
+        """Whole-sequence forward as the reference's `__call__` (llama_model.py:80-110): (B, S) ids -> (B, S, vocab)."""
+        B, S = input_ids.shape
+        h = self.embed(input_ids.reshape(-1)).view(B, S, -1)
+        pending = None
+        for layer in self.layers:
+            h, pending = layer.forward_parts(h, position_offset, use_causal_mask, pending=pending)
+        H = self.config.hidden_size
+        return self._logits(h.reshape(B * S, H), pending.reshape(B * S, H)).view(B, S, -1)
+
+    def _alloc_caches(self, B: int, max_len: int):
+        cfg = self.config
+        pages_per_seq = (max_len + PAGE_TOKENS - 1) // PAGE_TOKENS
+        self.caches = []
+        for _ in self.layers:
+            c = PagedKVCache(B * pages_per_seq, B, pages_per_seq, cfg.num_key_value_heads, cfg.head_dim, cfg.rope_theta)
+            c.page_table.copy_(torch.arange(B * pages_per_seq, dtype=torch.int32, device="cuda").view(B, pages_per_seq))
+            self.caches.append(c)
+
+    def prefill(self, input_ids: torch.Tensor, max_len: int) -> torch.Tensor:
+        """Prompt pass: (B, S) ids -> logits of the last position (B, vocab); fills the KV caches."""
+        cfg = self.config
+        B, S = input_ids.shape
+        self._alloc_caches(B, max_len)
+        h = self.embed(input_ids.reshape(-1)).view(B, S, -1)
+        seq_ids = torch.arange(B, dtype=torch.int32, device="cuda").repeat_interleave(S)
+        positions = torch.arange(S, dtype=torch.int32, device="cuda").repeat(B)
+        pending = None
+        H = cfg.hidden_size
+        for layer, cache in zip(self.layers, self.caches):
+            x2 = h.reshape(B * S, H)
+            residual, normed = ops.add_rmsnorm_bf16(x2, None if pending is None else pending.reshape(B * S, H),
+                                                    layer.input_layernorm_weight, layer.eps)
+            at = layer.self_attn
+            q = ops.gemm_bf16_nt(normed, at.q_proj).view(B, S, at.num_heads, at.head_dim)
+            k = ops.gemm_bf16_nt(normed, at.k_proj)
+            v = ops.gemm_bf16_nt(normed, at.v_proj)
+            cache.append(seq_ids, positions, k, v)                # RoPE(K) + page write
+            cache.seq_lens.fill_(S)
+            attn = ops.attn_prefill_bf16(q, k.view(B, S, at.num_kv_heads, at.head_dim),
+                                         v.view(B, S, at.num_kv_heads, at.head_dim), scale=float(at.scale),
+                                         theta=at.rotary_emb.base, causal=True)
+            o = ops.gemm_bf16_nt(attn.view(B * S, H), at.o_proj)
+            residual, normed = ops.add_rmsnorm_bf16(residual, o, layer.post_attention_layernorm_weight, layer.eps)
+            h, pending = residual.view(B, S, H), layer.mlp(normed).view(B, S, H)
+        return self._logits(h[:, -1].contiguous(), pending[:, -1].contiguous())
+
+    def decode_step(self, token_ids: torch.Tensor) -> torch.Tensor:
+        """One new token per sequence: (B,) ids -> (B, vocab) logits; appends to the caches."""
+        B = token_ids.numel()
+        h = self.embed(token_ids)
+        seq_ids = torch.arange(B, dtype=torch.int32, device="cuda")
+        pending = None
+        for layer, cache in zip(self.layers, self.caches):
+            positions = cache.seq_lens.clone()                    # the new token's position = current length
+            residual, normed = ops.add_rmsnorm_bf16(h, pending, layer.input_layernorm_weight, layer.eps)
+            at = layer.self_attn
+            q = ops.gemm_bf16_nt(normed, at.q_proj).view(B, at.num_heads, at.head_dim)
+            k = ops.gemm_bf16_nt(normed, at.k_proj)
+            v = ops.gemm_bf16_nt(normed, at.v_proj)
+            cache.append(seq_ids, positions, k, v)
+            cache.seq_lens.add_(1)
+            attn = cache.decode(q, num_heads=at.num_heads, scale=float(at.scale))      # RoPE(q) at position len - 1
+            o = ops.gemm_bf16_nt(attn.view(B, -1), at.o_proj)
+            residual, normed = ops.add_rmsnorm_bf16(residual, o, layer.post_attention_layernorm_weight, layer.eps)
+            h, pending = residual, layer.mlp(normed)
+        return self._logits(h, pending)
+
+    def generate(self, input_ids: np.ndarray, max_new_tokens: int = 50) -> List[List[int]]:
+        """Greedy `generate` (llama_model.py:112-168 with temperature -> 0): prompts (B, S) of equal length."""
+        ids = torch.from_numpy(np.ascontiguousarray(input_ids, dtype=np.int32)).cuda()
+        if ids.dim() == 1:
+            ids = ids[None]
+        B, S = ids.shape
+        logits = self.prefill(ids, S + max_new_tokens)
+        out = [list(map(int, row)) for row in ids.cpu().numpy()]
+        done = [False] * B
+        for _ in range(max_new_tokens):
+            nxt = self.argmax(logits)
+            host = nxt.cpu().numpy()
+            for b in range(B):
+                if not done[b]:
+                    if int(host[b]) == self.config.eos_token_id:
+                        done[b] = True
+                    else:
+                        out[b].append(int(host[b]))
+            if all(done):
+                break
+            logits = self.decode_step(nxt)
+        return out
+
+    def parameters(self):
+        p = [self.embed_tokens]
+        for layer in self.layers:
+            p.extend(layer.parameters())
+        return p + [self.norm_weight, self.lm_head]

@@ -1,0 +1,59 @@
+"""The bf16 model with a paged KV cache: one-token decode steps against whole-sequence recomputation (what the
+reference's generate() does, mygrad/llama/llama_model.py:136-144), on the same weights."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def tiny_model(seed=0):
+    from baranet_bdml_b200.layers import LLaMAConfig
+    from baranet_bdml_b200.model import LLaMAModelBF16
+    cfg = LLaMAConfig(vocab_size=1000, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=256)
+    np.random.seed(seed)
+    return LLaMAModelBF16(cfg)
+
+
+def test_cached_decode_matches_recomputation(lib):
+    """Logits of every new position from prefill + decode steps (K/V from the cache, one query row) against the last
+    row of a whole-sequence forward over the same tokens.  Both run bf16 kernels with different reduction orders, so
+    the gate is a tolerance: 3e-2 of the logit range."""
+    model = tiny_model()
+    rng = np.random.default_rng(1)
+    B, S, new = 3, 37, 6
+    ids = torch.from_numpy(rng.integers(3, 1000, (B, S + new)).astype(np.int32)).cuda()
+    logits = model.prefill(ids[:, :S].contiguous(), S + new)
+    for t in range(new + 1):
+        full = model(ids[:, :S + t].contiguous())[:, -1]             # recompute everything, keep the last row
+        torch.cuda.synchronize()
+        scale = float(full.abs().max())
+        assert float((logits - full).abs().max()) <= 3e-2 * scale, (t, float((logits - full).abs().max()), scale)
+        if t < new:
+            logits = model.decode_step(ids[:, S + t].contiguous())
+    assert int(model.caches[0].seq_lens[0]) == S + new
+
+
+def test_generate_greedy_equals_recompute_generate(lib):
+    """Greedy generate() with the cache picks the tokens that recomputing the whole sequence would pick, as long as
+    the best two logits of the recomputed row are further apart than the bf16 tolerance of the two paths."""
+    model = tiny_model(3)
+    rng = np.random.default_rng(4)
+    prompt = rng.integers(3, 1000, (2, 20)).astype(np.int32)
+    out = model.generate(prompt, max_new_tokens=5)
+    assert all(len(o) >= 20 for o in out)
+    for b in range(2):
+        seq = list(prompt[b])
+        for tok in out[b][20:]:
+            full = model(torch.tensor([seq], dtype=torch.int32, device="cuda"))[0, -1]
+            top2 = torch.topk(full, 2).values
+            if float(top2[0] - top2[1]) > 3e-2 * float(full.abs().max()):
+                assert int(torch.argmax(full)) == tok
+            seq.append(tok)
+
+
+def test_model_rejects_bad_ids(lib):
+    model = tiny_model()
+    with pytest.raises(IndexError):
+        model.embed(torch.tensor([5, 1000], dtype=torch.int32, device="cuda"))
