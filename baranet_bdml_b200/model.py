@@ -35,8 +35,9 @@ class LLaMAModelBF16:
         self.caches: Optional[List[PagedKVCache]] = None
 
     # ------------------------------------------------------------------ pieces
-    def embed(self, input_ids: torch.Tensor) -> torch.Tensor:
-        """(n,) int32 token ids on the device -> (n, hidden) bf16 (gather on the device)."""
+    def embed(self, input_ids: torch.Tensor, check: bool = True) -> torch.Tensor:
+        """(n,) int32 token ids on the device -> (n, hidden) bf16 (gather on the device).  `check=False` skips the
+        host read of the out-of-range flag (a synchronisation), for use inside a CUDA graph."""
         ids = input_ids.to(torch.int32).contiguous()
         n, H = ids.numel(), self.config.hidden_size
         out = torch.empty((n, H), dtype=torch.float32, device="cuda")
@@ -44,7 +45,7 @@ class LLaMAModelBF16:
         _lib.check(_lib.load().bn_embedding_gather_f32(self.embed_tokens.data_ptr(), H, ids.data_ptr(), out.data_ptr(), H,
                                                        n, H, self.config.vocab_size, err.data_ptr(),
                                                        torch.cuda.current_stream().cuda_stream))
-        if int(err.item()) != 0:
+        if check and int(err.item()) != 0:
             raise IndexError("token id out of range")
         return out.to(torch.bfloat16)
 
@@ -108,10 +109,10 @@ class LLaMAModelBF16:
             h, pending = residual.view(B, S, H), layer.mlp(normed).view(B, S, H)
         return self._logits(h[:, -1].contiguous(), pending[:, -1].contiguous())
 
-    def decode_step(self, token_ids: torch.Tensor) -> torch.Tensor:
+    def decode_step(self, token_ids: torch.Tensor, check: bool = True) -> torch.Tensor:
         """One new token per sequence: (B,) ids -> (B, vocab) logits; appends to the caches."""
         B = token_ids.numel()
-        h = self.embed(token_ids)
+        h = self.embed(token_ids, check)
         seq_ids = torch.arange(B, dtype=torch.int32, device="cuda")
         pending = None
         for layer, cache in zip(self.layers, self.caches):
@@ -128,6 +129,35 @@ class LLaMAModelBF16:
             residual, normed = ops.add_rmsnorm_bf16(residual, o, layer.post_attention_layernorm_weight, layer.eps)
             h, pending = residual, layer.mlp(normed)
         return self._logits(h, pending)
+
+    def capture_decode_step(self):
+        """Captures `decode_step` + argmax for the current batch into a CUDA graph: a step is about 30 launches that
+        Python issues one by one (the host, not the GPU, bounds it); replayed from a graph they are one submission.
+        Returns step(token_ids) -> (logits, next_ids), both static buffers overwritten by the next call.  The caches'
+        lengths advance inside the graph, so every replay is the next position."""
+        B = self.caches[0].num_seqs
+        static_tok = torch.zeros((B,), dtype=torch.int32, device="cuda")
+        saved = [c.seq_lens.clone() for c in self.caches]
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):                      # warm-up outside the capture (workspaces, attributes)
+            self.decode_step(static_tok, check=False)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = self.decode_step(static_tok, check=False)
+            nxt = self.argmax(logits)
+        torch.cuda.synchronize()
+        for c, s0 in zip(self.caches, saved):              # warm-up and capture must not count as positions
+            c.seq_lens.copy_(s0)
+
+        def step(token_ids: torch.Tensor):
+            static_tok.copy_(token_ids)
+            graph.replay()
+            return logits, nxt
+
+        step.graph = graph
+        return step
 
     def generate(self, input_ids: np.ndarray, max_new_tokens: int = 50) -> List[List[int]]:
         """Greedy `generate` (llama_model.py:112-168 with temperature -> 0): prompts (B, S) of equal length."""

@@ -53,6 +53,25 @@ def test_generate_greedy_equals_recompute_generate(lib):
             seq.append(tok)
 
 
+def test_graphed_decode_step_equals_eager(lib):
+    """The decode step replayed from a CUDA graph gives the bits of the eager step, position after position."""
+    rng = np.random.default_rng(6)
+    ids = torch.from_numpy(rng.integers(3, 1000, (2, 30)).astype(np.int32)).cuda()
+    toks = torch.from_numpy(rng.integers(3, 1000, (4, 2)).astype(np.int32)).cuda()
+    eager = tiny_model(5)
+    eager.prefill(ids, 64)
+    want = [eager.decode_step(t).clone() for t in toks]
+    graphed = tiny_model(5)                       # same seed: same weights
+    graphed.prefill(ids, 64)
+    step = graphed.capture_decode_step()
+    for t, w in zip(toks, want):
+        logits, nxt = step(t)
+        torch.cuda.synchronize()
+        assert torch.equal(logits, w)
+        assert torch.equal(nxt, graphed.argmax(w))
+    assert int(graphed.caches[0].seq_lens[0]) == 34
+
+
 def test_model_rejects_bad_ids(lib):
     model = tiny_model()
     with pytest.raises(IndexError):
