@@ -26,28 +26,36 @@ namespace bn {
 
 using namespace ptx;
 
-constexpr int GM_BM = 128, GM_BN = 256, GM_BK = 64;
-constexpr int GM_NSTAGE = 4;
+constexpr int GM_BM = 128, GM_BK = 64;
 constexpr int GM_A_BYTES = GM_BM * GM_BK * 2;          // 16384
-constexpr int GM_B_BYTES = GM_BN * GM_BK * 2;          // 32768
-constexpr int GM_STAGE_BYTES = GM_A_BYTES + GM_B_BYTES;
-constexpr int GM_SMEM_BYTES = 1024 + GM_NSTAGE * GM_STAGE_BYTES;
 constexpr int GM_THREADS = 192;
-constexpr uint32_t GM_TMEM_COLS = 512;                 // two accumulators of 256 columns
+// per N-tile width BN (256: the throughput shape; 64: many small tiles for M <= 128, where the weight stream has to
+// be spread over all SMs): ring depth, bytes, TMEM columns (two accumulators of BN columns, a power of two >= 32)
+template <int BN> struct GemmShape {
+    static constexpr int NSTAGE = BN == 256 ? 4 : 8;
+    static constexpr int B_BYTES = BN * GM_BK * 2;
+    static constexpr int STAGE_BYTES = GM_A_BYTES + B_BYTES;
+    static constexpr int SMEM_BYTES = 1024 + NSTAGE * STAGE_BYTES;
+    static constexpr uint32_t TMEM_COLS = 2 * BN;
+};
 
 struct GemmParams {
     __nv_bfloat16* c;
     int* error_word;       // optional
     int M, N, K;           // N = rows of Bt
     int n_out;             // columns of C: N (plain) or the intermediate size (SwiGLU)
+    float* partial;        // EPI_PARTIAL: [split][M][N] fp32
+    int splits, k_per_split;   // EPI_PARTIAL: K steps are cut into `splits` ranges of k_per_split steps
 };
 
-constexpr int EPI_PLAIN = 0, EPI_SWIGLU = 1;
+constexpr int EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_PARTIAL = 2;
 
-template <int EPI>
+template <int EPI, int GM_BN>
 __global__ void __launch_bounds__(GM_THREADS, 1)
 gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const GemmParams p) {
+    constexpr int GM_NSTAGE = GemmShape<GM_BN>::NSTAGE, GM_STAGE_BYTES = GemmShape<GM_BN>::STAGE_BYTES;
+    constexpr uint32_t GM_TMEM_COLS = GemmShape<GM_BN>::TMEM_COLS;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[GM_NSTAGE], bar_empty[GM_NSTAGE], bar_acc_full[2], bar_acc_empty[2];
     __shared__ uint32_t s_tmem_base;
@@ -56,8 +64,19 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int tiles_m = (p.M + GM_BM - 1) / GM_BM, tiles_n = (p.N + GM_BN - 1) / GM_BN;
-    const int n_tiles = tiles_m * tiles_n;
-    const int k_steps = (p.K + GM_BK - 1) / GM_BK;
+    const int k_steps_all = (p.K + GM_BK - 1) / GM_BK;
+    // a work item is an output tile, or (EPI_PARTIAL) a tile and one range of the K steps
+    const int splits = EPI == EPI_PARTIAL ? p.splits : 1;
+    const int n_tiles = tiles_m * tiles_n * splits;
+    auto k_range = [&](int t, int& ks0, int& ks1) {
+        if (EPI == EPI_PARTIAL) {
+            ks0 = (t / (tiles_m * tiles_n)) * p.k_per_split;
+            ks1 = min(k_steps_all, ks0 + p.k_per_split);
+        } else {
+            ks0 = 0;
+            ks1 = k_steps_all;
+        }
+    };
 
     if (tid == 0) {
         for (int s = 0; s < GM_NSTAGE; ++s) {
@@ -88,8 +107,10 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             uint32_t it = 0;      // ring steps issued
             bool ok = true;
             for (int t = blockIdx.x; ok && t < n_tiles; t += gridDim.x) {
-                const int m0 = (t % tiles_m) * GM_BM, n0 = (t / tiles_m) * GM_BN;
-                for (int ks = 0; ks < k_steps; ++ks, ++it) {
+                const int m0 = (t % tiles_m) * GM_BM, n0 = ((t / tiles_m) % tiles_n) * GM_BN;
+                int ks0, ks1;
+                k_range(t, ks0, ks1);
+                for (int ks = ks0; ks < ks1; ++ks, ++it) {
                     const int stage = it % GM_NSTAGE;
                     ok = mbar_wait(smem_u32(&bar_empty[stage]), ((it / GM_NSTAGE) & 1u) ^ 1u, &s_abort);
                     if (!ok) break;
@@ -112,7 +133,9 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             ok = mbar_wait(smem_u32(&bar_acc_empty[acc]), ((local >> 1) & 1u) ^ 1u, &s_abort);
             if (!ok) break;
             tc::fence_after_sync();
-            for (int ks = 0; ks < k_steps; ++ks, ++it) {
+            int ks0, ks1;
+            k_range(t, ks0, ks1);
+            for (int ks = ks0; ks < ks1; ++ks, ++it) {
                 const int stage = it % GM_NSTAGE;
                 ok = mbar_wait(smem_u32(&bar_full[stage]), (it / GM_NSTAGE) & 1u, &s_abort);
                 if (!ok) break;
@@ -122,9 +145,9 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
                     for (int kk = 0; kk < GM_BK / 16; ++kk)
                         tc::mma_ss(tmem + acc * GM_BN, dZero + (uint64_t)((sA >> 4) + kk * 2),
-                                   dZero + (uint64_t)((sB >> 4) + kk * 2), IDESC, (ks > 0) || (kk > 0));
+                                   dZero + (uint64_t)((sB >> 4) + kk * 2), IDESC, (ks > ks0) || (kk > 0));
                     tc::commit(smem_u32(&bar_empty[stage]));                       // the stage may be refilled
-                    if (ks == k_steps - 1) tc::commit(smem_u32(&bar_acc_full[acc]));  // the tile is complete
+                    if (ks == ks1 - 1) tc::commit(smem_u32(&bar_acc_full[acc]));  // the tile is complete
                 }
                 __syncwarp();
             }
@@ -137,7 +160,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         bool ok = true;
         for (int t = blockIdx.x; ok && t < n_tiles; t += gridDim.x, ++local) {
             const uint32_t acc = local & 1u;
-            const int m0 = (t % tiles_m) * GM_BM, n0 = (t / tiles_m) * GM_BN;
+            const int m0 = (t % tiles_m) * GM_BM, n0 = ((t / tiles_m) % tiles_n) * GM_BN;
             ok = mbar_wait(smem_u32(&bar_acc_full[acc]), (local >> 1) & 1u, &s_abort);
             if (!ok) break;
             tc::fence_after_sync();
@@ -161,6 +184,25 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                                 o4.w = pack_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
                                 *reinterpret_cast<uint4*>(crow + c * 32 + v * 8) = o4;
                             }
+                        }
+                    }
+                }
+            } else if (EPI == EPI_PARTIAL) {
+                // the fp32 partial sum of this K range; the ranges are added in order by the reduce kernel
+                float* prow = p.partial + ((size_t)(t / (tiles_m * tiles_n)) * p.M + gm) * p.N + n0;
+#pragma unroll 1
+                for (int c = 0; c < GM_BN / 32; ++c) {
+                    uint32_t r[32];
+                    tc::ld32(tmem + lane_base + acc * GM_BN + c * 32, r);
+                    tc::wait_ld(r);
+                    if (gm < p.M) {
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) {
+                            const int col = n0 + c * 32 + v * 4;
+                            if (col < p.N)          // N is a multiple of 8
+                                *reinterpret_cast<float4*>(prow + c * 32 + v * 4) =
+                                    make_float4(__uint_as_float(r[v * 4]), __uint_as_float(r[v * 4 + 1]),
+                                                __uint_as_float(r[v * 4 + 2]), __uint_as_float(r[v * 4 + 3]));
                         }
                     }
                 }
@@ -219,8 +261,47 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
 using namespace bn;
 
+// sum of the split-K partials, in split order (deterministic), rounded once to bf16
+__global__ void __launch_bounds__(256)
+gemm_splitk_reduce_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ c, long long mn4, int splits) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;     // one group of 4 outputs
+    if (i >= mn4) return;
+    const float4* p4 = reinterpret_cast<const float4*>(partial);
+    float4 acc = __ldcg(p4 + i);
+    for (int s = 1; s < splits; ++s) {
+        const float4 v = __ldcg(p4 + (long long)s * mn4 + i);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    reinterpret_cast<uint2*>(c)[i] = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
+}
+
+// how a small-M product is cut: 64-wide N tiles, and the K steps into `splits` ranges so that about one work item
+// per SM exists; never more than 8 ranges (the partial sums are extra traffic) nor ranges shorter than 4 K steps
+static void splitk_plan(int M, int N, int K, int sms, int* splits, int* k_per_split) {
+    const long long tiles = (long long)((M + GM_BM - 1) / GM_BM) * ((N + 63) / 64);
+    const int k_steps = (K + GM_BK - 1) / GM_BK;
+    long long want = tiles >= sms ? 1 : (sms + tiles - 1) / tiles;
+    if (want > 8) want = 8;
+    if (want > k_steps / 4) want = k_steps / 4 > 0 ? k_steps / 4 : 1;
+    const int per = (int)((k_steps + want - 1) / want);
+    *k_per_split = per;
+    *splits = (k_steps + per - 1) / per;
+}
+
+template <int EPI, int BN>
+static int gemm_configure(int dev) {
+    static thread_local int configured_dev = -1;
+    if (configured_dev == dev) return BN_OK;
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_nt_kernel<EPI, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         GemmShape<BN>::SMEM_BYTES);
+    if (e != cudaSuccess) return fail(BN_ERR_CUDA, "cudaFuncSetAttribute(gemm): %s", cudaGetErrorString(e));
+    configured_dev = dev;
+    return BN_OK;
+}
+
 static int gemm_launch(const void* a, const void* bt, void* c, int M, int N, int K, int n_out, int epi, int* error_word,
-                       bn_stream_t stream, const char* what) {
+                       bn_stream_t stream, const char* what, float* partial = nullptr, int splits = 1,
+                       int k_per_split = 0) {
     if (!a || !bt || !c) return fail(BN_ERR_INVALID_ARG, "%s: null pointer", what);
     if (M < 0 || N < 0 || K < 0 || n_out < 0) return fail(BN_ERR_INVALID_ARG, "%s: bad shape M=%d N=%d K=%d", what, M, N, K);
     if (n_out % 8 || K % 8)
@@ -233,6 +314,7 @@ static int gemm_launch(const void* a, const void* bt, void* c, int M, int N, int
         cudaError_t e = cudaMemsetAsync(c, 0, (size_t)M * n_out * 2, as_stream(stream));
         return e == cudaSuccess ? BN_OK : fail(BN_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
     }
+    const int bn = epi == EPI_PARTIAL ? 64 : 256;
     CUtensorMap tmap_a, tmap_b;
     {
         const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M}, strides[1] = {(uint64_t)K * 2};
@@ -243,31 +325,32 @@ static int gemm_launch(const void* a, const void* bt, void* c, int M, int N, int
     }
     {
         const uint64_t dims[2] = {(uint64_t)K, (uint64_t)N}, strides[1] = {(uint64_t)K * 2};
-        const uint32_t box[2] = {GM_BK, GM_BN};
+        const uint32_t box[2] = {GM_BK, (uint32_t)bn};
         if (int rc = make_tensor_map(&tmap_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, bt, dims, strides, box,
                                      CU_TENSOR_MAP_SWIZZLE_128B))
             return rc;
     }
-    static thread_local int configured_dev = -1;
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
-    if (configured_dev != dev) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_nt_kernel<EPI_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             GM_SMEM_BYTES);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(gemm_bf16_nt_kernel<EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     GM_SMEM_BYTES);
-        if (e != cudaSuccess) return fail(BN_ERR_CUDA, "cudaFuncSetAttribute(gemm): %s", cudaGetErrorString(e));
-        configured_dev = dev;
-    }
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const long long n_tiles = (long long)((M + GM_BM - 1) / GM_BM) * ((N + GM_BN - 1) / GM_BN);
-    GemmParams p{static_cast<__nv_bfloat16*>(c), error_word, M, N, K, n_out};
-    const unsigned grid = (unsigned)(n_tiles < sms ? n_tiles : sms);
-    if (epi == EPI_PLAIN)
-        gemm_bf16_nt_kernel<EPI_PLAIN><<<grid, GM_THREADS, GM_SMEM_BYTES, as_stream(stream)>>>(tmap_a, tmap_b, p);
-    else
-        gemm_bf16_nt_kernel<EPI_SWIGLU><<<grid, GM_THREADS, GM_SMEM_BYTES, as_stream(stream)>>>(tmap_a, tmap_b, p);
+    const long long n_items = (long long)((M + GM_BM - 1) / GM_BM) * ((N + bn - 1) / bn) * splits;
+    GemmParams p{static_cast<__nv_bfloat16*>(c), error_word, M, N, K, n_out, partial, splits, k_per_split};
+    const unsigned grid = (unsigned)(n_items < sms ? n_items : sms);
+    cudaStream_t st = as_stream(stream);
+    if (epi == EPI_PLAIN) {
+        if (int rc = gemm_configure<EPI_PLAIN, 256>(dev)) return rc;
+        gemm_bf16_nt_kernel<EPI_PLAIN, 256><<<grid, GM_THREADS, GemmShape<256>::SMEM_BYTES, st>>>(tmap_a, tmap_b, p);
+    } else if (epi == EPI_SWIGLU) {
+        if (int rc = gemm_configure<EPI_SWIGLU, 256>(dev)) return rc;
+        gemm_bf16_nt_kernel<EPI_SWIGLU, 256><<<grid, GM_THREADS, GemmShape<256>::SMEM_BYTES, st>>>(tmap_a, tmap_b, p);
+    } else {
+        if (int rc = gemm_configure<EPI_PARTIAL, 64>(dev)) return rc;
+        gemm_bf16_nt_kernel<EPI_PARTIAL, 64><<<grid, GM_THREADS, GemmShape<64>::SMEM_BYTES, st>>>(tmap_a, tmap_b, p);
+        if (int rc = launch_status(what)) return rc;
+        const long long mn4 = (long long)M * N / 4;
+        gemm_splitk_reduce_kernel<<<(unsigned)((mn4 + 255) / 256), 256, 0, st>>>(partial, static_cast<__nv_bfloat16*>(c),
+                                                                             mn4, splits);
+    }
     return launch_status(what);
 }
 
@@ -281,4 +364,31 @@ extern "C" int bn_gemm_swiglu_bf16_nt(const void* x, const void* gate_up_t, void
     if (inter < 0) return fail(BN_ERR_INVALID_ARG, "bn_gemm_swiglu_bf16_nt: bad shape inter=%d", inter);
     const int n_rows = (inter + 127) / 128 * 256;      // rows of the packed gate/up weight
     return gemm_launch(x, gate_up_t, h, M, n_rows, K, inter, EPI_SWIGLU, error_word, stream, "bn_gemm_swiglu_bf16_nt");
+}
+
+extern "C" size_t bn_gemm_bf16_nt_small_m_workspace_bytes(int M, int N, int K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    int dev = 0, sms = 0, splits = 1, per = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+    splitk_plan(M, N, K, sms, &splits, &per);
+    return (size_t)splits * M * N * sizeof(float);
+}
+
+extern "C" int bn_gemm_bf16_nt_small_m(const void* a, const void* bt, void* c, int M, int N, int K, void* workspace,
+                                       size_t workspace_bytes, int* error_word, bn_stream_t stream) {
+    if (M > 0 && N > 0 && K > 0) {
+        if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15))
+            return fail(BN_ERR_WORKSPACE, "bn_gemm_bf16_nt_small_m: workspace missing or not 16-byte aligned");
+        int dev = 0, sms = 0, splits = 1, per = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        splitk_plan(M, N, K, sms, &splits, &per);
+        if (workspace_bytes < (size_t)splits * M * N * sizeof(float))
+            return fail(BN_ERR_WORKSPACE, "bn_gemm_bf16_nt_small_m: workspace of %zu bytes is too small", workspace_bytes);
+        return gemm_launch(a, bt, c, M, N, K, N, EPI_PARTIAL, error_word, stream, "bn_gemm_bf16_nt_small_m",
+                           static_cast<float*>(workspace), splits, per);
+    }
+    return gemm_launch(a, bt, c, M, N, K, N, EPI_PARTIAL, error_word, stream, "bn_gemm_bf16_nt_small_m");
 }

@@ -208,10 +208,12 @@ class MLPBF16:
         self.intermediate_size = inter
         self._gate_up = ops.pack_gate_up(self.gate_proj, self.up_proj)
 
-    def __call__(self, x):
+    def __call__(self, x, few_rows: bool = False):
         from . import ops
         h = ops.gemm_swiglu_bf16_nt(x, self._gate_up, self.intermediate_size)
-        return ops.gemm_bf16_nt(h, self.down_proj)
+        # the down projection has few output tiles: with few rows (a decode step) the split-K form streams its weight
+        # with all SMs
+        return ops.linear_bf16(h, self.down_proj) if few_rows else ops.gemm_bf16_nt(h, self.down_proj)
 
     def parameters(self):
         return [self.gate_proj, self.up_proj, self.down_proj]

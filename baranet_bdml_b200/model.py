@@ -119,15 +119,15 @@ class LLaMAModelBF16:
             positions = cache.seq_lens.clone()                    # the new token's position = current length
             residual, normed = ops.add_rmsnorm_bf16(h, pending, layer.input_layernorm_weight, layer.eps)
             at = layer.self_attn
-            q = ops.gemm_bf16_nt(normed, at.q_proj).view(B, at.num_heads, at.head_dim)
-            k = ops.gemm_bf16_nt(normed, at.k_proj)
-            v = ops.gemm_bf16_nt(normed, at.v_proj)
+            q = ops.linear_bf16(normed, at.q_proj).view(B, at.num_heads, at.head_dim)
+            k = ops.linear_bf16(normed, at.k_proj)
+            v = ops.linear_bf16(normed, at.v_proj)
             cache.append(seq_ids, positions, k, v)
             cache.seq_lens.add_(1)
             attn = cache.decode(q, num_heads=at.num_heads, scale=float(at.scale))      # RoPE(q) at position len - 1
-            o = ops.gemm_bf16_nt(attn.view(B, -1), at.o_proj)
+            o = ops.linear_bf16(attn.view(B, -1), at.o_proj)
             residual, normed = ops.add_rmsnorm_bf16(residual, o, layer.post_attention_layernorm_weight, layer.eps)
-            h, pending = residual, layer.mlp(normed)
+            h, pending = residual, layer.mlp(normed, few_rows=True)
         return self._logits(h, pending)
 
     def capture_decode_step(self):

@@ -88,6 +88,43 @@ def gemm_bf16_nt(a: torch.Tensor, bt: torch.Tensor, *, out: Optional[torch.Tenso
     return out
 
 
+_small_m_ws = {}
+
+
+def gemm_bf16_nt_small_m(a: torch.Tensor, bt: torch.Tensor, *, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a (M,K) @ bt (N,K)^T for few rows (a decode step: one token per sequence): the weight stream is spread over
+    all SMs (64-wide N tiles, K split, partial sums added in a fixed order).  The fp32 scratch is kept per
+    (device, size) and reused by later calls on the same stream."""
+    _need(a, torch.bfloat16, "gemm_bf16_nt_small_m(a)")
+    _need(bt, torch.bfloat16, "gemm_bf16_nt_small_m(bt)")
+    if a.dim() != 2 or bt.dim() != 2 or a.shape[1] != bt.shape[1]:
+        raise RuntimeError(f"MatMul: inner dimensions mismatch {tuple(a.shape)} x {tuple(bt.shape)}^T")
+    M, K = a.shape
+    N = bt.shape[0]
+    lib = _lib.load()
+    n = int(lib.bn_gemm_bf16_nt_small_m_workspace_bytes(M, N, K))
+    key = (a.device, n)
+    ws = _small_m_ws.get(key)
+    if ws is None:
+        ws = _small_m_ws[key] = torch.empty(max(n, 16), dtype=torch.uint8, device=a.device)
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    _need(out, torch.bfloat16, "gemm_bf16_nt_small_m(out)")
+    _lib.check(lib.bn_gemm_bf16_nt_small_m(a.data_ptr(), bt.data_ptr(), out.data_ptr(), M, N, K, ws.data_ptr(), n, None,
+                                           _stream()))
+    return out
+
+
+def linear_bf16(x: torch.Tensor, weight_t: torch.Tensor) -> torch.Tensor:
+    """x (rows, in) @ weight_t (out, in)^T, choosing the kernel by shape: with few rows and too few 256-wide output
+    tiles to occupy the GPU (measured cross-over: fewer than half as many tiles as SMs) the split-K small-M form,
+    otherwise the large-tile kernel."""
+    rows, n_out = x.shape[0], weight_t.shape[0]
+    if rows <= 128 and (n_out + 255) // 256 < 74:
+        return gemm_bf16_nt_small_m(x, weight_t)
+    return gemm_bf16_nt(x, weight_t)
+
+
 def add_rmsnorm_bf16(a: torch.Tensor, b: Optional[torch.Tensor], weight: torch.Tensor, eps: float = 1e-6, *,
                      want_sum: bool = True) -> Tuple[Optional[torch.Tensor], torch.Tensor]:
     """(a + b rounded to bf16, rmsnorm of that sum) for a bf16 residual stream (tokens, hidden); b None: plain norm."""

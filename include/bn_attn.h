@@ -118,6 +118,14 @@ BN_API int bn_argmax_rows_f32(const float* x, int64_t x_rs, int64_t x_cs, uint32
 BN_API int bn_gemm_bf16_nt(const void* a, const void* bt, void* c, int M, int N, int K, int* error_word,
                            bn_stream_t stream);
 
+/* The same product for FEW rows (M <= 128 is where it pays: one token per sequence in a decode step), where the
+ * weight matrix has to be streamed by all SMs: 64-wide N tiles and the K range cut into up to 8 parts, fp32 partial
+ * sums in `workspace`, added in a fixed order by a second small kernel (results do not depend on timing).
+ * workspace: bn_gemm_bf16_nt_small_m_workspace_bytes(M, N, K) bytes, 16-byte aligned; contents need not be kept. */
+BN_API size_t bn_gemm_bf16_nt_small_m_workspace_bytes(int M, int N, int K);
+BN_API int bn_gemm_bf16_nt_small_m(const void* a, const void* bt, void* c, int M, int N, int K, void* workspace,
+                                   size_t workspace_bytes, int* error_word, bn_stream_t stream);
+
 /* h (M, inter) bf16 = silu(x @ Wgate) * (x @ Wup): both GEMMs of the SwiGLU MLP, the activation and the product in
  * one launch of the tensor-core GEMM.  x (M,K) bf16; gate_up_t is the PACKED weight, ceil(inter/128)*256 rows of K
  * bf16: for every block of 128 intermediate indices, the 128 rows of Wgate^T followed by the 128 rows of Wup^T for

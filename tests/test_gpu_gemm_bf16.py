@@ -185,3 +185,24 @@ def test_graphed_decoder_layer_equals_eager(lib):
         res_g, mlp_g = graphed(x)
         torch.cuda.synchronize()
         assert torch.equal(res_e, res_g) and torch.equal(mlp_e, mlp_g)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 8, 8), (64, 2048, 2048), (64, 256, 2048), (17, 2048, 5632), (128, 1000, 520),
+                                   (64, 32000, 2048), (130, 136, 264)])
+def test_small_m_gemm(lib, M, N, K):
+    """The split-K form for few rows: against fp64 on the same operands, equal run to run (fixed summation order), and
+    within one bf16 ulp of the large-tile kernel."""
+    from baranet_bdml_b200 import ops
+    rng = np.random.default_rng(M * 3 + N + K)
+    a = R.round_bf16(rng.standard_normal((M, K), dtype=np.float32))
+    bt = R.round_bf16((rng.standard_normal((N, K)) * 0.05).astype(np.float32))
+    ta, tb = torch.from_numpy(a).cuda().to(torch.bfloat16), torch.from_numpy(bt).cuda().to(torch.bfloat16)
+    got = ops.gemm_bf16_nt_small_m(ta, tb)
+    again = ops.gemm_bf16_nt_small_m(ta, tb)
+    big = ops.gemm_bf16_nt(ta, tb)
+    torch.cuda.synchronize()
+    assert torch.equal(got, again)
+    ref = a.astype(np.float64) @ bt.astype(np.float64).T
+    scale = max(np.abs(ref).max(), 1e-30)
+    assert np.abs(got.float().cpu().numpy() - ref).max() <= scale * 2.0 ** -8
+    assert float((got.float() - big.float()).abs().max()) <= scale * 2.0 ** -7
