@@ -45,6 +45,7 @@ SIGNATURES = {
     "bn_attn_decode_paged": (_i, [_p, _p, _i64, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _f, _i, _i, _i,
                                   _p, _sz, _p]),
     "bn_attn_decode_paged_static": (_i, [_p, _p, _i64, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _f, _i, _i, _p]),
+    "bn_attn_decode_paged_static_status": (_i, [_p]),
     "bn_attn_lse_combine": (_i, [_p, _p, _i, _i64, _i, _p, _p, _p, _p]),
     "bn_attn_lse_combine_strided": (_i, [_p, _i64, _p, _i64, _i, _i64, _i, _p, _p, _p, _p]),
     "bn_workspace_status": (_i, [_p, _p]),

@@ -68,19 +68,25 @@ struct DecodeLayout {
     int max_parts;      // partial slots per (sequence, KV head)
 };
 
-static DecodeLayout decode_layout(int B, int Hkv, int max_seq_len, int min_tokens) {
+// `ticket_slots` is the capacity of the ticket region, NOT B * Hkv: the tickets are the only words of the scratch
+// that outlive a launch (a merging CTA re-arms the ones it used), so their place must not move with the batch
+// size, or a later, larger batch would find its tickets where an earlier call wrote partials.
+static DecodeLayout decode_layout(int B, int Hkv, int max_seq_len, int min_tokens, size_t ticket_slots) {
     DecodeLayout L;
     auto up = [](size_t x) { return (x + 255) / 256 * 256; };
     // a (sequence, head) of n stages overlaps at most n / (min stages per CTA) + 2 CTA ranges
     L.max_parts = (max_seq_len + min_tokens - 1) / min_tokens + 2;
     size_t bg = (size_t)B * Hkv;
     L.tickets = 256;
-    L.part_m = L.tickets + up(bg * sizeof(int));
+    L.part_m = L.tickets + up(ticket_slots * sizeof(int));
     L.part_l = L.part_m + up(bg * L.max_parts * DEC_G * sizeof(float));
     L.part_o = L.part_l + up(bg * L.max_parts * DEC_G * sizeof(float));
     L.total = L.part_o + up(bg * L.max_parts * DEC_G * DEC_D * sizeof(float));
     return L;
 }
+
+// caller-owned scratch: room for the tickets of the largest batch a launch accepts, whatever B this call has
+static size_t regular_ticket_slots(int Hkv) { return (size_t)DEC_MAX_SEQS * Hkv; }
 
 static int pick_min_tokens(int chunk_tokens) {
     const int t = chunk_tokens > 0 ? chunk_tokens : DEC_DEFAULT_MIN_TOKENS;
@@ -643,14 +649,14 @@ extern "C" size_t bn_attn_decode_workspace_bytes(int B, int Hq, int Hkv, int D, 
     (void)Hq;
     if (B <= 0 || Hkv <= 0 || D != DEC_D || max_seq_len < 0) return 0;
     if (chunk_tokens < 0 || chunk_tokens % 128) return 0;
-    return decode_layout(B, Hkv, max_seq_len, pick_min_tokens(chunk_tokens)).total;
+    return decode_layout(B, Hkv, max_seq_len, pick_min_tokens(chunk_tokens), regular_ticket_slots(Hkv)).total;
 }
 
 static int decode_launch(const void* q, const void* pool, int64_t pool_pages, const int32_t* page_table,
                          int max_pages, const int32_t* seq_lens, const int32_t* q_positions, void* out,
                          float* out_f32, float* lse, int B, int Hq, int Hkv, int D, float scale, float theta,
                          int rope_q, int max_seq_len, int chunk_tokens, void* workspace, size_t workspace_bytes,
-                         bn_stream_t stream) {
+                         size_t ticket_slots, bn_stream_t stream) {
     if (!q || !pool || !page_table || !seq_lens) return fail(BN_ERR_INVALID_ARG, "bn_attn_decode_paged: null pointer");
     if (!out && !out_f32) return fail(BN_ERR_INVALID_ARG, "bn_attn_decode_paged: no output buffer");
     if (B < 0 || Hq <= 0 || Hkv <= 0 || max_pages < 0 || max_seq_len < 0 || pool_pages <= 0)
@@ -678,7 +684,7 @@ static int decode_launch(const void* q, const void* pool, int64_t pool_pages, co
     if (int rc = require_sm100()) return rc;
     if (B == 0) return BN_OK;
     const int min_tokens = pick_min_tokens(chunk_tokens);
-    const DecodeLayout L = decode_layout(B, Hkv, max_seq_len, min_tokens);
+    const DecodeLayout L = decode_layout(B, Hkv, max_seq_len, min_tokens, ticket_slots ? ticket_slots : regular_ticket_slots(Hkv));
     if (!workspace || workspace_bytes < L.total)
         return fail(BN_ERR_WORKSPACE, "bn_attn_decode_paged: workspace of %zu bytes given, %zu needed", workspace_bytes,
                     L.total);
@@ -753,7 +759,7 @@ extern "C" int bn_attn_decode_paged(const void* q, const void* pool, int64_t poo
                                     float theta, int rope_q, int max_seq_len, int chunk_tokens, void* workspace,
                                     size_t workspace_bytes, bn_stream_t stream) {
     return decode_launch(q, pool, pool_pages, page_table, max_pages, seq_lens, q_positions, out, out_f32, lse, B, Hq,
-                         Hkv, D, scale, theta, rope_q, max_seq_len, chunk_tokens, workspace, workspace_bytes, stream);
+                         Hkv, D, scale, theta, rope_q, max_seq_len, chunk_tokens, workspace, workspace_bytes, 0, stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -763,11 +769,35 @@ extern "C" int bn_attn_decode_paged(const void* q, const void* pool, int64_t poo
 // library's device image: every GPU that loads the library holds these bytes until the process exits.
 constexpr int DEC_STATIC_MAX_BG = 256;        // sequences x KV heads
 constexpr int DEC_STATIC_MAX_SEQ_LEN = 4096;  // tokens per sequence
+constexpr size_t DEC_STATIC_HEAD_BYTES = 256 + DEC_STATIC_MAX_BG * sizeof(int);   // header + tickets: the part that must start at zero
 constexpr size_t DEC_STATIC_BYTES =
-    256 + 1024 +                                                             // header + tickets
+    DEC_STATIC_HEAD_BYTES +
     2 * (size_t)DEC_STATIC_MAX_BG * (DEC_STATIC_MAX_SEQ_LEN / DEC_DEFAULT_MIN_TOKENS + 2) * DEC_G * sizeof(float) +
     (size_t)DEC_STATIC_MAX_BG * (DEC_STATIC_MAX_SEQ_LEN / DEC_DEFAULT_MIN_TOKENS + 2) * DEC_G * DEC_D * sizeof(float);
 static __device__ __align__(256) unsigned char g_decode_static_scratch[DEC_STATIC_BYTES];
+
+// Device address of the built-in scratch on the current device.  The array's name is only a host-side handle, so
+// the runtime is asked for the address, once per device and with that device current; that first time the header
+// and the tickets are cleared on `stream`.
+static int static_scratch(const char* who, bn_stream_t stream, void** out) {
+    constexpr int kMaxDevices = 64;
+    static void* s_scratch[kMaxDevices] = {};
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+        return fail(BN_ERR_CUDA, "%s: cudaGetDevice: %s", who, cudaGetErrorString(e));
+    void* scratch = s_scratch[dev];
+    if (!scratch) {
+        e = cudaGetSymbolAddress(&scratch, g_decode_static_scratch);
+        if (e != cudaSuccess || !scratch)
+            return fail(BN_ERR_CUDA, "%s: cudaGetSymbolAddress: %s", who, cudaGetErrorString(e));
+        e = cudaMemsetAsync(scratch, 0, DEC_STATIC_HEAD_BYTES, as_stream(stream));
+        if (e != cudaSuccess) return fail(BN_ERR_CUDA, "%s: cudaMemsetAsync: %s", who, cudaGetErrorString(e));
+        s_scratch[dev] = scratch;
+    }
+    *out = scratch;
+    return BN_OK;
+}
 
 extern "C" int bn_attn_decode_paged_static(const void* q, const void* pool, int64_t pool_pages,
                                            const int32_t* page_table, int max_pages, const int32_t* seq_lens,
@@ -783,26 +813,30 @@ extern "C" int bn_attn_decode_paged_static(const void* q, const void* pool, int6
                     "max_seq_len <= %d); use bn_attn_decode_paged with a caller-owned buffer",
                     (long long)B * Hkv, max_seq_len, DEC_STATIC_MAX_BG, DEC_STATIC_MAX_SEQ_LEN);
     if (int rc = require_sm100()) return rc;
-    // Per device, once: the array's name is only a host-side handle, so ask the runtime for the device address
-    // (with that device current) and clear the words that must start at zero.
-    constexpr int kMaxDevices = 64;
-    static void* s_scratch[kMaxDevices] = {};
-    int dev = -1;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices)
-        return fail(BN_ERR_CUDA, "bn_attn_decode_paged_static: cudaGetDevice: %s", cudaGetErrorString(e));
-    void* scratch = s_scratch[dev];
-    if (!scratch) {
-        e = cudaGetSymbolAddress(&scratch, g_decode_static_scratch);
-        if (e != cudaSuccess || !scratch)
-            return fail(BN_ERR_CUDA, "bn_attn_decode_paged_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
-        e = cudaMemsetAsync(scratch, 0, 256 + 1024, as_stream(stream));
-        if (e != cudaSuccess)
-            return fail(BN_ERR_CUDA, "bn_attn_decode_paged_static: cudaMemsetAsync: %s", cudaGetErrorString(e));
-        s_scratch[dev] = scratch;
-    }
+    void* scratch = nullptr;
+    if (int rc = static_scratch("bn_attn_decode_paged_static", stream, &scratch)) return rc;
+    // The ticket region always has DEC_STATIC_MAX_BG slots, so the partials start at the same byte for every
+    // batch size and a call can never find an earlier call's partials where it expects zeroed tickets.
     return decode_launch(q, pool, pool_pages, page_table, max_pages, seq_lens, q_positions, out, out_f32, lse, B, Hq,
-                         Hkv, D, scale, theta, rope_q, max_seq_len, 0, scratch, DEC_STATIC_BYTES, stream);
+                         Hkv, D, scale, theta, rope_q, max_seq_len, 0, scratch, DEC_STATIC_BYTES, DEC_STATIC_MAX_BG,
+                         stream);
+}
+
+extern "C" int bn_attn_decode_paged_static_status(bn_stream_t stream) {
+    if (int rc = require_sm100()) return rc;
+    void* scratch = nullptr;
+    if (int rc = static_scratch("bn_attn_decode_paged_static_status", stream, &scratch)) return rc;
+    int word = 0;
+    cudaError_t e = cudaMemcpyAsync(&word, scratch, sizeof(word), cudaMemcpyDeviceToHost, as_stream(stream));
+    if (e == cudaSuccess) e = cudaStreamSynchronize(as_stream(stream));
+    if (e != cudaSuccess) return fail(BN_ERR_CUDA, "bn_attn_decode_paged_static_status: %s", cudaGetErrorString(e));
+    if (word != BN_ERR_TIMEOUT) return BN_OK;
+    // a launch gave up half way: its tickets may be left non-zero, so header and tickets are cleared for the next call
+    e = cudaMemsetAsync(scratch, 0, DEC_STATIC_HEAD_BYTES, as_stream(stream));
+    if (e == cudaSuccess) e = cudaStreamSynchronize(as_stream(stream));
+    if (e != cudaSuccess) return fail(BN_ERR_CUDA, "bn_attn_decode_paged_static_status: %s", cudaGetErrorString(e));
+    return fail(BN_ERR_TIMEOUT, "a bounded device-side wait ran out in a bn_attn_decode_paged_static call; its result "
+                                "is invalid (the built-in scratch has been cleared for the next call)");
 }
 
 extern "C" int bn_attn_lse_combine_strided(const float* outs, int64_t outs_part_stride, const float* lses,

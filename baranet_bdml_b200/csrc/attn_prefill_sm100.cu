@@ -396,40 +396,49 @@ prefill_kernel_v1(const __grid_constant__ CUtensorMap tmap_k, const __grid_const
 
 
 // ---------------------------------------------------------------------------
-// launch 2, main kernel: persistent, one CTA per SM, TWO query tiles in flight
+// launch 2, main kernel: persistent, one CTA per SM, TWO query tiles in flight,
+// THREE score buffers in tensor memory
 // ---------------------------------------------------------------------------
 // Work unit = (batch, query head, pair of 128-row query tiles); units are ordered
 // heaviest first and dealt in snake order to the CTAs (grid = number of SMs), each
-// CTA walking its units in a loop so that the next unit's Q/K/V loads overlap the
-// current unit's tail.  Eighteen warps:
+// CTA walking its units in a loop.  Eighteen warps:
 //   warps 0-7   softmax of query tile 2t   (warps 0-3 keys 0..63 of a step, 4-7 keys 64..127)
 //   warps 8-15  softmax of query tile 2t+1 (same split)
 //   warp 16     MMA issuer                  warp 17  TMA producer
 // Two threads per query row: thread = (TMEM lane = row, half of the step's 128
-// keys, half of the 64 output columns).  Four softmax warps per scheduler hide
-// the latencies of TMEM loads, barrier waits and exponentials; the two threads
-// of a row share the exponent reference, their per-step exchange is one named
-// barrier (64 threads) that ORs an "out of range" flag.
-// Both tiles read the same K/V stages, so each K/V tile is fetched once per
-// 256 query rows, and the tensor pipe works on one tile (next Q K^T, then P V)
-// while the other tile's softmax runs.  Q tiles arrive by TMA (double buffered
-// across units) and are rotated in place, a row per warp instruction (lane =
-// rotation pair), one unit AHEAD: right after a tile's last step and before its
-// epilogue, so the MMA warp can start the next unit while O is written out.
-// TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,320) O1 [320,384)
-//                     P0 [384,448) P1 [448,512)
+// keys, half of the 64 output columns).
+//
+// The steps (query tile u, key tile j) of a CTA form ONE sequence s = 0, 1, 2, ...
+// (within a unit: j ascending, tile 0 before tile 1; units one after the other).
+// Step s computes its scores into buffer s % 3, and the bf16 probabilities are
+// written over the scores they came from (thread (row, half) reads 16 fp32 columns
+// ahead of the 8 packed columns it overwrites), so a step owns one 128-column
+// buffer from its Q K^T to the end of its P V:
+//   TMEM (512 columns): S/P buffers [0,128) [128,256) [256,384) | O0 [384,448) O1 [448,512)
+//   P of keys 0..63 at columns [0,32) of the buffer, keys 64..127 at [64,96).
+// The MMA warp issues  Q K^T(s+3)  right after  P V(s): the tensor pipe executes
+// in issue order, so the new scores cannot overtake the read of the old
+// probabilities, and no softmax warp ever waits for the Q K^T of its NEXT step,
+// which was issued a whole step earlier.  With the exponent reference fixed
+// (below) the steps of a tile need nothing from each other but the order of their
+// P V, so the two groups of softmax warps run back to back on scores that are
+// already there, and the exponential unit (16 per clock per SM: 1024 cycles for a
+// 128x128 step against 512 tensor cycles at head_dim 64) is the pipe that bounds
+// the kernel.
+// Both tiles read the same K/V stages, so each K/V tile is fetched once per 256
+// query rows.  Q tiles arrive by TMA (double buffered across units) and are rotated
+// in place, a row per warp instruction (lane = rotation pair), one unit AHEAD:
+// right after a tile's last step and before its epilogue.
 // Softmax is ONE pass per step with an exponent reference that starts at 0 and
 // moves only when a probability would leave [2^-64, 2^64] (bf16 and fp32 keep
-// their relative precision over that range): then the two warps of the rows
-// take the true row maximum, rescale O and l and redo the step.
-// What bounds it (measured): with the exponential replaced by an FMA the kernel
-// still takes 87 % of its time, so the chain  S ready -> TMEM loads -> P stored ->
-// MMA warp wakes -> next Q K^T issued, executed, committed  (about 850 cycles of
-// it pure hand-off latency per step and tile), not MUFU or the tensor pipe, is
-// the limit; TMEM has no room for a second S buffer per tile at 128-key steps.
-// Measured and dropped: exponentials on the FMA pipe; 64-key steps with double-
-// buffered S; one MMA warp per tile; pairing two heads on the same query rows;
-// an extra warp for the Q rotation; issuing P V before the next Q K^T.
+// their relative precision over that range).  That case is decided per tile and
+// step (one 256-thread named barrier that ORs the flag); the tile then asks the
+// MMA warp to compute the step's scores again (the first pass has overwritten
+// part of them), takes the true row maxima, rescales O and l and redoes the step.
+// Named barriers are not bounded waits; they cannot hang because a warp that
+// gives up (a bounded mbarrier wait ran out, or the CTA-wide abort flag was seen)
+// arrives once on every named barrier it belongs to before it leaves, and every
+// warp checks the abort flag after each named barrier.
 // Optional event log for performance work (compiled out unless built with -DBN_TIMELINE): the warps of CTA 0
 // append (clock64, code) pairs to the caller's lse buffer, 2048 entries per warp, INSTEAD of the log-sum-exp.
 #ifdef BN_TIMELINE
@@ -437,15 +446,25 @@ prefill_kernel_v1(const __grid_constant__ CUtensorMap tmap_k, const __grid_const
 #else
 #define BN_LOG(code) do {} while (0)
 #endif
+#ifdef BN_TIMELINE_MMA
+#define BN_LOG_MMA(code) BN_LOG(code)
+#else
+#define BN_LOG_MMA(code) do {} while (0)
+#endif
+#ifndef BN_MMA_LEADER
+#define BN_MMA_LEADER elect_one()
+#endif
 constexpr int P2_THREADS = 576;
 constexpr int P2_NSTAGE = 4;
+constexpr int P2_NSBUF = 3;                  // score / probability buffers in tensor memory
 constexpr int P2_SMEM_BYTES = 1024 + PF_TILE_BYTES * (4 + 2 * P2_NSTAGE);
 constexpr uint32_t P2_TMEM_COLS = 512;
+constexpr uint32_t P2_COL_O = 384;
 
 // exp2 of 16 scores -> 8 packed bf16x2; the row sum is accumulated in two independent chains.  The arithmetic is
 // plain scalar FFMA / FADD: the packed two-wide forms (fma.rn.f32x2, add.rn.f32x2) were measured slower here.
 // The scale, the shift and the two sums travel as register pairs (scale2, mneg2 = the value twice; sum2): in this
-// form ptxas keeps the kernel inside its 96 registers without spilling, which is worth 4 % of the run time.
+// form ptxas keeps the kernel inside its 96 registers without spilling.
 template <bool MASK>
 __device__ __forceinline__ void softmax_chunk16(uint32_t (&r)[16], uint32_t (&pk)[8], uint64_t scale2, uint64_t mneg2,
                                                 int first_key, int row_last, uint64_t& sum2) {
@@ -508,6 +527,30 @@ __device__ __forceinline__ int unit_of(int round, int n_units) {
     return k < n_units ? k : -1;
 }
 
+// Rare paths of the MMA thread.
+// Key tiles of the two query tiles of the unit of round `it`, packed n0 | n1 << 16; -1 when the CTA has no such unit.
+__device__ __forceinline__ int mma_unit_tiles(const PrefillParams& p, int n_units, int it) {
+    const int k = unit_of(it, n_units);
+    if (k < 0) return -1;
+    const UnitInfo w = unit_info(p, k);
+    return w.n_t[0] | w.n_t[1] << 16;
+}
+
+__device__ __forceinline__ bool mma_wait_operands(uint32_t bar_q, uint32_t par_q, uint32_t bar_kv, uint32_t par_kv,
+                                               volatile int* abort_flag) {
+    if (bar_q && !mbar_wait(bar_q, par_q, abort_flag)) return false;
+    return mbar_wait(bar_kv, par_kv, abort_flag);
+}
+
+__device__ __forceinline__ bool mma_scores_again(uint32_t tS, uint32_t qd, uint32_t kd, uint32_t desc_hi, uint32_t idesc,
+                                              uint32_t bar_again, uint32_t bar_redone, uint32_t par, volatile int* abort_flag) {
+    tc::fence_after_sync();
+#pragma unroll
+    for (int kk = 0; kk < PF_D / 16; ++kk) tc::mma_ss_lohi(tS, qd + kk * 2, kd + kk * 2, desc_hi, idesc, kk > 0);
+    tc::commit(bar_again);
+    return mbar_wait(bar_redone, par, abort_flag);
+}
+
 // 18 warps = 5 on one scheduler: 16384 / (5 * 32) leaves 96 registers per thread
 __global__ void __launch_bounds__(P2_THREADS, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -515,10 +558,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     extern __shared__ uint8_t smem_raw[];
     // Q tile barriers are indexed [buffer][tile]
     __shared__ __align__(8) uint64_t bar_qfull[2][2], bar_qrot[2][2], bar_qfree[2][2];
-    __shared__ __align__(8) uint64_t bar_s[2], bar_p[2], bar_o[2], bar_pv[2];
-    __shared__ __align__(8) uint64_t bar_kfull[P2_NSTAGE], bar_vfull[P2_NSTAGE], bar_empty[P2_NSTAGE];
+    __shared__ __align__(8) uint64_t bar_s[P2_NSBUF], bar_p[P2_NSBUF];      // per score buffer
+    __shared__ __align__(8) uint64_t bar_o[2], bar_rs[2], bar_rp[2];        // per tile: O complete; scores again / redone
+    __shared__ __align__(8) uint64_t bar_kvfull[P2_NSTAGE], bar_empty[P2_NSTAGE];   // K and V of a stage arrive on one barrier
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
+    __shared__ int s_redo[2];
+                  // per tile: how many steps have asked for their scores again
     __shared__ float s_xchg[2][2][PF_BM];      // [tile][column half][row]: exchange between the two threads of a row
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
@@ -537,14 +583,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 mbar_init(smem_u32(&bar_qrot[i][u]), 8);
                 mbar_init(smem_u32(&bar_qfree[i][u]), 1);
             }
-            mbar_init(smem_u32(&bar_s[i]), 1);
-            mbar_init(smem_u32(&bar_p[i]), 8);
             mbar_init(smem_u32(&bar_o[i]), 1);
-            mbar_init(smem_u32(&bar_pv[i]), 1);
+            mbar_init(smem_u32(&bar_rs[i]), 1);
+            mbar_init(smem_u32(&bar_rp[i]), 8);
+            s_redo[i] = 0;
+        }
+        for (int s = 0; s < P2_NSBUF; ++s) {
+            mbar_init(smem_u32(&bar_s[s]), 1);
+            mbar_init(smem_u32(&bar_p[s]), 8);
         }
         for (int s = 0; s < P2_NSTAGE; ++s) {
-            mbar_init(smem_u32(&bar_kfull[s]), 1);
-            mbar_init(smem_u32(&bar_vfull[s]), 1);
+            mbar_init(smem_u32(&bar_kvfull[s]), 1);
             mbar_init(smem_u32(&bar_empty[s]), 1);
         }
         s_abort = 0;
@@ -573,8 +622,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 const int k = unit_of(it, n_units);
                 if (k < 0) break;
                 const UnitInfo w = unit_info(p, k);
-                for (int u = 0; u < 2 && ok; ++u) {
-                    if (w.n_t[u] == 0) continue;
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    if (!ok || w.n_t[u] == 0) continue;
                     const int buf = q_use[u] & 1;
                     const uint32_t par = (q_use[u] >> 1) & 1;
                     ++q_use[u];
@@ -587,121 +637,171 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 for (int j = 0; ok && j < w.n_max; ++j) {
                     ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &s_abort);
                     if (!ok) break;
-                    mbar_arrive_expect_tx(smem_u32(&bar_kfull[stage]), PF_TILE_BYTES);
-                    tma_load_4d(sK + stage * PF_TILE_BYTES, &tmap_k, 0, w.g, j * PF_BN, w.b, smem_u32(&bar_kfull[stage]));
-                    mbar_arrive_expect_tx(smem_u32(&bar_vfull[stage]), PF_TILE_BYTES);
-                    tma_load_4d(sV + stage * PF_TILE_BYTES, &tmap_v, 0, w.g, j * PF_BN, w.b, smem_u32(&bar_vfull[stage]));
+                    mbar_arrive_expect_tx(smem_u32(&bar_kvfull[stage]), 2 * PF_TILE_BYTES);
+                    tma_load_4d(sK + stage * PF_TILE_BYTES, &tmap_k, 0, w.g, j * PF_BN, w.b, smem_u32(&bar_kvfull[stage]));
+                    tma_load_4d(sV + stage * PF_TILE_BYTES, &tmap_v, 0, w.g, j * PF_BN, w.b, smem_u32(&bar_kvfull[stage]));
                     if (++stage == P2_NSTAGE) { stage = 0; phase ^= 1u; }
                 }
             }
         }
     } else if (warp == 16) {
         // ------------------------------------------------------------ MMA issuer
-        constexpr uint32_t IDESC_QK = tc::idesc_bf16(PF_BM, PF_BN, 0);
-        constexpr uint32_t IDESC_PV = tc::idesc_bf16(PF_BM, PF_D, 1);
-        // a shared-memory descriptor is this constant plus the tile's address in units of 16 bytes (bits 0-13)
-        const uint64_t dZero = tc::smem_desc_sw128(0);
-        int stage = 0;
-        uint32_t phase = 0;
-        int q_use[2] = {0, 0};
-        uint32_t tiles_done[2] = {0, 0};    // tiles of slot u completed so far (parity of bar_s / bar_p)
-        uint32_t units_done[2] = {0, 0};
-        bool ok = true;
-        for (int it = 0; ok; ++it) {
-            const int k = unit_of(it, n_units);
-            if (k < 0) break;
-            const UnitInfo w = unit_info(p, k);
-            uint32_t qaddr[2] = {0, 0};
-            for (int u = 0; u < 2 && ok; ++u) {
-                if (w.n_t[u] == 0) continue;
-                const int buf = q_use[u] & 1;
-                const uint32_t par = (q_use[u] >> 1) & 1;
-                ++q_use[u];
-                qaddr[u] = sQ + (buf * 2 + u) * PF_TILE_BYTES;
-                ok = mbar_wait(smem_u32(&bar_qrot[buf][u]), par, &s_abort);
-            }
-            if (!ok) break;
-            // S_u = Q_u K(j)^T; the last one of the unit also frees the Q buffer
-            auto issue_qk = [&](int u, int st, int j) {
-                if (elect_one()) {
-                    tc::fence_after_sync();
-#pragma unroll
-                    for (int kk = 0; kk < PF_D / 16; ++kk)
-                        tc::mma_ss(tmem + u * 128, dZero + (uint64_t)((qaddr[u] >> 4) + kk * 2),
-                                   dZero + (uint64_t)(((sK + st * PF_TILE_BYTES) >> 4) + kk * 2), IDESC_QK, kk > 0);
-                    tc::commit(smem_u32(&bar_s[u]));
-                    if (j == w.n_t[u] - 1) tc::commit(smem_u32(&bar_qfree[(q_use[u] - 1) & 1][u]));
-                }
-                __syncwarp();
+        // ONE thread runs this loop, and its own instruction stream is the critical resource: it shares a scheduler
+        // with four busy softmax warps.  So the steady-state path is kept short and straight: one generator (for
+        // the Q K^T side) whose steps travel to the P V side through a three-entry queue of packed words; K and V
+        // of a stage behind one barrier, looked at once per stage; everything rare (a new unit, a wait that does
+        // not succeed at once, scores wanted again) out of line.
+        if (BN_MMA_LEADER) {
+            constexpr uint32_t IDESC_QK = tc::idesc_bf16(PF_BM, PF_BN, 0);
+            constexpr uint32_t IDESC_PV = tc::idesc_bf16(PF_BM, PF_D, 1);
+            // a shared-memory descriptor is (DESC_HI : DESC_LO + the tile's address in units of 16 bytes)
+            constexpr uint32_t DESC_LO = (uint32_t)(tc::smem_desc_sw128(0) & 0xffffffffu);
+            constexpr uint32_t DESC_HI = (uint32_t)(tc::smem_desc_sw128(0) >> 32);
+            const uint32_t dQ = DESC_LO + (sQ >> 4), dK = DESC_LO + (sK >> 4), dV = DESC_LO + (sV >> 4);
+            constexpr uint32_t TILE16 = PF_TILE_BYTES >> 4;
+            const uint32_t aBarS = smem_u32(&bar_s[0]), aBarP = smem_u32(&bar_p[0]);
+            const uint32_t aFull = smem_u32(&bar_kvfull[0]), aEmpty = smem_u32(&bar_empty[0]);
+            const uint32_t aQrot = smem_u32(&bar_qrot[0][0]), aQfree = smem_u32(&bar_qfree[0][0]);   // [buffer][tile]
+
+            // generator state: the step whose Q K^T is issued next
+            int g_it = 0, g_n0 = 0, g_n1 = 0, g_nmax = 0, g_j = 0;   // round; key tiles of the unit's two query tiles; key tile
+            uint32_t g_u = 0;                   // query tile of the pair
+            uint32_t g_kt = 0;                  // ring position of the step's key tile (all earlier key tiles of the CTA)
+            uint32_t g_quse0 = 0, g_quse1 = 0;  // earlier units in which tile 0 / 1 existed (-> Q buffer, barrier parity)
+            bool g_valid;
+            auto gen_unit = [&]() {
+                const int t = mma_unit_tiles(p, n_units, g_it);
+                g_valid = t >= 0;
+                g_n0 = t & 0xffff;
+                g_n1 = t >> 16;
+                g_nmax = max(g_n0, g_n1);
+                g_j = 0;
+                g_u = g_n0 > 0 ? 0u : 1u;
             };
-            if (w.n_max > 0) ok = mbar_wait(smem_u32(&bar_kfull[stage]), phase, &s_abort);
-            if (!ok) break;
-            if (elect_one()) BN_LOG(20);
-            if (w.n_t[0] > 0) issue_qk(0, stage, 0);
-            if (w.n_t[1] > 0) issue_qk(1, stage, 0);
-            if (elect_one()) BN_LOG(21);
-            for (int j = 0; ok && j < w.n_max; ++j) {
-                const int nstage = (stage + 1 == P2_NSTAGE) ? 0 : stage + 1;
-                const uint32_t nphase = (stage + 1 == P2_NSTAGE) ? phase ^ 1u : phase;
-                bool next_k_ready = false;
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    if (j >= w.n_t[u]) continue;
-                    ok = mbar_wait(smem_u32(&bar_p[u]), (tiles_done[u] + j) & 1, &s_abort);
-                    if (!ok) break;
-                    if (elect_one()) BN_LOG(24 | u << 8 | j << 16);
-                    // S_u(j+1) = Q_u K(j+1)^T first: its S columns are free because P_u(j) has been written, and
-                    // the softmax of tile j+1 can start while P_u(j) V(j) still runs
-                    if (j + 1 < w.n_t[u]) {
-                        if (!next_k_ready) {
-                            ok = mbar_wait(smem_u32(&bar_kfull[nstage]), nphase, &s_abort);
+            gen_unit();
+            // queue entry: bit 0 tile, 1 accumulate (j > 0), 2 last step of the tile in its unit, 3 last user of the
+            // K/V stage, 4-5 stage, 6 Q buffer
+            uint32_t q0 = 0, q1 = 0, q2 = 0;
+            int qlen = 0;
+            uint32_t bq = 0, bp = 0, par_p = 0;       // score buffers of the next Q K^T / P V; parity of bar_p[bp]
+            int redo0 = 0, redo1 = 0;
+            uint32_t spins = 0;
+            bool ok = true;
+
+            for (;;) {
+                // ---- Q K^T, up to three steps ahead of the P V.  Only the step the P V needs next is worth blocking
+                // for; for the others a missing operand (the next unit's Q still being rotated) means "look again soon".
+                bool pending = false;
+                while (g_valid && qlen < P2_NSBUF) {
+                    const uint32_t quse = g_u ? g_quse1 : g_quse0;
+                    const uint32_t qslot = (quse & 1u) * 2 + g_u;         // [buffer][tile]
+                    const uint32_t stage = g_kt & (P2_NSTAGE - 1);
+                    if (g_j == 0 || g_u == 0 || g_j >= g_n0) {
+                        // first step of a tile in its unit: is Q rotated?  first user of a K/V stage: has it landed?
+                        bool ready = true;
+                        if (g_j == 0) ready = mbar_test_wait(aQrot + qslot * 8, (quse >> 1) & 1u);
+                        if (ready && (g_u == 0 || g_j >= g_n0)) ready = mbar_test_wait(aFull + stage * 8, (g_kt >> 2) & 1u);
+                        if (!ready) {
+                            if (qlen > 0) { pending = true; break; }
+                            // nothing in flight: this step is the one everybody waits for
+                            ok = mma_wait_operands(g_j == 0 ? aQrot + qslot * 8 : 0u, (quse >> 1) & 1u, aFull + stage * 8,
+                                                   (g_kt >> 2) & 1u, &s_abort);
                             if (!ok) break;
-                            next_k_ready = true;
                         }
-                        issue_qk(u, nstage, j + 1);
                     }
-                    // O_u += P_u(j) V(j)
-                    ok = mbar_wait(smem_u32(&bar_vfull[stage]), phase, &s_abort);
-                    if (!ok) break;
-                    if (elect_one()) {
-                        tc::fence_after_sync();
+                    tc::fence_after_sync();
+                    {
+                        const uint32_t qd = dQ + qslot * TILE16, kd = dK + stage * TILE16;
 #pragma unroll
-                        for (int kk = 0; kk < PF_BN / 16; ++kk)
-                            tc::mma_ts(tmem + 256 + u * 64, tmem + 384 + u * 64 + kk * 8,
-                                       dZero + (uint64_t)(((sV + stage * PF_TILE_BYTES) >> 4) + kk * 128), IDESC_PV,
-                                       (j > 0) || (kk > 0));
-                        tc::commit(smem_u32(&bar_pv[u]));                          // P_u(j) may be overwritten
-                        if (j == w.n_t[u] - 1) tc::commit(smem_u32(&bar_o[u]));
-                        const bool last_user = (u == 1) || (j >= w.n_t[1]);
-                        if (last_user) tc::commit(smem_u32(&bar_empty[stage]));   // K(j)/V(j) may be overwritten
-                        BN_LOG(25 | u << 8 | j << 16);
+                        for (int kk = 0; kk < PF_D / 16; ++kk)
+                            tc::mma_ss_lohi(tmem + bq * 128, qd + kk * 2, kd + kk * 2, DESC_HI, IDESC_QK, kk > 0);
                     }
-                    __syncwarp();
+                    tc::commit(aBarS + bq * 8);
+                    BN_LOG_MMA(20 | g_u << 8 | g_j << 16);
+                    uint32_t e = g_u | stage << 4 | (quse & 1u) << 6;
+                    if (g_j > 0) e |= 2u;
+                    if (g_j == (g_u ? g_n1 : g_n0) - 1) e |= 4u;
+                    if (g_u == 1 || g_j >= g_n1) e |= 8u;
+                    if (qlen == 0) q0 = e; else if (qlen == 1) q1 = e; else q2 = e;
+                    ++qlen;
+                    bq = (bq == P2_NSBUF - 1) ? 0 : bq + 1;
+                    // next step: j ascending, tile 0 before tile 1, skipping steps a tile does not have
+                    if (g_u == 0 && g_j < g_n1) g_u = 1;
+                    else {
+                        ++g_j;
+                        ++g_kt;
+                        g_u = g_j < g_n0 ? 0u : 1u;
+                        if (g_j >= g_nmax) {
+                            g_quse0 += g_n0 > 0;
+                            g_quse1 += g_n1 > 0;
+                            ++g_it;
+                            gen_unit();
+                        }
+                    }
                 }
-                stage = nstage;
-                phase = nphase;
+                if (!ok || qlen == 0) break;
+
+                // ---- P of the oldest step in flight, written by the eight softmax warps of its tile
+                if (!mbar_try_wait(aBarP + bp * 8, par_p)) {
+                    if (!pending) {
+                        ok = mbar_wait(aBarP + bp * 8, par_p, &s_abort);
+                        if (!ok) break;
+                    } else {
+                        // a Q K^T is waiting for an operand: look again at that operand (bounded, about 2 s)
+                        if (++spins > (1u << 24) || s_abort) { s_abort = 1; break; }
+                        continue;
+                    }
+                }
+                spins = 0;
+                const uint32_t e = q0;
+                q0 = q1; q1 = q2;
+                --qlen;
+                const uint32_t u = e & 1u, stage = (e >> 4) & 3u;
+                // read now, tested after the address arithmetic below: the load takes its time
+                const int redo_now = *reinterpret_cast<volatile int*>(&s_redo[u]);
+                const uint32_t tP = tmem + bp * 128, tOu = tmem + P2_COL_O + u * 64, vd = dV + stage * TILE16;
+                const uint32_t qslot = ((e >> 6) & 1u) * 2 + u;
+                const int seen = u ? redo1 : redo0;
+                if (redo_now != seen) {
+                    // the tile wants the scores of this step again (its first pass has overwritten part of them):
+                    // K(j) and Q are still in place, they are released by the commits that follow the P V
+                    if (u) ++redo1; else ++redo0;
+                    ok = mma_scores_again(tmem + bp * 128, dQ + qslot * TILE16, dK + stage * TILE16, DESC_HI, IDESC_QK,
+                                          smem_u32(&bar_rs[u]), smem_u32(&bar_rp[u]), seen & 1, &s_abort);
+                    if (!ok) break;
+                }
+                // O_u += P V(j)
+                tc::fence_after_sync();
+                tc::mma_ts_lohi(tOu, tP, vd, DESC_HI, IDESC_PV, (e >> 1) & 1u);
+#pragma unroll
+                for (int kk = 1; kk < PF_BN / 16; ++kk)
+                    tc::mma_ts_lohi(tOu, tP + (kk & 3) * 8 + (kk >> 2) * 64, vd + kk * 128, DESC_HI, IDESC_PV, 1u);
+                if (e & 4u) {
+                    tc::commit(smem_u32(&bar_o[u]));          // O of this unit is complete
+                    tc::commit(aQfree + qslot * 8);           // and its Q tile is done with
+                }
+                if (e & 8u) tc::commit(aEmpty + stage * 8);   // K(j)/V(j) may be overwritten
+                BN_LOG_MMA(25 | u << 8);
+                if (bp == P2_NSBUF - 1) { bp = 0; par_p ^= 1u; }
+                else ++bp;
             }
-            tiles_done[0] += w.n_t[0];
-            tiles_done[1] += w.n_t[1];
-            units_done[0] += w.n_t[0] > 0;
-            units_done[1] += w.n_t[1] > 0;
         }
+        __syncwarp();
     } else {
         // ------------------------------------------ softmax groups (warps 0..15)
         // Eight warps per query tile: TWO threads per query row, each owning 64 of a step's 128 keys (and 32 of the
-        // 64 output columns).  Four softmax warps per scheduler instead of two hide the latencies of TMEM loads,
-        // barrier waits and the exponential's result.  The two threads of a row share the exponent reference;
-        // their only per-step exchange is one named barrier that ORs the "probability left the safe range" flag.
+        // 64 output columns).  The two threads of a row share the exponent reference.
         const int u = warp / 8;                     // which query tile of the pair
         const int hf = (warp / 4) % 2;              // which half of the keys of a step (and of the O columns)
         const int row = (warp % 4) * 32 + lane;     // TMEM lane = query row inside the tile
         const int pair_bar = 1 + u * 4 + (warp % 4);   // named barrier of the two warps that share these 32 rows
+        const int tile_bar = 9 + u;                    // named barrier of the tile's eight warps
         const uint32_t lane_base = ((uint32_t)((warp % 4) * 32)) << 16;
-        const uint32_t tS = tmem + lane_base + u * 128 + hf * 64;
-        const uint32_t tO = tmem + lane_base + 256 + u * 64 + hf * 32;
-        const uint32_t tP = tmem + lane_base + 384 + u * 64 + hf * 32;
+        const uint32_t tO = tmem + lane_base + P2_COL_O + u * 64 + hf * 32;
         int q_use = 0;
-        uint32_t tiles_done = 0, units_done = 0;
+        int sbase = 0;                              // steps of all earlier units (both tiles)
+        int redo_n = 0;
+        uint32_t units_done = 0;
         bool ok = true;
         // the next unit (from round `from` on) in which this group's query tile exists; it < 0: none
         auto find_unit = [&](int from, int& it, UnitInfo& w) {
@@ -709,7 +809,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 const int k = unit_of(it, n_units);
                 if (k < 0) { it = -1; return; }
                 w = unit_info(p, k);
-                if (w.n_t[u] > 0) return;
+                if ((u ? w.n_t[1] : w.n_t[0]) > 0) return;
+                sbase += w.n_t[0] + w.n_t[1];
             }
         };
         // RoPE on the TMA-loaded Q tile, in place (128-byte-swizzled, K-major).  Each of the tile's eight warps
@@ -751,7 +852,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         find_unit(0, it, w);
         if (it >= 0) ok = rotate_q(w);
         while (ok && it >= 0) {
-            const int nt = w.n_t[u];
+            const int nt = u ? w.n_t[1] : w.n_t[0];
+            const int n_both = min(w.n_t[0], w.n_t[1]);     // key tiles that both query tiles of the pair have
             const int b = w.b, h = w.h;
             const int i0 = (2 * w.qp + u) * PF_BM;
             const int gi = i0 + row;
@@ -762,15 +864,22 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             const int tile_free_last = p.causal ? min(p.S - 1, i0 + p.position_offset) : p.S - 1;   // no mask needed up to here
 
             for (int j = 0; j < nt; ++j) {
-                ok = mbar_wait(smem_u32(&bar_s[u]), (tiles_done + j) & 1, &s_abort);
+                // this step's place in the CTA's sequence, hence its score buffer
+                const uint32_t s = (uint32_t)(sbase + (j < n_both ? 2 * j + u : n_both + j));
+                const uint32_t sb = s % P2_NSBUF;
+                const uint32_t tS = tmem + lane_base + sb * 128 + hf * 64;   // 64 fp32 scores; P goes over the first 32
+                BN_LOG(1 | u << 8 | j << 16);
+                ok = mbar_wait(smem_u32(&bar_s[sb]), (s / P2_NSBUF) & 1, &s_abort);
                 if (!ok) break;
                 tc::fence_after_sync();
+                BN_LOG(2 | u << 8 | j << 16);
                 const int j0 = j * PF_BN + hf * 64;             // first key of this thread's 64 columns
                 const bool need_mask = (j0 + 63) > tile_free_last;
 
-                // one pass over this thread's 64 columns: P = exp2(S * scale_log2 - m_ref * scale_log2) -> TMEM, with
-                // the load of the next 16 columns in flight while the current 16 are processed
-                auto half_pass = [&](float mneg, bool first_store_needs_pv) {
+                // one pass over this thread's 64 columns: P = exp2(S * scale_log2 - m_ref * scale_log2), written over
+                // columns that have already been read, with the load of the next 16 columns in flight while the
+                // current 16 are processed
+                auto half_pass = [&](float mneg) {
                     uint64_t sum2 = 0;   // (0.f, 0.f)
                     const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2), mneg2 = pack_f32x2(mneg, mneg);
                     uint32_t r0[16], r1[16], pk[8];
@@ -782,38 +891,43 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                     tc::wait_ld(r0);
                     tc::ld16(tS + 16, r1);
                     chunk(r0, 0);
-                    // P(j-1) is still being read by its P V until bar_pv says otherwise
-                    bool good = true;
-                    if (first_store_needs_pv) {
-                        good = mbar_wait(smem_u32(&bar_pv[u]), (tiles_done + j - 1) & 1, &s_abort);
-                        tc::fence_after_sync();
-                    }
-                    tc::st8(tP + 0, pk);
+                    tc::st8(tS + 0, pk);
                     tc::wait_ld(r1);
                     tc::ld16(tS + 32, r0);
                     chunk(r1, 1);
-                    tc::st8(tP + 8, pk);
+                    tc::st8(tS + 8, pk);
                     tc::wait_ld(r0);
                     tc::ld16(tS + 48, r1);
                     chunk(r0, 2);
-                    tc::st8(tP + 16, pk);
+                    tc::st8(tS + 16, pk);
                     tc::wait_ld(r1);
                     chunk(r1, 3);
-                    tc::st8(tP + 24, pk);
+                    tc::st8(tS + 24, pk);
                     float s0, s1;
                     unpack_f32x2(sum2, s0, s1);
-                    return good ? s0 + s1 : NAN;
+                    return s0 + s1;
                 };
 
                 // The exponent reference starts at 0 and moves only when it has to: p = 2^(s*c - ref) may be
                 // anywhere in [2^-64, 2^64] without any loss (bf16 and fp32 keep their relative precision over
                 // that range), so for ordinary score magnitudes there is never a second pass or an O rescale.
-                float lsum = half_pass(-m_ref * p.scale_log2, tiles_done + j > 0);
-                if (s_abort) { ok = false; break; }
+                float lsum = half_pass(-m_ref * p.scale_log2);
                 const bool over = !(lsum <= 0x1p64f) || (j == 0 && hf == 0 && lsum < 0x1p-64f);
-                if (named_bar_or(pair_bar, 64, over)) {
-                    // rare, and taken by both warps of these rows together: move the reference to the true row
-                    // maximum, rescale O and l, redo the step.
+                const bool redo = named_bar_or(tile_bar, 256, over);
+                if (s_abort) { ok = false; break; }
+                if (redo) {
+                    // Rare, and taken by the whole tile together.  The first pass has overwritten scores, so the
+                    // MMA warp computes them again; its commit also tells that every earlier P V of this tile has
+                    // completed, so O may be rescaled here.
+                    tc::wait_st();
+                    tc::fence_before_sync();
+                    ++redo_n;
+                    if ((warp & 7) == 0 && lane == 0) *reinterpret_cast<volatile int*>(&s_redo[u]) = redo_n;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bar_p[sb]));
+                    ok = mbar_wait(smem_u32(&bar_rs[u]), (redo_n - 1) & 1, &s_abort);
+                    if (!ok) break;
+                    tc::fence_after_sync();
                     float hmax = -INFINITY;
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
@@ -826,6 +940,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                     }
                     s_xchg[u][hf][row] = hmax;
                     named_bar_sync(pair_bar, 64);
+                    if (s_abort) { ok = false; break; }
                     const float tmax = fmaxf(hmax, s_xchg[u][hf ^ 1][row]);
                     const float m_new = j == 0 ? tmax : fmaxf(m_ref, tmax);   // the first step may also move it down
                     const float m_upd = m_new == -INFINITY ? m_ref : m_new;
@@ -840,17 +955,25 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                         tc::st32(tO, ro);
                     }
                     m_ref = m_upd;
-                    lsum = half_pass(-m_ref * p.scale_log2, false);
+                    lsum = half_pass(-m_ref * p.scale_log2);
                     named_bar_sync(pair_bar, 64);      // the exchange slots may be written again
+                    if (s_abort) { ok = false; break; }
+                    l_run += lsum;
+                    tc::wait_st();
+                    tc::fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bar_rp[u]));
+                } else {
+                    l_run += lsum;
+                    tc::wait_st();
+                    tc::fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bar_p[sb]));
                 }
-                l_run += lsum;
-                tc::wait_st();
-                tc::fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bar_p[u]));
+                BN_LOG(6 | u << 8 | j << 16);
             }
             if (!ok) break;
-            tiles_done += nt;
+            sbase += w.n_t[0] + w.n_t[1];
 
             // The next unit's Q tile is rotated BEFORE this unit's epilogue: the MMA warp needs it to start the
             // next unit, while the epilogue has to wait for the last P V anyway.
@@ -892,11 +1015,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                         l_row > 0.f ? (m_ref * p.scale_log2 + log2f(l_row)) * PF_LN2 : -INFINITY;
 #endif
             }
+            // the partner reads this thread's exchange slot before either of them can write it again: the next
+            // write is behind the tile barrier of the next step, or behind the partner's own arrival at the next
+            // epilogue's pair barrier
             it = it_next;
             w = w_next;
         }
-        // a warp that gives up (a bounded wait ran out) releases its partner, which may be waiting at the named barrier
-        if (!ok) named_bar_arrive(pair_bar, 64);
+        // a warp that gives up (a bounded wait ran out) releases whoever may be waiting for it at a named barrier
+        if (!ok) {
+            named_bar_arrive(pair_bar, 64);
+            named_bar_arrive(tile_bar, 256);
+        }
     }
 
     // common exit: everybody arrives here (all waits are bounded), then TMEM is freed

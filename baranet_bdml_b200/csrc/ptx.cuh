@@ -67,6 +67,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// try_wait with a suspend-time hint: returns when the phase completes or after about `ns` nanoseconds
+__device__ __forceinline__ bool mbar_try_wait_ns(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+
 // Non-blocking test (try_wait may suspend the thread for a while before it answers; this one never does): for
 // a thread that polls several barriers in turn.
 __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {

@@ -30,8 +30,7 @@ class PagedKVCache:
         self.pool = torch.zeros((num_pages, num_kv_heads, 2, PAGE_TOKENS, head_dim), dtype=torch.bfloat16, device=device)
         self.page_table = torch.zeros((num_seqs, max_pages_per_seq), dtype=torch.int32, device=device)
         self.seq_lens = torch.zeros((num_seqs,), dtype=torch.int32, device=device)
-        self._ws: Optional[Workspace] = None
-        self._ws_key = None
+        self._ws = {}          # decode scratch per (B, Hq, max_seq_len, chunk_tokens); kept while the cache lives
 
     @property
     def max_seq_len(self) -> int:
@@ -57,14 +56,22 @@ class PagedKVCache:
             0 if k_new.dtype == torch.float32 else 1, self.num_kv_heads, self.head_dim, self.theta, _stream()))
 
     def workspace(self, B: int, Hq: int, max_seq_len: int, chunk_tokens: int = 0) -> Workspace:
+        """The decode scratch for this shape.  A buffer, once handed out, is never freed or replaced while the
+        cache lives: a captured CUDA graph may hold its address."""
         key = (B, Hq, max_seq_len, chunk_tokens)
-        if self._ws is None or self._ws_key != key:
+        ws = self._ws.get(key)
+        if ws is None:
             n = _lib.load().bn_attn_decode_workspace_bytes(B, Hq, self.num_kv_heads, self.head_dim, max_seq_len,
                                                           chunk_tokens)
             if n == 0:
                 raise RuntimeError("bn_attn_decode_paged: unsupported shape")
-            self._ws, self._ws_key = Workspace(n, self.pool.device), key
-        return self._ws
+            ws = self._ws[key] = Workspace(n, self.pool.device)
+        return ws
+
+    def status(self) -> None:
+        """Raises if a decode launch on any of this cache's scratch buffers gave up on a bounded wait."""
+        for ws in self._ws.values():
+            ws.status()
 
     def decode(self, q: torch.Tensor, *, num_heads: int, scale: Optional[float] = None, rope_q: bool = True,
                q_positions: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,

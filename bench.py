@@ -344,8 +344,7 @@ def measure_decode(torch, args, rank, world, dist, reduce_max, pk):
     dsteps = args.steps if args.decode_only else max(args.steps, 16)
     ms_dec = reduce_max(time_loop(torch, dstep, dsteps, max(3, args.warmup), dist))
     for cch in caches:
-        if cch._ws is not None:
-            cch._ws.status()
+        cch.status()
     gbs = bytes_alg / (ms_dec * 1e-3) / 1e9
     return {
         "metric": "decode_attention_hbm_gbs", "value": gbs * world, "unit": "GB/s", "ms_per_step": ms_dec,
@@ -604,7 +603,7 @@ def measure_longctx(torch, args, rank, world, dist, reduce_max, pk):
 
     steps = max(args.steps // 4, 8)
     ms = reduce_max(time_loop(torch, step, steps, 3, dist))
-    cache._ws.status()
+    cache.status()
     bytes_alg = B * L * Hkv * D * 2 * 2           # the whole job, all ranks
     gbs = bytes_alg / (ms * 1e-3) / 1e9
     return {

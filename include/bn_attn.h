@@ -219,7 +219,10 @@ BN_API int bn_kv_append(void* pool, int64_t pool_pages, const int32_t* page_tabl
 /* Bytes of scratch bn_attn_decode_paged needs (partial results of sequences
  * that span several SMs + tickets), for the same chunk_tokens.
  * The scratch must be zero-filled once before its first use; the kernel leaves
- * it clean for the next call. */
+ * it clean for the next call.  The words that must stay clean (the tickets)
+ * have a fixed place that depends on Hkv only, so one buffer sized for the
+ * largest batch may serve calls with any smaller B, max_seq_len and
+ * chunk_tokens, one call at a time, as long as Hkv is the same. */
 BN_API size_t bn_attn_decode_workspace_bytes(int B, int Hq, int Hkv, int D, int max_seq_len, int chunk_tokens);
 
 /* Single-token decode over the paged cache: for every sequence b the last row
@@ -256,12 +259,19 @@ BN_API int bn_attn_decode_paged(const void* q, const void* pool, int64_t pool_pa
  *
  * The first call on each device looks up the array's device address and clears its header with that device
  * current; make that first call outside any stream capture.  All calls on a device share the one array, which
- * keeps what the previous call left (the kernel re-arms its own counters): calls that overlap on the GPU — two
- * streams, two host threads — race on it; issue them on one stream or otherwise serialise them. */
+ * keeps what the previous call left (the kernel re-arms its own counters, which sit at a fixed place whatever the
+ * batch size): calls that overlap on the GPU — two streams, two host threads — race on it; issue them on one
+ * stream or otherwise serialise them. */
 BN_API int bn_attn_decode_paged_static(const void* q, const void* pool, int64_t pool_pages, const int32_t* page_table,
                                        int max_pages, const int32_t* seq_lens, const int32_t* q_positions, void* out,
                                        float* out_f32, float* lse, int B, int Hq, int Hkv, int D, float scale,
                                        float theta, int rope_q, int max_seq_len, bn_stream_t stream);
+
+/* bn_workspace_status for the built-in scratch of bn_attn_decode_paged_static, whose address the caller does not
+ * have (no counterpart in the reference).  Waits for `stream`, reads the scratch's error word and returns BN_OK,
+ * or BN_ERR_TIMEOUT when a call gave up on a bounded wait; in that case the header and the counters are cleared
+ * here, so the next call starts clean.  Allocates nothing; it synchronises, so keep it off the hot path. */
+BN_API int bn_attn_decode_paged_static_status(bn_stream_t stream);
 
 /* Log-sum-exp merge of P partial attention results (split-KV across GPUs):
  *   outs (P, n, D) fp32 normalised partial outputs, lses (P, n) natural log

@@ -48,7 +48,7 @@ def run_decode(cache, q, **kw):
     out = torch.empty((B, Hq, D), dtype=torch.bfloat16, device="cuda")
     cache.decode(tq, num_heads=Hq, out=out, out_f32=out32, lse=lse, **kw)
     torch.cuda.synchronize()
-    cache._ws.status()
+    cache.status()
     return out.float().cpu().numpy().reshape(B, -1), out32.cpu().numpy().reshape(B, -1), lse.cpu().numpy()
 
 

@@ -73,6 +73,42 @@ def test_static_scratch_decode_matches_regular_entry_twice(lib):
         assert np.abs(got_lse - ref_lse).max() <= 1e-3
 
 
+def test_static_scratch_survives_a_growing_batch(lib):
+    """The words that outlive a call (the merge tickets) must not sit where an earlier, smaller batch wrote its
+    partial results: a small batch of long sequences, then the largest batch the entry accepts with long sequences
+    at every index, then small again.  Every (sequence, head) of the large batch is cut across CTAs."""
+    from baranet_bdml_b200 import _lib
+    for seed, lens in ((11, [4096] * 8), (12, [3500] * 64), (13, [4096]), (14, [2100] * 32), (15, [4096] * 8)):
+        cache, q = _case(seed, lens)
+        ref, ref_lse = _regular(lib, cache, q)
+        got, got_lse = _static(lib, cache, q)
+        assert np.isfinite(got).all()
+        assert np.abs(got - ref).max() <= 1e-3, lens[:2]
+        assert np.abs(got_lse - ref_lse).max() <= 1e-3
+    assert lib.bn_attn_decode_paged_static_status(None) == _lib.BN_OK
+
+
+def test_one_caller_owned_scratch_serves_batches_of_any_size(lib):
+    """The same rule for bn_attn_decode_paged: one buffer sized for the largest batch, zero-filled once, then used
+    with a small batch, the large one and a small one again; each against a fresh buffer of its own."""
+    from baranet_bdml_b200 import _lib, ops
+    big = ops.Workspace(lib.bn_attn_decode_workspace_bytes(64, Hq, Hkv, D, 4096, 0))
+    for seed, lens in ((21, [4096] * 4), (22, [3700] * 64), (23, [4096, 5, 3000])):
+        cache, q = _case(seed, lens)
+        ref, ref_lse = _regular(lib, cache, q)
+        B = len(lens)
+        out = torch.empty((B, Hq, D), dtype=torch.float32, device="cuda")
+        lse = torch.empty((B, Hq), dtype=torch.float32, device="cuda")
+        _lib.check(lib.bn_attn_decode_paged(q.data_ptr(), cache.pool.data_ptr(), cache.num_pages,
+                                            cache.page_table.data_ptr(), cache.max_pages, cache.seq_lens.data_ptr(),
+                                            None, None, out.data_ptr(), lse.data_ptr(), B, Hq, Hkv, D, 0.125, 10000.0,
+                                            1, 4096, 0, big.ptr, big.nbytes, None))
+        torch.cuda.synchronize()
+        big.status()
+        assert np.abs(out.cpu().numpy() - ref).max() <= 1e-3, lens[:2]
+        assert np.abs(lse.cpu().numpy() - ref_lse).max() <= 1e-3
+
+
 def test_static_scratch_rejects_what_does_not_fit(lib):
     from baranet_bdml_b200 import _lib
     cache, q = _case(3, [100] * 4)
