@@ -49,14 +49,15 @@ constexpr float PF_LN2 = 0.6931471805599453f;
 constexpr float PF_RESCALE_THRESHOLD = 8.0f;   // log2 units
 
 struct PrefillWsLayout {
-    size_t table, krot, total;
+    size_t table, kmax2, krot, total;
 };
 
 static PrefillWsLayout prefill_layout(int B, int S, int Hkv) {
     PrefillWsLayout L;
     auto up = [](size_t x) { return (x + 255) / 256 * 256; };
     L.table = 256;                                               // after the header (error word)
-    L.krot = L.table + up((size_t)S * (PF_D / 2) * sizeof(float2));
+    L.kmax2 = L.table + up((size_t)S * (PF_D / 2) * sizeof(float2));   // [B][Hkv][key tiles of 128] largest |k|^2
+    L.krot = L.kmax2 + up((size_t)B * Hkv * ((S + PF_BN - 1) / PF_BN) * sizeof(float));
     L.total = L.krot + up((size_t)B * S * Hkv * PF_D * sizeof(__nv_bfloat16));
     return L;
 }
@@ -67,9 +68,11 @@ static PrefillWsLayout prefill_layout(int B, int S, int Hkv) {
 constexpr int RK_POS = 8;   // positions per block
 
 __global__ void __launch_bounds__(256)
-rope_k_kernel(const __nv_bfloat16* __restrict__ k, __nv_bfloat16* __restrict__ krot, float2* __restrict__ table, int B,
-              int S, int Hkv, float theta, int position_offset, int* __restrict__ error_word) {
+rope_k_kernel(const __nv_bfloat16* __restrict__ k, __nv_bfloat16* __restrict__ krot, float2* __restrict__ table,
+              int* __restrict__ kmax2, int B, int S, int Hkv, float theta, int position_offset,
+              int* __restrict__ error_word) {
     __shared__ float2 cs[RK_POS][PF_D / 2];
+    __shared__ int s_kmax[64];          // per KV head (up to 64): largest |k|^2 of this block's keys, as float bits
     const int s0 = blockIdx.x * RK_POS, b = blockIdx.y;
     if (blockIdx.x == 0 && b == 0 && threadIdx.x == 0) *error_word = 0;
     // 16-byte pieces (4 rotation pairs) of this block's positions: issue the loads before the cos/sin work
@@ -84,6 +87,7 @@ rope_k_kernel(const __nv_bfloat16* __restrict__ k, __nv_bfloat16* __restrict__ k
         const int e = threadIdx.x + i * 256;
         raw[i] = e < n_chunks ? __ldg(src + e) : make_uint4(0, 0, 0, 0);
     }
+    if (threadIdx.x < 64) s_kmax[threadIdx.x] = 0;
     {
         const int ds = threadIdx.x / (PF_D / 2), i = threadIdx.x % (PF_D / 2);
         const float freq = rope_inv_freq(i, PF_D, theta);
@@ -93,23 +97,47 @@ rope_k_kernel(const __nv_bfloat16* __restrict__ k, __nv_bfloat16* __restrict__ k
         if (b == 0 && s0 + ds < S) table[(size_t)(s0 + ds) * (PF_D / 2) + i] = v;
     }
     __syncthreads();
-    auto rotate = [&](uint4 x, int e) {
+    // Rotates one 16-byte piece (4 pairs); the squared norm of the key it belongs to is summed over the 8 threads
+    // that hold the key's 8 pieces (neighbouring lanes) and the block's maximum per KV head kept in shared memory.
+    // A non-negative float orders like its bit pattern, so the maxima are integer atomics.
+    auto rotate = [&](uint4 x, int e, bool valid) {
         const int ds = e / chunks_per_pos, c = e % (PF_D / 8);     // position, and which 4 pairs of the head
         uint32_t w[4] = {x.x, x.y, x.z, x.w};
+        float n2 = 0.f;
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
-            const float2 v = cs[ds][c * 4 + t];
+            const float2 v = cs[valid ? ds : 0][c * 4 + t];
             const float x0 = bf16_lo(w[t]), x1 = bf16_hi(w[t]);
             w[t] = pack_bf16(x0 * v.x - x1 * v.y, x0 * v.y + x1 * v.x);
+            const float y0 = bf16_lo(w[t]), y1 = bf16_hi(w[t]);
+            n2 = fmaf(y0, y0, fmaf(y1, y1, n2));
+        }
+        n2 += __shfl_xor_sync(0xffffffffu, n2, 1);
+        n2 += __shfl_xor_sync(0xffffffffu, n2, 2);
+        n2 += __shfl_xor_sync(0xffffffffu, n2, 4);
+        if (valid && c == 0) {
+            const int hh = (e % chunks_per_pos) / (PF_D / 8);
+            // a NaN or an infinity must read as "unbounded": their bit patterns are above every finite float's
+            atomicMax(&s_kmax[hh & 63], n2 == n2 ? __float_as_int(n2) : 0x7fffffff);
         }
         return make_uint4(w[0], w[1], w[2], w[3]);
     };
 #pragma unroll
     for (int i = 0; i < RK_UNROLL; ++i) {
         const int e = threadIdx.x + i * 256;
-        if (e < n_chunks) dst[e] = rotate(raw[i], e);
+        const uint4 y = rotate(raw[i], e, e < n_chunks);
+        if (e < n_chunks) dst[e] = y;
     }
-    for (int e = threadIdx.x + RK_UNROLL * 256; e < n_chunks; e += 256) dst[e] = rotate(__ldg(src + e), e);
+    for (int e0 = RK_UNROLL * 256; e0 < n_chunks; e0 += 256) {     // whole warps take part in the shuffles
+        const int e = e0 + threadIdx.x;
+        const uint4 y = rotate(e < n_chunks ? __ldg(src + e) : make_uint4(0, 0, 0, 0), e, e < n_chunks);
+        if (e < n_chunks) dst[e] = y;
+    }
+    __syncthreads();
+    // the 8 positions of a block lie inside one 128-key tile
+    // (more than 64 KV heads share slots: a head then reads the maximum over the heads of its slot, still a bound)
+    for (int hh = threadIdx.x; hh < Hkv; hh += 256)
+        atomicMax(kmax2 + ((size_t)b * Hkv + hh) * ((S + PF_BN - 1) / PF_BN) + s0 / PF_BN, s_kmax[hh & 63]);
 }
 
 // ---------------------------------------------------------------------------
@@ -120,10 +148,12 @@ struct PrefillParams {
     __nv_bfloat16* out;
     float* lse;
     const float2* table;
+    const float* kmax2;                  // [B][Hkv][n_ktiles]: largest squared norm of a rotated key in a 128-key tile
     int* error_word;
-    int B, S, Hq, Hkv, n_rep, n_qtiles, position_offset, causal;
+    int B, S, Hq, Hkv, n_rep, n_qtiles, n_ktiles, position_offset, causal;
     float inv_bh, inv_hq, inv_n_rep;     // reciprocals of B*Hq, Hq, n_rep for the persistent kernel's unit decode
     float scale_log2;
+    float bound_scale;                   // scale_log2^2 / 60^2: |q|^2 |k|^2 times this <= 1 means every exponent stays within +-60
 };
 
 __global__ void __launch_bounds__(PF_THREADS, 2)
@@ -416,33 +446,51 @@ prefill_kernel_v1(const __grid_constant__ CUtensorMap tmap_k, const __grid_const
 // buffer from its Q K^T to the end of its P V:
 //   TMEM (512 columns): S/P buffers [0,128) [128,256) [256,384) | O0 [384,448) O1 [448,512)
 //   P of keys 0..63 at columns [0,32) of the buffer, keys 64..127 at [64,96).
-// The MMA warp issues  Q K^T(s+3)  right after  P V(s): the tensor pipe executes
+// The MMA thread issues  Q K^T(s+3)  right after  P V(s): the tensor pipe executes
 // in issue order, so the new scores cannot overtake the read of the old
-// probabilities, and no softmax warp ever waits for the Q K^T of its NEXT step,
-// which was issued a whole step earlier.  With the exponent reference fixed
-// (below) the steps of a tile need nothing from each other but the order of their
-// P V, so the two groups of softmax warps run back to back on scores that are
-// already there, and the exponential unit (16 per clock per SM: 1024 cycles for a
-// 128x128 step against 512 tensor cycles at head_dim 64) is the pipe that bounds
-// the kernel.
-// Both tiles read the same K/V stages, so each K/V tile is fetched once per 256
-// query rows.  Q tiles arrive by TMA (double buffered across units) and are rotated
-// in place, a row per warp instruction (lane = rotation pair), one unit AHEAD:
-// right after a tile's last step and before its epilogue.
+// probabilities, and a softmax warp normally finds the scores of its NEXT step
+// (issued a step and a half earlier) already there.  With the exponent reference
+// fixed (below) the steps of a tile need nothing from each other but the order of
+// their P V, so the two groups of softmax warps run back to back; the exponential
+// unit (16 per clock per SM: 1024 cycles for a 128x128 step against 512 tensor
+// cycles at head_dim 64) is the pipe that bounds a step.
+// Both tiles read the same K/V stages (K and V of a stage behind ONE barrier), so
+// each K/V tile is fetched once per 256 query rows.  Q tiles are requested by TMA a
+// whole unit ahead (as soon as the unit before last has released the buffer) and
+// rotated in place by the tile's own softmax warps, a row per warp instruction
+// (lane = rotation pair), right after the tile's last step and before its epilogue.
 // Softmax is ONE pass per step with an exponent reference that starts at 0 and
 // moves only when a probability would leave [2^-64, 2^64] (bf16 and fp32 keep
-// their relative precision over that range).  That case is decided per tile and
-// step (one 256-thread named barrier that ORs the flag); the tile then asks the
-// MMA warp to compute the step's scores again (the first pass has overwritten
-// part of them), takes the true row maxima, rescales O and l and redoes the step.
+// their relative precision over that range).  Whether that can happen at all is
+// known before the step: |q . k| <= |q| |k|, with the largest squared norm of the
+// tile's rotated query rows (taken during the rotation) and of the key tile's
+// rotated keys (taken by the K rotation launch).  A step whose bound keeps every
+// exponent within +-60 runs with no check and NO synchronisation between warps
+// beyond the two mbarriers of its score buffer.  Only an unbounded step is checked:
+// the tile's eight warps OR an "out of range" flag through a 256-thread named
+// barrier; if it is raised the tile asks the MMA thread to compute the step's
+// scores again (the first pass has overwritten part of them), takes the true row
+// maxima, rescales O and l and redoes the step, and the rest of the unit stays on
+// the checked path.
+// On a tile that touches the diagonal a 16-key chunk is classified per warp: all
+// keys valid for its 32 rows (no mask), none (zeros, no arithmetic), or mixed.
 // Named barriers are not bounded waits; they cannot hang because a warp that
 // gives up (a bounded mbarrier wait ran out, or the CTA-wide abort flag was seen)
 // arrives once on every named barrier it belongs to before it leaves, and every
 // warp checks the abort flag after each named barrier.
+// Measured and dropped on this structure: a quarter of the exponentials as a cubic
+// on the FMA pipe (the softmax warps' issue slots are as scarce as the exponential
+// unit: 248 vs 225 us); two extra warps that only rotate Q (a single warp per tile
+// is too slow for the short units); rotating the next unit's Q after a unit's
+// first step; a rolled 16-column loop with out-of-line helpers (smaller code,
+// slower: 260 us).
 // Optional event log for performance work (compiled out unless built with -DBN_TIMELINE): the warps of CTA 0
 // append (clock64, code) pairs to the caller's lse buffer, 2048 entries per warp, INSTEAD of the log-sum-exp.
 #ifdef BN_TIMELINE
-#define BN_LOG(code) do { if (blockIdx.x == 0 && p.lse && log_n < 2048) { long long* L_ = reinterpret_cast<long long*>(p.lse) + ((size_t)(threadIdx.x / 32) * 2048 + log_n) * 2; L_[0] = clock64(); L_[1] = (long long)(code); ++log_n; } } while (0)
+#ifndef BN_TL_CTA
+#define BN_TL_CTA 0
+#endif
+#define BN_LOG(code) do { if (blockIdx.x == BN_TL_CTA && p.lse && log_n < 2048) { long long* L_ = reinterpret_cast<long long*>(p.lse) + ((size_t)(threadIdx.x / 32) * 2048 + log_n) * 2; L_[0] = clock64(); L_[1] = (long long)(code); ++log_n; } } while (0)
 #else
 #define BN_LOG(code) do {} while (0)
 #endif
@@ -565,6 +613,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     __shared__ int s_abort;
     __shared__ int s_redo[2];
                   // per tile: how many steps have asked for their scores again
+    __shared__ float s_qmax2[2][2][8];         // [Q buffer][tile][warp of the tile]: largest |q|^2 of the rows it rotated
     __shared__ float s_xchg[2][2][PF_BM];      // [tile][column half][row]: exchange between the two threads of a row
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
@@ -610,31 +659,47 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 
     if (warp == 17) {
         // ---------------------------------------------------------- TMA producer
+        // K/V tiles stream through a four-stage ring.  The Q tiles of a unit are requested a whole unit ahead: as
+        // soon as the unit before last has released their buffer, so that the rotation warp has the whole current
+        // unit to rotate them.
         if (lane == 0) {
             prefetch_tensormap(&tmap_q);
             prefetch_tensormap(&tmap_k);
             prefetch_tensormap(&tmap_v);
             int stage = 0;
             uint32_t phase = 0;
-            int q_use[2] = {0, 0};        // how many units have used tile slot u so far
+            int q_round[2] = {0, 0};      // per tile slot: the next round whose Q tile is still to be requested
+            int q_cnt[2] = {0, 0};        // ... and how many have been requested (buffer and barrier parity)
             bool ok = true;
+            // requests tile slot u's Q tiles up to round `upto`; with `block` the buffer is waited for
+            auto load_q = [&](int u, int upto, bool block) {
+                while (ok && q_round[u] <= upto) {
+                    const int k = unit_of(q_round[u], n_units);
+                    if (k < 0) { q_round[u] = 0x7fffffff; return; }
+                    const UnitInfo w = unit_info(p, k);
+                    if ((u ? w.n_t[1] : w.n_t[0]) > 0) {
+                        const int buf = q_cnt[u] & 1;
+                        const uint32_t par = ((q_cnt[u] >> 1) & 1) ^ 1u;
+                        const uint32_t bar = smem_u32(&bar_qfree[buf][u]);
+                        if (block) { ok = mbar_wait(bar, par, &s_abort); if (!ok) return; }
+                        else if (!mbar_test_wait(bar, par)) return;
+                        ++q_cnt[u];
+                        mbar_arrive_expect_tx(smem_u32(&bar_qfull[buf][u]), PF_TILE_BYTES);
+                        tma_load_4d(sQ + (buf * 2 + u) * PF_TILE_BYTES, &tmap_q, 0, w.h, (2 * w.qp + u) * PF_BM, w.b,
+                                    smem_u32(&bar_qfull[buf][u]));
+                    }
+                    ++q_round[u];
+                }
+            };
             for (int it = 0; ok; ++it) {
                 const int k = unit_of(it, n_units);
                 if (k < 0) break;
                 const UnitInfo w = unit_info(p, k);
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    if (!ok || w.n_t[u] == 0) continue;
-                    const int buf = q_use[u] & 1;
-                    const uint32_t par = (q_use[u] >> 1) & 1;
-                    ++q_use[u];
-                    ok = mbar_wait(smem_u32(&bar_qfree[buf][u]), par ^ 1u, &s_abort);
-                    if (!ok) break;
-                    mbar_arrive_expect_tx(smem_u32(&bar_qfull[buf][u]), PF_TILE_BYTES);
-                    tma_load_4d(sQ + (buf * 2 + u) * PF_TILE_BYTES, &tmap_q, 0, w.h, (2 * w.qp + u) * PF_BM, w.b,
-                                smem_u32(&bar_qfull[buf][u]));
-                }
+                load_q(0, it, true);
+                load_q(1, it, true);
                 for (int j = 0; ok && j < w.n_max; ++j) {
+                    load_q(0, it + 1, false);
+                    load_q(1, it + 1, false);
                     ok = mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, &s_abort);
                     if (!ok) break;
                     mbar_arrive_expect_tx(smem_u32(&bar_kvfull[stage]), 2 * PF_TILE_BYTES);
@@ -815,7 +880,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         };
         // RoPE on the TMA-loaded Q tile, in place (128-byte-swizzled, K-major).  Each of the tile's eight warps
         // rotates 16 rows, a row at a time with lane = rotation pair: the row of the cos/sin table is one
-        // coalesced 256-byte load and the lanes touch the 32 banks of the row's 128 bytes.
+        // coalesced 256-byte load and the lanes touch the 32 banks of the row's 128 bytes.  Also leaves the largest
+        // squared norm of the warp's rotated rows for the bound on the scores.
         auto rotate_q = [&](const UnitInfo& w) -> bool {
             const int buf = q_use & 1;
             const uint32_t par = (q_use >> 1) & 1;
@@ -828,6 +894,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             if (!mbar_wait(smem_u32(&bar_qfull[buf][u]), par, &s_abort)) return false;
             const uint32_t tile = sQ + (buf * 2 + u) * PF_TILE_BYTES + r_first * 128 + (lane & 3) * 4;
             const uint32_t chunk = (uint32_t)lane >> 2;
+            unsigned row_max = 0;
 #pragma unroll
             for (int r0 = 0; r0 < 16; r0 += 8) {
                 uint32_t x[8];
@@ -840,11 +907,19 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                     const float x0 = bf16_lo(x[r]), x1 = bf16_hi(x[r]);
                     const uint32_t y = pack_bf16(x0 * t2.x - x1 * t2.y, x0 * t2.y + x1 * t2.x);
                     asm volatile("st.shared.b32 [%0], %1;" ::"r"(tile + (r0 + r) * 128 + ((chunk ^ r) << 4)), "r"(y) : "memory");
+                    // squared norm of the rotated row, summed over the 32 lanes in fixed point (units of 2^-10,
+                    // rounded up); a lane value at the cap makes the sum reach it, which reads as "unbounded"
+                    const float y0 = bf16_lo(y), y1 = bf16_hi(y);
+                    const float n2 = fmaf(y0, y0, y1 * y1) * 1024.f + 1.f;
+                    row_max = max(row_max, __reduce_add_sync(0xffffffffu, (unsigned)(n2 <= 1.3e8f ? n2 : 1.3e8f)));   // a NaN takes the cap
                 }
             }
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bar_qrot[buf][u]));
+            if (lane == 0) {
+                s_qmax2[buf][u][warp % 8] = row_max >= 130000000u ? INFINITY : (float)row_max * (1.f / 1024.f);
+                mbar_arrive(smem_u32(&bar_qrot[buf][u]));
+            }
             return true;
         };
         int it;
@@ -860,8 +935,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 
             float m_ref = 0.f;         // exponent reference, raw score units (the same in both threads of a row)
             float l_run = 0.f;         // this thread's half of the row sum
+            // A step whose scores are bounded needs no check at all: |q . k| <= |q| |k|, with the largest |q|^2 of
+            // the tile's rotated rows (left by the rotation) and the largest |k|^2 of the key tile (left by the K
+            // rotation launch).  q_bound * |k|^2 <= 1 means that every exponent of the step lies within +-60.
+            float q_bound = 0.f;       // set at the unit's first step
+            bool moved = false;        // the reference has left 0 in this unit: every later step is checked
+            const float* kmax2 = p.kmax2 + ((size_t)b * p.Hkv + w.g) * p.n_ktiles;
             const int row_last = p.causal ? min(p.S - 1, gi + p.position_offset) : p.S - 1;
             const int tile_free_last = p.causal ? min(p.S - 1, i0 + p.position_offset) : p.S - 1;   // no mask needed up to here
+            // last valid key of the first and of the last row of this warp's 32 rows
+            const int warp_first_last = p.causal ? min(p.S - 1, gi - lane + p.position_offset) : p.S - 1;
+            const int warp_last_last = p.causal ? min(p.S - 1, gi - lane + 31 + p.position_offset) : p.S - 1;
 
             for (int j = 0; j < nt; ++j) {
                 // this step's place in the CTA's sequence, hence its score buffer
@@ -869,56 +953,78 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 const uint32_t sb = s % P2_NSBUF;
                 const uint32_t tS = tmem + lane_base + sb * 128 + hf * 64;   // 64 fp32 scores; P goes over the first 32
                 BN_LOG(1 | u << 8 | j << 16);
+                const float k_max2 = __ldg(kmax2 + j);
                 ok = mbar_wait(smem_u32(&bar_s[sb]), (s / P2_NSBUF) & 1, &s_abort);
                 if (!ok) break;
                 tc::fence_after_sync();
                 BN_LOG(2 | u << 8 | j << 16);
+                if (j == 0) {
+                    // written by the tile's eight warps before they arrived on the barrier the MMA thread waited
+                    // for before this step's Q K^T
+                    const volatile float* qm = s_qmax2[(q_use - 1) & 1][u];
+                    float m2 = qm[0];
+#pragma unroll
+                    for (int i = 1; i < 8; ++i) m2 = fmaxf(m2, qm[i]);
+                    q_bound = m2 * p.bound_scale;
+                }
+                const bool bounded = !moved && (q_bound * k_max2 <= 1.0f);
                 const int j0 = j * PF_BN + hf * 64;             // first key of this thread's 64 columns
                 const bool need_mask = (j0 + 63) > tile_free_last;
 
-                // one pass over this thread's 64 columns: P = exp2(S * scale_log2 - m_ref * scale_log2), written over
-                // columns that have already been read, with the load of the next 16 columns in flight while the
-                // current 16 are processed
-                auto half_pass = [&](float mneg) {
-                    uint64_t sum2 = 0;   // (0.f, 0.f)
-                    const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2), mneg2 = pack_f32x2(mneg, mneg);
-                    uint32_t r0[16], r1[16], pk[8];
-                    auto chunk = [&](uint32_t (&r)[16], int c) {
-                        if (need_mask) softmax_chunk16<true>(r, pk, scale2, mneg2, j0 + c * 16, row_last, sum2);
-                        else softmax_chunk16<false>(r, pk, scale2, mneg2, j0 + c * 16, row_last, sum2);
-                    };
-                    tc::ld16(tS + 0, r0);
-                    tc::wait_ld(r0);
-                    tc::ld16(tS + 16, r1);
-                    chunk(r0, 0);
-                    tc::st8(tS + 0, pk);
-                    tc::wait_ld(r1);
-                    tc::ld16(tS + 32, r0);
-                    chunk(r1, 1);
-                    tc::st8(tS + 8, pk);
-                    tc::wait_ld(r0);
-                    tc::ld16(tS + 48, r1);
-                    chunk(r0, 2);
-                    tc::st8(tS + 16, pk);
-                    tc::wait_ld(r1);
-                    chunk(r1, 3);
-                    tc::st8(tS + 24, pk);
-                    float s0, s1;
-                    unpack_f32x2(sum2, s0, s1);
-                    return s0 + s1;
-                };
-
+                // One pass over this thread's 64 columns: P = exp2(S * scale_log2 - m_ref * scale_log2), each 8 packed
+                // columns written over scores that have already been read.  A 16-column chunk is decided for the
+                // warp: all 16 keys valid for its 32 rows -> no mask; none of them -> zeros without any arithmetic;
+                // else the masked form.
                 // The exponent reference starts at 0 and moves only when it has to: p = 2^(s*c - ref) may be
                 // anywhere in [2^-64, 2^64] without any loss (bf16 and fp32 keep their relative precision over
                 // that range), so for ordinary score magnitudes there is never a second pass or an O rescale.
-                float lsum = half_pass(-m_ref * p.scale_log2);
-                const bool over = !(lsum <= 0x1p64f) || (j == 0 && hf == 0 && lsum < 0x1p-64f);
-                const bool redo = named_bar_or(tile_bar, 256, over);
-                if (s_abort) { ok = false; break; }
-                if (redo) {
+                float lsum;
+                bool second = false;
+                for (;;) {
+                    {
+                        uint64_t sum2 = 0;   // (0.f, 0.f)
+                        const float mneg = -m_ref * p.scale_log2;
+                        const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2), mneg2 = pack_f32x2(mneg, mneg);
+                        uint32_t r0[16], r1[16], pk[8];
+                        auto chunk = [&](uint32_t (&r)[16], int c) {
+                            const int kc = j0 + c * 16;
+                            if (!need_mask || kc + 15 <= warp_first_last) softmax_chunk16<false>(r, pk, scale2, mneg2, kc, row_last, sum2);
+                            else if (kc > warp_last_last) {
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) pk[i] = 0u;
+                            } else softmax_chunk16<true>(r, pk, scale2, mneg2, kc, row_last, sum2);
+                        };
+                        // the load of the next 16 columns is in flight while the current 16 are processed
+                        tc::ld16(tS + 0, r0);
+                        tc::wait_ld(r0);
+                        tc::ld16(tS + 16, r1);
+                        chunk(r0, 0);
+                        tc::st8(tS + 0, pk);
+                        tc::wait_ld(r1);
+                        tc::ld16(tS + 32, r0);
+                        chunk(r1, 1);
+                        tc::st8(tS + 8, pk);
+                        tc::wait_ld(r0);
+                        tc::ld16(tS + 48, r1);
+                        chunk(r0, 2);
+                        tc::st8(tS + 16, pk);
+                        tc::wait_ld(r1);
+                        chunk(r1, 3);
+                        tc::st8(tS + 24, pk);
+                        float s0, s1;
+                        unpack_f32x2(sum2, s0, s1);
+                        lsum = s0 + s1;
+                    }
+                    if (bounded || second) break;
+                    const bool over = !(lsum <= 0x1p64f) || (j == 0 && hf == 0 && lsum < 0x1p-64f);
+                    const bool redo = named_bar_or(tile_bar, 256, over);
+                    if (s_abort) { ok = false; break; }
+                    if (!redo) break;
                     // Rare, and taken by the whole tile together.  The first pass has overwritten scores, so the
-                    // MMA warp computes them again; its commit also tells that every earlier P V of this tile has
+                    // MMA thread computes them again; its commit also tells that every earlier P V of this tile has
                     // completed, so O may be rescaled here.
+                    moved = true;
+                    second = true;
                     tc::wait_st();
                     tc::fence_before_sync();
                     ++redo_n;
@@ -929,7 +1035,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                     if (!ok) break;
                     tc::fence_after_sync();
                     float hmax = -INFINITY;
-#pragma unroll
+#pragma unroll 1
                     for (int c = 0; c < 4; ++c) {
                         uint32_t r[16];
                         tc::ld16(tS + c * 16, r);
@@ -947,35 +1053,34 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                     if (j > 0) {
                         const float alpha = ex2((m_ref - m_upd) * p.scale_log2);
                         l_run *= alpha;
-                        uint32_t ro[32];           // this thread's 32 of the 64 O columns
-                        tc::ld32(tO, ro);
-                        tc::wait_ld(ro);
+#pragma unroll 1
+                        for (int c = 0; c < 2; ++c) {       // this thread's 32 of the 64 O columns
+                            uint32_t ro[16];
+                            tc::ld16(tO + c * 16, ro);
+                            tc::wait_ld(ro);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) ro[i] = __float_as_uint(__uint_as_float(ro[i]) * alpha);
-                        tc::st32(tO, ro);
+                            for (int i = 0; i < 16; ++i) ro[i] = __float_as_uint(__uint_as_float(ro[i]) * alpha);
+                            tc::st16(tO + c * 16, ro);
+                        }
                     }
                     m_ref = m_upd;
-                    lsum = half_pass(-m_ref * p.scale_log2);
+                }
+                if (!ok) break;
+                if (second) {
                     named_bar_sync(pair_bar, 64);      // the exchange slots may be written again
                     if (s_abort) { ok = false; break; }
-                    l_run += lsum;
-                    tc::wait_st();
-                    tc::fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&bar_rp[u]));
-                } else {
-                    l_run += lsum;
-                    tc::wait_st();
-                    tc::fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&bar_p[sb]));
                 }
+                l_run += lsum;
+                tc::wait_st();
+                tc::fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(second ? smem_u32(&bar_rp[u]) : smem_u32(&bar_p[sb]));
                 BN_LOG(6 | u << 8 | j << 16);
             }
             if (!ok) break;
             sbase += w.n_t[0] + w.n_t[1];
 
-            // The next unit's Q tile is rotated BEFORE this unit's epilogue: the MMA warp needs it to start the
+            // The next unit's Q tile is rotated BEFORE this unit's epilogue: the MMA thread needs it to start the
             // next unit, while the epilogue has to wait for the last P V anyway.
             int it_next;
             UnitInfo w_next;
@@ -984,6 +1089,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 ok = rotate_q(w_next);
                 if (!ok) break;
             }
+
 
             // epilogue: O / l -> bf16 -> global; each thread of a row writes its 32 columns
             ok = mbar_wait(smem_u32(&bar_o[u]), units_done & 1, &s_abort);
@@ -1081,9 +1187,12 @@ extern "C" int bn_attn_prefill_bf16(const void* q, const void* k, const void* v,
     __nv_bfloat16* krot = reinterpret_cast<__nv_bfloat16*>(ws + L.krot);
     cudaStream_t st = as_stream(stream);
 
+    int* kmax2 = reinterpret_cast<int*>(ws + L.kmax2);
     if (!(flags & BN_PREFILL_REUSE_ROTATED_K)) {
-        rope_k_kernel<<<dim3((S + RK_POS - 1) / RK_POS, B), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(k), krot, table, B, S, Hkv, theta,
-                                                  position_offset, error_word);
+        cudaError_t e = cudaMemsetAsync(kmax2, 0, L.krot - L.kmax2, st);      // the rotation takes maxima into it
+        if (e != cudaSuccess) return fail(BN_ERR_CUDA, "bn_attn_prefill_bf16: cudaMemsetAsync: %s", cudaGetErrorString(e));
+        rope_k_kernel<<<dim3((S + RK_POS - 1) / RK_POS, B), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(k), krot, table,
+                                                                          kmax2, B, S, Hkv, theta, position_offset, error_word);
         if (int rc = launch_status("bn_attn_prefill_bf16 (rope_k)")) return rc;
     }
 
@@ -1111,12 +1220,15 @@ extern "C" int bn_attn_prefill_bf16(const void* q, const void* k, const void* v,
     p.out = static_cast<__nv_bfloat16*>(out);
     p.lse = lse;
     p.table = table;
+    p.kmax2 = reinterpret_cast<const float*>(kmax2);
+    p.n_ktiles = (S + PF_BN - 1) / PF_BN;
     p.error_word = error_word;
     p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv; p.n_rep = Hq / Hkv;
     p.n_qtiles = (int)n_qtiles;
     p.position_offset = position_offset;
     p.causal = causal;
     p.scale_log2 = scale * PF_LOG2E;
+    p.bound_scale = p.scale_log2 * p.scale_log2 / 3600.f;
 
     static thread_local int configured_dev = -1;
     int dev = 0;
