@@ -100,9 +100,8 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 // other waiter of the CTA leaves too and the kernel can return.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 
-// (the polling loop is out of line: a wait usually succeeds at once, and dozens of inlined copies of the loop
-// would only widen the kernels' instruction footprint)
-static __device__ __noinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
     uint64_t t0 = 0;
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -113,11 +112,6 @@ static __device__ __noinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity
             else if (now - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
         }
     }
-}
-
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_poll(bar, parity, abort_flag);
 }
 
 // Named barrier `id` over `n_threads` threads (a multiple of 32) that also ORs a predicate across them

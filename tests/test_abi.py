@@ -66,3 +66,41 @@ def test_host_mirror_shapes_without_gpu():
         t[::2]
     with pytest.raises(RuntimeError, match="only GPU implementation available"):
         t @ t.T
+
+
+C_CALLER = r"""
+#include <stdio.h>
+#include <string.h>
+#include "bn_attn.h"
+int main(void) {
+    /* a caller that has nothing but the header: statuses, the size queries and argument checks need no GPU */
+    if (bn_version() < 100) return 1;
+    if (bn_mm_f32(NULL, 0, 0, NULL, 0, 0, NULL, 0, 0, 1, 1, 1, NULL) != BN_ERR_INVALID_ARG) return 2;
+    if (strstr(bn_last_error(), "null pointer") == NULL) return 3;
+    if (bn_attn_prefill_bf16_workspace_bytes(8, 2048, 32, 4, 64) == 0) return 4;
+    if (bn_attn_decode_workspace_bytes(64, 32, 4, 64, 4096, 0) == 0) return 5;
+    printf("ok %d\n", bn_version());
+    return 0;
+}
+"""
+
+
+@pytest.mark.parametrize("compiler,ext,std", [("gcc", ".c", "-std=c99"), ("g++", ".cpp", "-std=c++11")])
+def test_header_serves_a_plain_c_and_a_cpp_caller(lib, tmp_path, compiler, ext, std):
+    """include/bn_attn.h compiled by a C and by a C++ compiler from outside the library (the position of the
+    reference's C++ layer, src/llama/llama_layers.hpp:57-113), linked against the built library and run."""
+    import subprocess
+    from baranet_bdml_b200 import _lib
+    src = tmp_path / ("caller" + ext)
+    src.write_text(C_CALLER)
+    exe = tmp_path / "caller"
+    libdir = os.path.dirname(_lib.LIB_PATH)
+    env = dict(os.environ)
+    env.pop("CC", None)
+    env.pop("CXX", None)
+    subprocess.run([compiler, std, "-Wall", "-Wextra", "-Werror", "-pedantic", "-I" + os.path.join(ROOT, "include"),
+                    str(src), "-o", str(exe), "-L" + libdir, "-l:" + os.path.basename(_lib.LIB_PATH),
+                    "-Wl,-rpath," + libdir], check=True, env=env, capture_output=True, text=True)
+    res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=60)
+    assert res.returncode == 0, (res.returncode, res.stdout, res.stderr)
+    assert res.stdout.startswith("ok")
