@@ -49,6 +49,12 @@ SIGNATURES = {
     "bn_attn_lse_combine": (_i, [_p, _p, _i, _i64, _i, _p, _p, _p, _p]),
     "bn_attn_lse_combine_strided": (_i, [_p, _i64, _p, _i64, _i, _i64, _i, _p, _p, _p, _p]),
     "bn_workspace_status": (_i, [_p, _p]),
+    "bn_exchange_create": (_i, [_i, _i, _i, _i, C.POINTER(_p)]),
+    "bn_exchange_ipc_handle": (_i, [_p, _p]),
+    "bn_exchange_open_peers": (_i, [_p, _p, _i]),
+    "bn_exchange_combine": (_i, [_p, _p, _p, _p, C.c_uint, _p]),
+    "bn_exchange_status": (_i, [_p, _p]),
+    "bn_exchange_destroy": (None, [_p]),
 }
 
 _lib = None

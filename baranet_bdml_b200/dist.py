@@ -77,25 +77,87 @@ def combine_partials(out_partial: torch.Tensor, lse_partial: torch.Tensor, group
 
 
 class PartialExchange:
-    """The exchange step of the sequence-split decode with nothing but three launches per step: the decode
-    kernel writes its normalised partial output and log-sum-exp straight into `out_view` / `lse_view` (two
-    regions of one contiguous send buffer), `combine()` gathers every rank's buffer with one all-gather and
-    merges them with bn_attn_lse_combine_strided.  All buffers are allocated once."""
+    """The exchange step of the sequence-split decode.  The decode kernel writes its normalised partial output and
+    log-sum-exp straight into `out_view` / `lse_view` (two regions of one contiguous send buffer); `combine()` merges
+    every rank's buffer into `out` / `lse`, identical on all ranks.  All buffers are allocated once.
 
-    def __init__(self, n: int, D: int, group=None, device="cuda"):
+    mode "nccl" (default): one all-gather into `recv`, then bn_attn_lse_combine_strided (two launches).
+    mode "peer": ONE launch, bn_exchange_combine: every rank stores its partial into every rank's exchange buffer
+        over NVLink peer memory (buffers made known to each other through CUDA IPC handles, gathered here with
+        torch.distributed), waits for the others with a time limit and merges.  `status()` raises if a wait ran
+        out; the object is then unusable.  Falls back to "nccl" (and says so in `kind`) when the peer mapping
+        cannot be set up."""
+
+    def __init__(self, n: int, D: int, group=None, device="cuda", mode: str = "nccl", wait_us: int = 1000000):
         import torch.distributed as dist
         self.n, self.D, self.group = int(n), int(D), group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.wait_us = int(wait_us)
         self.send = torch.empty(self.n * (self.D + 1), dtype=torch.float32, device=device)
         self.recv = torch.empty(self.world * self.n * (self.D + 1), dtype=torch.float32, device=device)
         self.out_view = self.send[: self.n * self.D].view(self.n, self.D)
         self.lse_view = self.send[self.n * self.D:]
         self.out = torch.empty((self.n, self.D), dtype=torch.float32, device=device)
         self.lse = torch.empty((self.n,), dtype=torch.float32, device=device)
+        self._peer = None
+        self.kind = "one NCCL all-gather + merge kernel" if self.world > 1 else "none (one rank)"
+        if mode == "peer":
+            why = self._open_peer()
+            if why is None:
+                self.kind = "one kernel: peer stores over NVLink + bounded wait + merge"
+            else:
+                self.kind += f" (peer exchange unavailable: {why})"
+        elif mode != "nccl":
+            raise ValueError(f"PartialExchange: unknown mode {mode!r}")
+
+    def _open_peer(self) -> Optional[str]:
+        """None on success, else the reason (every rank takes the same decision)."""
+        import ctypes as C
+        import torch.distributed as dist
+        from . import _lib
+        lib = _lib.load()
+        handle = C.c_void_p()
+        ok, why = True, ""
+        if lib.bn_exchange_create(self.n, self.D, self.world, self.rank, C.byref(handle)) != _lib.BN_OK:
+            ok, why = False, _lib.last_error()
+        mine = (C.c_char * 64)()
+        if ok and self.world > 1 and lib.bn_exchange_ipc_handle(handle, mine) != _lib.BN_OK:
+            ok, why = False, _lib.last_error()
+        if self.world > 1:
+            gathered = [None] * self.world
+            dist.all_gather_object(gathered, (ok, why, bytes(mine)), group=self.group)
+            bad = [g for g in gathered if not g[0]]
+            if bad:
+                if handle:
+                    lib.bn_exchange_destroy(handle)
+                return bad[0][1]
+            blob = b"".join(g[2] for g in gathered)
+            rc = lib.bn_exchange_open_peers(handle, blob, 0)
+            results = [None] * self.world
+            dist.all_gather_object(results, (rc, _lib.last_error() if rc else ""), group=self.group)
+            bad = [r for r in results if r[0] != _lib.BN_OK]
+            if bad:
+                lib.bn_exchange_destroy(handle)
+                return bad[0][1]
+        else:
+            if not ok:
+                return why
+            if lib.bn_exchange_open_peers(handle, None, 1) != _lib.BN_OK:
+                why = _lib.last_error()
+                lib.bn_exchange_destroy(handle)
+                return why
+        self._peer = handle
+        return None
 
     def combine(self) -> Tuple[torch.Tensor, torch.Tensor]:
         import torch.distributed as dist
         from . import _lib
+        stream = torch.cuda.current_stream().cuda_stream
+        if self._peer is not None:
+            _lib.check(_lib.load().bn_exchange_combine(self._peer, self.send.data_ptr(), self.out.data_ptr(),
+                                                       self.lse.data_ptr(), self.wait_us, stream))
+            return self.out, self.lse
         src = self.send
         if self.world > 1:
             dist.all_gather_into_tensor(self.recv, self.send, group=self.group)
@@ -103,5 +165,17 @@ class PartialExchange:
         stride = self.n * (self.D + 1)
         _lib.check(_lib.load().bn_attn_lse_combine_strided(
             src.data_ptr(), stride, src.data_ptr() + 4 * self.n * self.D, stride, self.world, self.n, self.D,
-            self.out.data_ptr(), None, self.lse.data_ptr(), torch.cuda.current_stream().cuda_stream))
+            self.out.data_ptr(), None, self.lse.data_ptr(), stream))
         return self.out, self.lse
+
+    def status(self) -> None:
+        """Raises if a bounded wait of the peer exchange ran out (a rank never delivered)."""
+        if self._peer is not None:
+            from . import _lib
+            _lib.check(_lib.load().bn_exchange_status(self._peer, torch.cuda.current_stream().cuda_stream))
+
+    def close(self) -> None:
+        if self._peer is not None:
+            from . import _lib
+            _lib.load().bn_exchange_destroy(self._peer)
+            self._peer = None

@@ -133,6 +133,40 @@ class GroupedQueryAttention:
         return [self.q_proj, self.k_proj, self.v_proj, self.o_proj]
 
 
+_DEVICE_INIT = None     # (std, torch.Generator) while `device_init` is active
+
+
+class device_init:
+    """Within this context the bf16 layers draw their weights on the GPU from N(0, std) instead of the reference's
+    Xavier initialisation on the host (mygrad/llama/llama_layers.py:80-85): for benchmarks at full model size,
+    where a billion host-side normal draws would take longer than the measurement."""
+
+    def __init__(self, std: float, seed: int = 0):
+        self.std, self.seed = float(std), int(seed)
+
+    def __enter__(self):
+        import torch
+        global _DEVICE_INIT
+        _DEVICE_INIT = (self.std, torch.Generator(device="cuda").manual_seed(self.seed))
+        return self
+
+    def __exit__(self, *exc):
+        global _DEVICE_INIT
+        _DEVICE_INIT = None
+        return False
+
+
+def _init_weight_t(in_features: int, out_features: int):
+    """(out_features, in_features) bf16 on the GPU: the weight of `x @ W` held transposed."""
+    import torch
+    if _DEVICE_INIT is not None:
+        std, gen = _DEVICE_INIT
+        return (torch.randn((out_features, in_features), generator=gen, device="cuda") * std).to(torch.bfloat16)
+    std = np.sqrt(2.0 / (in_features + out_features))          # Xavier/Glorot as llama_layers.py:80-85
+    w = np.random.randn(in_features, out_features).astype(np.float32) * std
+    return torch.from_numpy(np.ascontiguousarray(w.T)).cuda().to(torch.bfloat16)
+
+
 class GroupedQueryAttentionBF16:
     """The same layer on the bf16 tensor-core path, per-head grouped-query attention (BASELINE configs 2-4): the
     four projections are `bn_gemm_bf16_nt` (weights held transposed, (out_features, in_features), bf16), the core is
@@ -151,11 +185,7 @@ class GroupedQueryAttentionBF16:
         self.hidden_size = config.hidden_size
         kv = self.num_kv_heads * self.head_dim
 
-        def init(in_features, out_features):     # Xavier/Glorot as llama_layers.py:80-85, stored transposed
-            std = np.sqrt(2.0 / (in_features + out_features))
-            w = np.random.randn(in_features, out_features).astype(np.float32) * std
-            return torch.from_numpy(np.ascontiguousarray(w.T)).cuda().to(torch.bfloat16)
-
+        init = _init_weight_t
         self.q_proj, self.k_proj = init(self.hidden_size, self.hidden_size), init(self.hidden_size, kv)
         self.v_proj, self.o_proj = init(self.hidden_size, kv), init(self.hidden_size, self.hidden_size)
         self.rotary_emb = RotaryEmbedding(self.head_dim, max_position_embeddings=config.max_position_embeddings,
@@ -199,11 +229,7 @@ class MLPBF16:
         self.config = config
         hidden, inter = config.hidden_size, config.intermediate_size
 
-        def init(in_features, out_features):
-            std = np.sqrt(2.0 / (in_features + out_features))
-            w = np.random.randn(in_features, out_features).astype(np.float32) * std
-            return torch.from_numpy(np.ascontiguousarray(w.T)).cuda().to(torch.bfloat16)
-
+        init = _init_weight_t
         self.gate_proj, self.up_proj, self.down_proj = init(hidden, inter), init(hidden, inter), init(inter, hidden)
         self.intermediate_size = inter
         self._gate_up = ops.pack_gate_up(self.gate_proj, self.up_proj)

@@ -29,9 +29,8 @@ class LLaMAModelBF16:
             (np.random.randn(config.vocab_size, config.hidden_size) * 0.02).astype(np.float32)).cuda()
         self.layers = [LLaMADecoderLayerBF16(config) for _ in range(config.num_hidden_layers)]
         self.norm_weight = torch.ones(config.hidden_size, dtype=torch.bfloat16, device="cuda")
-        std = np.sqrt(2.0 / (config.hidden_size + config.vocab_size))
-        w = np.random.randn(config.hidden_size, config.vocab_size).astype(np.float32) * std
-        self.lm_head = torch.from_numpy(np.ascontiguousarray(w.T)).cuda().to(torch.bfloat16)    # (vocab, hidden)
+        from .layers import _init_weight_t
+        self.lm_head = _init_weight_t(config.hidden_size, config.vocab_size)                    # (vocab, hidden)
         self.caches: Optional[List[PagedKVCache]] = None
 
     # ------------------------------------------------------------------ pieces

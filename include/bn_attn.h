@@ -287,6 +287,34 @@ BN_API int bn_attn_lse_combine_strided(const float* outs, int64_t outs_part_stri
                                        int64_t lses_part_stride, int P, int64_t n, int D, float* out_f32,
                                        void* out_bf16, float* lse, bn_stream_t stream);
 
+/* ------------------------------------------------------------------------
+ * Exchange + merge over peer memory (sequence split across the GPUs of a node)
+ * ------------------------------------------------------------------------
+ * The merge of bn_attn_lse_combine with the exchange in the same launch: every rank stores its partial (n rows of D
+ * outputs, then n log-sum-exps: the layout the decode kernel writes when out_f32 and lse point into one buffer)
+ * into every rank's exchange buffer with plain peer stores, waits (bounded) for the others' and merges in rank
+ * order, so all ranks end with identical results.  No counterpart in the reference, which is single-GPU.
+ *
+ *   bn_exchange_create       one per rank (allocates the buffer: 2 * world * n * (D + 1) floats + 512 bytes);
+ *   bn_exchange_ipc_handle   64 bytes that name the buffer to the other processes of the node; the caller gathers
+ *                            the handles of all ranks (rank order) with whatever transport it has;
+ *   bn_exchange_open_peers   maps the other ranks' buffers (handles = world * 64 bytes); loopback != 0 instead keeps
+ *                            everything in this process (world 1, or a test that lets a wait run out);
+ *   bn_exchange_combine      one launch per step on every rank, in the same order on all of them; wait_us bounds the
+ *                            wait for the slowest rank (0 = one second);
+ *   bn_exchange_status       synchronises `stream`; BN_ERR_TIMEOUT if a wait ran out (the exchange must then be
+ *                            destroyed: the ranks are out of step);
+ *   bn_exchange_destroy      unmaps and frees.
+ * n * (D + 1) must be a multiple of 4; world <= 16. */
+typedef struct bn_exchange bn_exchange_t;
+BN_API int bn_exchange_create(int n, int D, int world, int rank, bn_exchange_t** out);
+BN_API int bn_exchange_ipc_handle(bn_exchange_t* x, void* handle64);
+BN_API int bn_exchange_open_peers(bn_exchange_t* x, const void* handles, int loopback);
+BN_API int bn_exchange_combine(bn_exchange_t* x, const float* partial, float* out, float* lse, unsigned wait_us,
+                               bn_stream_t stream);
+BN_API int bn_exchange_status(bn_exchange_t* x, bn_stream_t stream);
+BN_API void bn_exchange_destroy(bn_exchange_t* x);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,119 @@
+"""The peer-memory exchange + merge kernel (bn_exchange_*), through the C ABI.
+
+One GPU is enough for two of its properties: a single-rank exchange must reproduce the plain merge over many steps
+(counters, the two alternating slot sets), and a wait for a rank that never delivers must END with BN_ERR_TIMEOUT and
+leave the context usable (the failure is made by a counter that nothing advances - no fault, trap or endless loop).
+The two-rank run over real peer memory needs two GPUs and is skipped without them."""
+import ctypes as C
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _make(lib, n, D, world, rank, loopback):
+    from baranet_bdml_b200 import _lib
+    h = C.c_void_p()
+    _lib.check(lib.bn_exchange_create(n, D, world, rank, C.byref(h)))
+    _lib.check(lib.bn_exchange_open_peers(h, None, loopback))
+    return h
+
+
+def test_single_rank_exchange_reproduces_its_partial_over_many_steps(lib):
+    from baranet_bdml_b200 import _lib
+    n, D = 128, 64
+    h = _make(lib, n, D, 1, 0, 1)
+    out = torch.empty((n, D), device="cuda")
+    lse = torch.empty((n,), device="cuda")
+    for step in range(7):
+        part = torch.randn(n * (D + 1), device="cuda")
+        _lib.check(lib.bn_exchange_combine(h, part.data_ptr(), out.data_ptr(), lse.data_ptr(), 0, None))
+        torch.cuda.synchronize()
+        assert lib.bn_exchange_status(h, None) == _lib.BN_OK
+        assert torch.equal(out, part[: n * D].view(n, D))          # one part: weight exp(l - l) / 1 = 1 exactly
+        assert torch.allclose(lse, part[n * D:], rtol=0, atol=1e-6)
+    lib.bn_exchange_destroy(h)
+
+
+def test_a_rank_that_never_delivers_ends_in_a_timeout_status(lib):
+    from baranet_bdml_b200 import _lib
+    n, D = 128, 64
+    h = _make(lib, n, D, 2, 0, 1)        # world 2 inside one process: the counter of rank 1 is never advanced
+    out = torch.zeros((n, D), device="cuda")
+    part = torch.randn(n * (D + 1), device="cuda")
+    _lib.check(lib.bn_exchange_combine(h, part.data_ptr(), out.data_ptr(), None, 2000, None))     # 2 ms
+    assert lib.bn_exchange_status(h, None) == _lib.BN_ERR_TIMEOUT
+    assert "did not deliver" in _lib.last_error()
+    lib.bn_exchange_destroy(h)
+    # the context is intact: an ordinary exchange still works
+    h = _make(lib, n, D, 1, 0, 1)
+    _lib.check(lib.bn_exchange_combine(h, part.data_ptr(), out.data_ptr(), None, 0, None))
+    torch.cuda.synchronize()
+    assert lib.bn_exchange_status(h, None) == _lib.BN_OK
+    assert torch.equal(out, part[: n * D].view(n, D))
+    lib.bn_exchange_destroy(h)
+
+
+def test_bad_arguments(lib):
+    from baranet_bdml_b200 import _lib
+    h = C.c_void_p()
+    assert lib.bn_exchange_create(3, 64, 1, 0, C.byref(h)) == _lib.BN_ERR_UNSUPPORTED     # 3 * 65 not a multiple of 4
+    assert lib.bn_exchange_create(128, 64, 17, 0, C.byref(h)) == _lib.BN_ERR_INVALID_ARG
+    assert lib.bn_exchange_create(128, 64, 2, 2, C.byref(h)) == _lib.BN_ERR_INVALID_ARG
+
+
+WORKER = r"""
+import os, sys
+sys.path.insert(0, os.environ["BN_ROOT"])
+import torch, torch.distributed as dist
+from baranet_bdml_b200 import dist as bdist
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+n, D = 128, 64
+peer = bdist.PartialExchange(n, D, mode="peer")
+ref = bdist.PartialExchange(n, D, mode="nccl")
+if peer._peer is None:
+    print("nopeer", peer.kind)
+    dist.destroy_process_group()
+    sys.exit(0)
+g = torch.Generator(device="cuda").manual_seed(100 + rank)
+for step in range(9):
+    part = torch.randn(n * (D + 1), generator=g, device="cuda")
+    if step == 3 and rank == 1:
+        part[n * D:] = float("-inf")          # a rank that holds no token of any row
+    peer.send.copy_(part); ref.send.copy_(part)
+    o1, l1 = peer.combine()
+    o2, l2 = ref.combine()
+    torch.cuda.synchronize()
+    peer.status()
+    assert torch.allclose(o1, o2, rtol=0, atol=1e-5), (step, float((o1 - o2).abs().max()))
+    assert torch.allclose(l1, l2, rtol=0, atol=1e-5)
+    mine = o1.clone(); dist.broadcast(mine, 0)
+    assert torch.equal(mine, o1)              # the same bits on every rank
+peer.close()
+dist.destroy_process_group()
+print("ok", rank)
+"""
+
+
+def test_two_ranks_over_peer_memory_match_the_all_gather_path(lib, tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, BN_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29531", str(script)], env=env,
+                         capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout[-1500:] + res.stderr[-3000:]
+    if "nopeer" in res.stdout:
+        pytest.skip("peer mapping unavailable here: " + res.stdout.strip().splitlines()[-1])
+    assert res.stdout.count("ok") == 2
