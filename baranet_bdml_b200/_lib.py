@@ -49,6 +49,7 @@ SIGNATURES = {
     "bn_attn_lse_combine": (_i, [_p, _p, _i, _i64, _i, _p, _p, _p, _p]),
     "bn_attn_lse_combine_strided": (_i, [_p, _i64, _p, _i64, _i, _i64, _i, _p, _p, _p, _p]),
     "bn_workspace_status": (_i, [_p, _p]),
+    "bn_selftest_wait_timeout": (_i, [_p, C.c_uint, _p]),
     "bn_exchange_create": (_i, [_i, _i, _i, _i, C.POINTER(_p)]),
     "bn_exchange_ipc_handle": (_i, [_p, _p]),
     "bn_exchange_open_peers": (_i, [_p, _p, _i]),

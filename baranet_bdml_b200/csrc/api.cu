@@ -3,6 +3,7 @@
 #include <cstdio>
 
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace bn {
 
@@ -41,6 +42,24 @@ int launch_status(const char* what) {
     return BN_OK;
 }
 
+// The bounded wait of every kernel here (ptx::mbar_wait), on a barrier that nothing ever arrives at: the wait gives
+// up after `limit_ns`, raises the CTA's abort flag, and the kernel stores BN_ERR_TIMEOUT in the error word at the
+// head of the scratch buffer and returns - the path a kernel takes when a producer never delivers.
+__global__ void wait_that_runs_out_kernel(int* error_word, unsigned long long limit_ns) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int s_abort;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(ptx::smem_u32(&bar), 1);
+        s_abort = 0;
+        ptx::fence_mbar_init();
+    }
+    __syncthreads();
+    // every warp waits; the first one whose limit expires raises the flag, the others leave on seeing it
+    const bool ok = ptx::mbar_wait(ptx::smem_u32(&bar), 0, &s_abort, limit_ns);
+    __syncthreads();
+    if (threadIdx.x == 0 && (!ok || s_abort)) atomicExch(error_word, BN_ERR_TIMEOUT);
+}
+
 }  // namespace bn
 
 extern "C" {
@@ -58,6 +77,15 @@ int bn_workspace_status(const void* workspace, bn_stream_t stream) {
     if (word == BN_ERR_TIMEOUT)
         return bn::fail(BN_ERR_TIMEOUT, "a bounded device-side wait ran out; the result is invalid");
     return BN_OK;
+}
+
+int bn_selftest_wait_timeout(void* workspace, unsigned limit_us, bn_stream_t stream) {
+    if (!workspace) return bn::fail(BN_ERR_INVALID_ARG, "bn_selftest_wait_timeout: null workspace");
+    if (limit_us == 0 || limit_us > 100000) return bn::fail(BN_ERR_INVALID_ARG, "bn_selftest_wait_timeout: limit of 1..100000 us");
+    if (int rc = bn::require_sm100()) return rc;
+    bn::wait_that_runs_out_kernel<<<2, 128, 0, bn::as_stream(stream)>>>(static_cast<int*>(workspace),
+                                                                        (unsigned long long)limit_us * 1000ull);
+    return bn::launch_status("bn_selftest_wait_timeout");
 }
 
 }  // extern "C"

@@ -100,7 +100,8 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 // other waiter of the CTA leaves too and the kernel can return.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          uint64_t limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     uint64_t t0 = 0;
     for (uint32_t it = 1;; ++it) {
@@ -109,7 +110,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (*abort_flag) return false;
             uint64_t now = globaltimer_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
+            else if (now - t0 > limit_ns) { *abort_flag = 1; return false; }
         }
     }
 }

@@ -50,21 +50,41 @@ def sequence_split_ranges(length: int, world: int, page_tokens: int = 16) -> Lis
     return out
 
 
+class ExchangeTimeout(RuntimeError):
+    """The exchange did not complete within its deadline: a rank never arrived."""
+
+
 def combine_partials(out_partial: torch.Tensor, lse_partial: torch.Tensor, group=None,
-                     merge: Optional[Callable] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+                     merge: Optional[Callable] = None, deadline_s: Optional[float] = None
+                     ) -> Tuple[torch.Tensor, torch.Tensor]:
     """out_partial (n, D) fp32 normalised over this rank's tokens, lse_partial (n,) fp32
     natural log (-inf when the rank holds no token of the row).  One all-gather, then every
     rank merges locally, so all ranks end with identical results.
 
     `merge(outs[P,n,D], lses[P,n]) -> (out, lse)` defaults to the CUDA kernel
-    (bn_attn_lse_combine); CPU-only tests of the exchange pass their own."""
+    (bn_attn_lse_combine); CPU-only tests of the exchange pass their own.
+    `deadline_s`: give up with ExchangeTimeout when the collective has not completed by then."""
     import torch.distributed as dist
     n, D = out_partial.shape
     packed = torch.cat([out_partial, lse_partial.reshape(n, 1)], dim=1).contiguous()
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     if world > 1:
         gathered = [torch.empty_like(packed) for _ in range(world)]
-        dist.all_gather(gathered, packed, group=group)
+        if deadline_s is None:
+            dist.all_gather(gathered, packed, group=group)
+        else:
+            # host deadline of our own, shorter than the process group's: the collective is started without blocking
+            # and polled; past the deadline the caller gets ExchangeTimeout (and should tear the group down: the
+            # collective that never completed leaves it unusable)
+            import time
+            work = dist.all_gather(gathered, packed, group=group, async_op=True)
+            t_end = time.monotonic() + float(deadline_s)
+            while not work.is_completed():
+                if time.monotonic() > t_end:
+                    raise ExchangeTimeout(f"exchange of partial results: no completion within {deadline_s} s "
+                                          f"(a rank did not arrive)")
+                time.sleep(0.001)
+            work.wait()
         allp = torch.stack(gathered)
     else:
         allp = packed[None]

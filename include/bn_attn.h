@@ -75,6 +75,12 @@ BN_API int bn_version(void);
  * zero-filled again before reuse. */
 BN_API int bn_workspace_status(const void* workspace, bn_stream_t stream);
 
+/* Self-test of that mechanism (no counterpart in the reference): launches a small kernel whose only wait is for a
+ * barrier that nothing arrives at, with a limit of limit_us microseconds (1..100000).  The wait gives up, the kernel
+ * stores BN_ERR_TIMEOUT in the error word at the head of `workspace` (any scratch buffer of this library, or 4
+ * zeroed bytes) and returns; bn_workspace_status then reports it.  The GPU is never hung or faulted by it. */
+BN_API int bn_selftest_wait_timeout(void* workspace, unsigned limit_us, bn_stream_t stream);
+
 /* ------------------------------------------------------------------------
  * fp32 path (bit-faithful to the reference's operator arithmetic)
  * ------------------------------------------------------------------------ */

@@ -106,3 +106,33 @@ def test_missing_rank_raises_instead_of_hanging(tmp_path):
     port = 31500 + (os.getpid() % 2000)
     mp.spawn(_missing_rank_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     assert "rank0.raised" in os.listdir(tmp_path)
+
+
+def _deadline_main(rank, world, port, tmp):
+    """Rank 1 is late (it arrives after rank 0's own deadline): rank 0 gets ExchangeTimeout after about its
+    deadline, long before the process group's timeout."""
+    sys.path.insert(0, ROOT)
+    import datetime
+    import time
+    import torch.distributed as dist
+    from baranet_bdml_b200.dist import ExchangeTimeout, combine_partials
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    if rank == 1:
+        time.sleep(4)
+        os._exit(0)
+    t0 = time.monotonic()
+    try:
+        combine_partials(torch.zeros(4, 8), torch.zeros(4), merge=lambda a, b: (a[0], b[0]), deadline_s=1.0)
+        name = "rank0.no_error"
+    except ExchangeTimeout:
+        name = "rank0.deadline_%d" % int(time.monotonic() - t0 < 3.0)
+    open(os.path.join(tmp, name), "w").close()
+    os._exit(0)
+
+
+def test_exchange_deadline_fires_before_the_group_timeout(tmp_path):
+    port = 33500 + (os.getpid() % 2000)
+    mp.spawn(_deadline_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert "rank0.deadline_1" in os.listdir(tmp_path)

@@ -76,3 +76,50 @@ def test_model_rejects_bad_ids(lib):
     model = tiny_model()
     with pytest.raises(IndexError):
         model.embed(torch.tensor([5, 1000], dtype=torch.int32, device="cuda"))
+
+
+def test_model_logits_against_staged_fp64(lib):
+    """The model's whole-sequence forward (teacher-forced logits of a 2-layer reduced TinyLLaMA: embedding gather,
+    two blocks with the deferred residual add, final norm, lm_head) against an fp64 restatement assembled from the
+    oracle's pieces, with a bf16 rounding wherever a kernel rounds - the model's own plumbing (casts, the pending
+    residual, the last-position slice of prefill) checked against something that is not the model."""
+    from oracle import ref_attention as R
+    model = tiny_model(7)
+    cfg = model.config
+    rng = np.random.default_rng(8)
+    B, S = 2, 70
+    ids_np = rng.integers(0, cfg.vocab_size, (B, S)).astype(np.int32)
+    ids = torch.from_numpy(ids_np).cuda()
+    got = model(ids).float().cpu().numpy()                              # (B, S, vocab)
+    got_last = model.prefill(ids, S + 4).float().cpu().numpy()          # prompt pass: last position only
+
+    rb = lambda a: R.round_bf16(np.asarray(a, dtype=np.float32)).astype(np.float64)
+    f64 = lambda t: t.float().cpu().numpy().astype(np.float64)
+    table = f64(model.embed_tokens)
+    Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+
+    def norm(s, w):
+        return rb(s / np.sqrt((s * s).mean(axis=1, keepdims=True) + cfg.rms_norm_eps) * w)
+
+    for b in range(B):
+        h = rb(table[ids_np[b]])                                        # gather (fp32 rows), cast to bf16
+        pending = None
+        for layer in model.layers:
+            at, ml = layer.self_attn, layer.mlp
+            s0 = h if pending is None else rb(h + pending)              # the fused add of the previous block's MLP output
+            n1 = norm(s0, f64(layer.input_layernorm_weight))
+            q, k, v = rb(n1 @ f64(at.q_proj).T), rb(n1 @ f64(at.k_proj).T), rb(n1 @ f64(at.v_proj).T)
+            attn = rb(R.attention_per_head(q, k, v, num_heads=Hq, num_kv_heads=Hkv, head_dim=D, causal=True,
+                                           dtype=np.float64, round_rope_bf16=True))
+            s1 = rb(s0 + rb(attn @ f64(at.o_proj).T))
+            n2 = norm(s1, f64(layer.post_attention_layernorm_weight))
+            g, u = n2 @ f64(ml.gate_proj).T, n2 @ f64(ml.up_proj).T
+            pending = rb(rb(g / (1.0 + np.exp(-g)) * u) @ f64(ml.down_proj).T)
+            h = s1
+        final = norm(rb(h + pending), f64(model.norm_weight))
+        ref = rb(final @ f64(model.lm_head).T)                          # logits leave the GEMM as bf16
+        scale = np.abs(ref).max()
+        err = np.abs(got[b] - ref).max()
+        # two blocks of the decoder-layer gate (2e-2 + two bf16 ulps each) carried through a norm and one more GEMM
+        assert err <= 3e-2 * scale, (b, err, scale)
+        assert np.abs(got_last[b] - ref[-1]).max() <= 3e-2 * scale
