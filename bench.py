@@ -358,6 +358,40 @@ def measure_prefill(torch, ops, args, rank, world, dist, reduce_max, pk):
         ms_e2e = reduce_max(e0.elapsed_time(e1) / args.steps)
         h2d = (hq.numel() + hk.numel() + hv.numel()) * 2
         d2h = ho.numel() * 2
+        # the floor of that number: the same bytes moved by plain copies with no kernel at all (H2D of q, k, v on one
+        # stream, D2H of an output-sized buffer on another, every rank at once) - one cudaMemcpyAsync per tensor
+        dq, dk, dv, do_ = (torch.empty_like(t, device="cuda") for t in (hq, hk, hv, ho))
+        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+
+        def copies(steps):
+            for _ in range(steps):
+                with torch.cuda.stream(s_in):
+                    dq.copy_(hq, non_blocking=True)
+                    dk.copy_(hk, non_blocking=True)
+                    dv.copy_(hv, non_blocking=True)
+                with torch.cuda.stream(s_out):
+                    ho.copy_(do_, non_blocking=True)
+            torch.cuda.current_stream().wait_stream(s_in)
+            torch.cuda.current_stream().wait_stream(s_out)
+
+        copies(3)
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s_in.wait_stream(torch.cuda.current_stream())
+        s_out.wait_stream(torch.cuda.current_stream())
+        c0.record()
+        s_in.wait_stream(torch.cuda.current_stream())
+        s_out.wait_stream(torch.cuda.current_stream())
+        copies(args.steps)
+        c1.record()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        ms_copies = reduce_max(c0.elapsed_time(c1) / args.steps)
+        del dq, dk, dv, do_
 
     flops = prefill_flops()
     ach = flops / (ms_kernel * 1e-3) / 1e12
@@ -400,6 +434,9 @@ def measure_prefill(torch, ops, args, rank, world, dist, reduce_max, pk):
         "e2e": None if ms_e2e is None else {
             "value": flops * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
             "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e,
+            "copies_only_ms_per_step": ms_copies, "fraction_of_copies_only": ms_copies / ms_e2e,
+            "copies_only_note": "the same H2D + D2H bytes per step as plain concurrent copies on every rank, no kernel: "
+                                "the floor that the host links set for this number",
             "api": "ops.HostPrefillPipeline.submit per step (pinned host q/k/v/out; H2D, kernels and D2H of "
                    "neighbouring steps overlap on three streams over two device buffer sets)"},
         "gpu_launches": 2 * args.steps,
@@ -455,6 +492,23 @@ def measure_decode(torch, args, rank, world, dist, reduce_max, pk):
     ms_dec = reduce_max(ms_own)
     per_rank = _all_ranks(torch, dist, ms_own)
     per_rank_bytes = _all_ranks(torch, dist, float(bytes_alg))
+    # the same launches replayed from a CUDA graph (what a serving loop does; no host work between the launches)
+    ms_graph = None
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for i in range(dsets):
+                dstep(i)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(dsets):
+                dstep(i)
+        ms_graph = reduce_max(time_loop(torch, lambda i: graph.replay(), max(4, dsteps // dsets), 3, dist)) / dsets
+        del graph
+    except Exception as e:
+        ms_graph = None
     for cch in caches:
         cch.status()
     gbs = bytes_alg / (ms_dec * 1e-3) / 1e9
@@ -470,6 +524,8 @@ def measure_decode(torch, args, rank, world, dist, reduce_max, pk):
                      "traffic_unit": "bytes of DRAM traffic per launch (ncu capture, profiles/decode_paged_kernel_config3.md)",
                      "peak_source": pk["source"], "kernel": "decode_paged_kernel"},
         "ms_per_step_by_rank": per_rank,
+        "ms_per_step_cuda_graph": ms_graph,
+        "gbs_cuda_graph": None if not ms_graph else bytes_alg / (ms_graph * 1e-3) / 1e9,
         "gpu_launches": dsteps,
     }
     del caches
@@ -997,10 +1053,11 @@ def run_ours(args):
                 result["decoder_layer"] = measure_decoder_layer(torch, args, rank, world, dist, reduce_max, pk)
             except Exception as e:
                 result["decoder_layer"] = {"error": repr(e)}
-            try:
-                result["generate"] = measure_generate(torch, args, rank, world, dist, reduce_max, pk)
-            except Exception as e:
-                result["generate"] = {"error": repr(e)}
+            if not args.no_generate:
+                try:
+                    result["generate"] = measure_generate(torch, args, rank, world, dist, reduce_max, pk)
+                except Exception as e:
+                    result["generate"] = {"error": repr(e)}
             if rank == 0 and world == 1:
                 try:
                     result["layer_f32"] = measure_layer_f32(torch, args, rank, world, pk)
@@ -1028,6 +1085,7 @@ def run_ours(args):
             "prefill_sharded_tflops": pick(result, "sharded", "value"),
             "decode_gbs": pick(result, "decode", "value"), "decode_ms": pick(result, "decode", "ms_per_step"),
             "decode_frac": pick(result, "decode", "roofline", "frac"),
+            "decode_gbs_per_gpu_cuda_graph": pick(result, "decode", "gbs_cuda_graph"),
             "decode_sharded_gbs": pick(result, "decode", "sharded", "value"),
             "decode_sharded_ms": pick(result, "decode", "sharded", "ms_per_step"),
             "decode_long_gbs": pick(result, "decode_long", "value"), "decode_long_ms": pick(result, "decode_long", "ms_per_step"),
@@ -1063,6 +1121,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end measurement")
     ap.add_argument("--no-decode", action="store_true", help="skip the config-3 decode measurement")
+    ap.add_argument("--no-generate", action="store_true", help="skip the config-5 generation measurement")
     ap.add_argument("--decode-only", action="store_true",
                     help="run only the decode measurement (for profiling); prints its object alone")
     args = ap.parse_args()
