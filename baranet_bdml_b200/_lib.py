@@ -40,6 +40,8 @@ SIGNATURES = {
                                  _i, _i, _i, _i, _f, _f, _i, _i, _i, _i, _p]),
     "bn_attn_prefill_bf16_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "bn_attn_prefill_bf16": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _f, _i, _i, _i, _p, _sz, _p]),
+    "bn_attn_prefill_bf16_table": (_i, [_i, _i, _i, _i, _f, _i, _p, _sz, _p]),
+    "bn_gemm_qkv_rope_bf16": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _sz, _p, _i64, _p, _i, _p, _p]),
     "bn_kv_append": (_i, [_p, _i64, _p, _i, _p, _p, _i, _p, _p, _i64, _i, _i, _i, _f, _p]),
     "bn_attn_decode_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i]),
     "bn_attn_decode_paged": (_i, [_p, _p, _i64, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _f, _i, _i, _i,

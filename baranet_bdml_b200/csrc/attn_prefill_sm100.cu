@@ -62,6 +62,22 @@ static PrefillWsLayout prefill_layout(int B, int S, int Hkv) {
     return L;
 }
 
+void prefill_bf16_workspace_layout(int B, int S, int Hkv, size_t* table, size_t* kmax2, size_t* krot, size_t* total) {
+    const PrefillWsLayout L = prefill_layout(B, S, Hkv);
+    *table = L.table; *kmax2 = L.kmax2; *krot = L.krot; *total = L.total;
+}
+
+// the cos/sin table alone (for a caller that produces the rotated K itself): [S][32] of position s + position_offset
+__global__ void __launch_bounds__(256)
+rope_table_kernel(float2* __restrict__ table, int S, float theta, int position_offset, int* __restrict__ error_word) {
+    const int idx = blockIdx.x * 256 + threadIdx.x;
+    if (idx == 0) *error_word = 0;
+    if (idx >= S * (PF_D / 2)) return;
+    const int s = idx / (PF_D / 2), i = idx % (PF_D / 2);
+    const float angle = (s + position_offset) * rope_inv_freq(i, PF_D, theta);
+    table[idx] = make_float2(cosf(angle), sinf(angle));
+}
+
 // ---------------------------------------------------------------------------
 // launch 1: K rotation + cos/sin table
 // ---------------------------------------------------------------------------
@@ -1154,11 +1170,30 @@ extern "C" size_t bn_attn_prefill_bf16_workspace_bytes(int B, int S, int Hq, int
     return prefill_layout(B, S, Hkv).total;
 }
 
+extern "C" int bn_attn_prefill_bf16_table(int B, int S, int Hkv, int D, float theta, int position_offset, void* workspace,
+                                          size_t workspace_bytes, bn_stream_t stream) {
+    if (B <= 0 || S <= 0 || Hkv <= 0 || position_offset < 0)
+        return fail(BN_ERR_INVALID_ARG, "bn_attn_prefill_bf16_table: bad shape B=%d S=%d Hkv=%d", B, S, Hkv);
+    if (D != PF_D) return fail(BN_ERR_UNSUPPORTED, "bn_attn_prefill_bf16_table: head_dim=%d (64 supported)", D);
+    const PrefillWsLayout L = prefill_layout(B, S, Hkv);
+    if (!workspace || workspace_bytes < L.total)
+        return fail(BN_ERR_WORKSPACE, "bn_attn_prefill_bf16_table: workspace of %zu bytes given, %zu needed", workspace_bytes,
+                    L.total);
+    if (reinterpret_cast<uintptr_t>(workspace) & 255)
+        return fail(BN_ERR_INVALID_ARG, "bn_attn_prefill_bf16_table: workspace must be 256-byte aligned");
+    if (int rc = require_sm100()) return rc;
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    rope_table_kernel<<<(S * (PF_D / 2) + 255) / 256, 256, 0, as_stream(stream)>>>(
+        reinterpret_cast<float2*>(ws + L.table), S, theta, position_offset, reinterpret_cast<int*>(ws));
+    return launch_status("bn_attn_prefill_bf16_table");
+}
+
 extern "C" int bn_attn_prefill_bf16(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S,
                                     int Hq, int Hkv, int D, float scale, float theta, int position_offset,
                                     int causal, int flags, void* workspace, size_t workspace_bytes,
                                     bn_stream_t stream) {
-    if (!q || !k || !v || !out) return fail(BN_ERR_INVALID_ARG, "bn_attn_prefill_bf16: null pointer");
+    if (!q || !v || !out || (!k && !(flags & BN_PREFILL_REUSE_ROTATED_K)))
+        return fail(BN_ERR_INVALID_ARG, "bn_attn_prefill_bf16: null pointer");
     if (B < 0 || S < 0 || Hq <= 0 || Hkv <= 0)
         return fail(BN_ERR_INVALID_ARG, "bn_attn_prefill_bf16: bad shape B=%d S=%d Hq=%d Hkv=%d", B, S, Hq, Hkv);
     if (Hq % Hkv != 0) return fail(BN_ERR_INVALID_ARG, "bn_attn_prefill_bf16: Hq=%d not a multiple of Hkv=%d", Hq, Hkv);
@@ -1166,7 +1201,7 @@ extern "C" int bn_attn_prefill_bf16(const void* q, const void* k, const void* v,
     if (position_offset < 0) return fail(BN_ERR_INVALID_ARG, "bn_attn_prefill_bf16: position_offset=%d < 0", position_offset);
     if (flags & ~(BN_PREFILL_REUSE_ROTATED_K | BN_PREFILL_SINGLE_TILE_KERNEL))
         return fail(BN_ERR_UNSUPPORTED, "bn_attn_prefill_bf16: flags=0x%x not understood", flags);
-    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+    if ((reinterpret_cast<uintptr_t>(q) | (k ? reinterpret_cast<uintptr_t>(k) : 0) | reinterpret_cast<uintptr_t>(v) |
          reinterpret_cast<uintptr_t>(out)) & 15)
         return fail(BN_ERR_INVALID_ARG, "bn_attn_prefill_bf16: q/k/v/out must be 16-byte aligned");
     if (int rc = require_sm100()) return rc;

@@ -24,6 +24,10 @@ inline cudaStream_t as_stream(bn_stream_t s) { return reinterpret_cast<cudaStrea
 
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+// Byte offsets inside the scratch buffer of bn_attn_prefill_bf16 (cos/sin table, per-tile key norms, rotated K) and
+// its size: the fused q/k/v projection writes the last two itself.
+void prefill_bf16_workspace_layout(int B, int S, int Hkv, size_t* table, size_t* kmax2, size_t* krot, size_t* total);
+
 // The RoPE frequency of pair i, with the reference's exact arithmetic
 // (src/ops/op_rope.cuh:82): fp32 exponent, fp32 pow, reciprocal taken in
 // double, rounded to fp32.

@@ -39,6 +39,22 @@ template <int BN> struct GemmShape {
     static constexpr uint32_t TMEM_COLS = 2 * BN;
 };
 
+// EPI_QKV: the q, k and v projections of the layer as ONE product with the concatenated weight; the epilogue sends
+// each 32-column piece where it belongs (below)
+struct QkvEpilogue {
+    __nv_bfloat16* q;            // (tokens, NQ) as projected (the attention kernel rotates Q itself)
+    __nv_bfloat16* krot;         // (tokens, NK) rotated K, the attention kernel's operand
+    __nv_bfloat16* v;            // (tokens, NK)
+    const float2* table;         // [S][32] cos/sin of position s + position_offset
+    int* kmax2;                  // [B][Hkv][key tiles of 128]: largest |rotated k|^2 as float bits (atomic max)
+    __nv_bfloat16* pool;         // paged cache (may be null): pool[page][kv_head][K|V][16][64]
+    const int32_t* page_table;   // (B, max_pages)
+    long long pool_pages;
+    int max_pages, S, NQ, NK, Hkv, n_ktiles, position_offset;
+};
+
+constexpr int EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_PARTIAL = 2, EPI_QKV = 3;
+
 struct GemmParams {
     __nv_bfloat16* c;
     int* error_word;       // optional
@@ -46,9 +62,10 @@ struct GemmParams {
     int n_out;             // columns of C: N (plain) or the intermediate size (SwiGLU)
     float* partial;        // EPI_PARTIAL: [split][M][N] fp32
     int splits, k_per_split;   // EPI_PARTIAL: K steps are cut into `splits` ranges of k_per_split steps
+    QkvEpilogue qkv;       // EPI_QKV
 };
 
-constexpr int EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_PARTIAL = 2;
+
 
 template <int EPI, int GM_BN>
 __global__ void __launch_bounds__(GM_THREADS, 1)
@@ -187,6 +204,102 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         }
                     }
                 }
+            } else if (EPI == EPI_QKV) {
+                // Columns [0, NQ) are Q: written as they are.  [NQ, NQ + NK) are K: rotated at the row's position
+                // (pairs (2i, 2i+1) of each 64-wide head, src/ops/op_rope.cuh:55-99, from the fp32 accumulators:
+                // one rounding instead of two), written as the attention kernel's K operand AND into the row's page
+                // of the cache, with the largest squared norm per (sequence, KV head, 128-key tile) kept for that
+                // kernel's bound on the scores.  The rest is V: written to the V operand and into the cache.
+                // A 32-column piece is half a head, so a piece never straddles two of these regions or two heads.
+                const QkvEpilogue& e = p.qkv;
+                const bool live = gm < p.M;
+                const int b = live ? gm / e.S : 0, srow = live ? gm - b * e.S : 0;
+                const int pos = srow + e.position_offset;
+                long long page = -1;
+                if (e.pool && live && n0 + GM_BN > e.NQ) {
+                    const int lp = pos / BN_PAGE_TOKENS;
+                    if (lp < e.max_pages) page = e.page_table[(size_t)b * e.max_pages + lp];
+                    if (page >= e.pool_pages) page = -1;
+                }
+                const int slot = pos % BN_PAGE_TOKENS;
+                const int key = live ? b * e.n_ktiles + srow / 128 : -1;         // which norm slot this row feeds
+                const bool same_key = __all_sync(0xffffffffu, key == __shfl_sync(0xffffffffu, key, 0) && key >= 0);
+                float head_n2 = 0.f;
+#pragma unroll 1
+                for (int c = 0; c < GM_BN / 32; ++c) {
+                    uint32_t r[32];
+                    tc::ld32(tmem + lane_base + acc * GM_BN + c * 32, r);
+                    tc::wait_ld(r);
+                    const int col = n0 + c * 32;
+                    if (col >= p.N) continue;                 // (uniform) beyond the concatenated weight
+                    uint4 o4[4];
+                    if (col < e.NQ || col >= e.NQ + e.NK) {   // Q or V: plain rounding
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            o4[v].x = pack_bf16(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+                            o4[v].y = pack_bf16(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+                            o4[v].z = pack_bf16(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+                            o4[v].w = pack_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+                        }
+                        if (live) {
+                            if (col < e.NQ) {
+                                uint4* dst = reinterpret_cast<uint4*>(e.q + (size_t)gm * e.NQ + col);
+#pragma unroll
+                                for (int v = 0; v < 4; ++v) dst[v] = o4[v];
+                            } else {
+                                const int vc = col - e.NQ - e.NK;
+                                uint4* dst = reinterpret_cast<uint4*>(e.v + (size_t)gm * e.NK + vc);
+#pragma unroll
+                                for (int v = 0; v < 4; ++v) dst[v] = o4[v];
+                                if (page >= 0) {
+                                    uint4* pd = reinterpret_cast<uint4*>(
+                                        e.pool + (((page * e.Hkv + vc / 64) * 2 + 1) * BN_PAGE_TOKENS + slot) * 64 + vc % 64);
+#pragma unroll
+                                    for (int v = 0; v < 4; ++v) pd[v] = o4[v];
+                                }
+                            }
+                        }
+                    } else {                                   // K: rotate, round, norms
+                        const int kc = col - e.NQ;             // column inside K; kc % 64 is 0 or 32
+                        const float2* cs = e.table + (size_t)srow * 32 + (kc % 64) / 2;
+                        uint32_t w[16];
+                        float n2 = 0.f;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const float2 t2 = live ? __ldg(cs + i) : make_float2(1.f, 0.f);
+                            const float x0 = __uint_as_float(r[2 * i]), x1 = __uint_as_float(r[2 * i + 1]);
+                            w[i] = pack_bf16(x0 * t2.x - x1 * t2.y, x0 * t2.y + x1 * t2.x);
+                            const float y0 = bf16_lo(w[i]), y1 = bf16_hi(w[i]);
+                            n2 = fmaf(y0, y0, fmaf(y1, y1, n2));
+                        }
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) o4[v] = make_uint4(w[v * 4], w[v * 4 + 1], w[v * 4 + 2], w[v * 4 + 3]);
+                        if (live) {
+                            uint4* dst = reinterpret_cast<uint4*>(e.krot + (size_t)gm * e.NK + kc);
+#pragma unroll
+                            for (int v = 0; v < 4; ++v) dst[v] = o4[v];
+                            if (page >= 0) {
+                                uint4* pd = reinterpret_cast<uint4*>(
+                                    e.pool + (((page * e.Hkv + kc / 64) * 2 + 0) * BN_PAGE_TOKENS + slot) * 64 + kc % 64);
+#pragma unroll
+                                for (int v = 0; v < 4; ++v) pd[v] = o4[v];
+                            }
+                        }
+                        head_n2 += n2;
+                        if (kc % 64) {                         // second half of the head: its norm is complete
+                            // a NaN or an infinity must read as "unbounded": their bit patterns are above every finite float's
+                            int bits = live ? (head_n2 == head_n2 ? __float_as_int(head_n2) : 0x7fffffff) : 0;
+                            const int hh = kc / 64;
+                            if (same_key) {
+                                bits = __reduce_max_sync(0xffffffffu, bits);
+                                if (lane == 0) atomicMax(e.kmax2 + ((size_t)b * e.Hkv + hh) * e.n_ktiles + srow / 128, bits);
+                            } else if (live) {
+                                atomicMax(e.kmax2 + ((size_t)b * e.Hkv + hh) * e.n_ktiles + srow / 128, bits);
+                            }
+                            head_n2 = 0.f;
+                        }
+                    }
+                }
             } else if (EPI == EPI_PARTIAL) {
                 // the fp32 partial sum of this K range; the ranges are added in order by the reduce kernel
                 float* prow = p.partial + ((size_t)(t / (tiles_m * tiles_n)) * p.M + gm) * p.N + n0;
@@ -301,7 +414,7 @@ static int gemm_configure(int dev) {
 
 static int gemm_launch(const void* a, const void* bt, void* c, int M, int N, int K, int n_out, int epi, int* error_word,
                        bn_stream_t stream, const char* what, float* partial = nullptr, int splits = 1,
-                       int k_per_split = 0) {
+                       int k_per_split = 0, const QkvEpilogue* qkv = nullptr) {
     if (!a || !bt || !c) return fail(BN_ERR_INVALID_ARG, "%s: null pointer", what);
     if (M < 0 || N < 0 || K < 0 || n_out < 0) return fail(BN_ERR_INVALID_ARG, "%s: bad shape M=%d N=%d K=%d", what, M, N, K);
     if (n_out % 8 || K % 8)
@@ -334,7 +447,8 @@ static int gemm_launch(const void* a, const void* bt, void* c, int M, int N, int
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const long long n_items = (long long)((M + GM_BM - 1) / GM_BM) * ((N + bn - 1) / bn) * splits;
-    GemmParams p{static_cast<__nv_bfloat16*>(c), error_word, M, N, K, n_out, partial, splits, k_per_split};
+    GemmParams p{static_cast<__nv_bfloat16*>(c), error_word, M, N, K, n_out, partial, splits, k_per_split, QkvEpilogue{}};
+    if (qkv) p.qkv = *qkv;
     const unsigned grid = (unsigned)(n_items < sms ? n_items : sms);
     cudaStream_t st = as_stream(stream);
     if (epi == EPI_PLAIN) {
@@ -343,6 +457,9 @@ static int gemm_launch(const void* a, const void* bt, void* c, int M, int N, int
     } else if (epi == EPI_SWIGLU) {
         if (int rc = gemm_configure<EPI_SWIGLU, 256>(dev)) return rc;
         gemm_bf16_nt_kernel<EPI_SWIGLU, 256><<<grid, GM_THREADS, GemmShape<256>::SMEM_BYTES, st>>>(tmap_a, tmap_b, p);
+    } else if (epi == EPI_QKV) {
+        if (int rc = gemm_configure<EPI_QKV, 256>(dev)) return rc;
+        gemm_bf16_nt_kernel<EPI_QKV, 256><<<grid, GM_THREADS, GemmShape<256>::SMEM_BYTES, st>>>(tmap_a, tmap_b, p);
     } else {
         if (int rc = gemm_configure<EPI_PARTIAL, 64>(dev)) return rc;
         gemm_bf16_nt_kernel<EPI_PARTIAL, 64><<<grid, GM_THREADS, GemmShape<64>::SMEM_BYTES, st>>>(tmap_a, tmap_b, p);
@@ -391,4 +508,43 @@ extern "C" int bn_gemm_bf16_nt_small_m(const void* a, const void* bt, void* c, i
                            static_cast<float*>(workspace), splits, per);
     }
     return gemm_launch(a, bt, c, M, N, K, N, EPI_PARTIAL, error_word, stream, "bn_gemm_bf16_nt_small_m");
+}
+
+extern "C" int bn_gemm_qkv_rope_bf16(const void* x, const void* wqkv_t, void* q_out, void* v_out, int B, int S, int hidden,
+                                     int Hq, int Hkv, int D, int position_offset, void* prefill_workspace,
+                                     size_t prefill_workspace_bytes, void* pool, int64_t pool_pages,
+                                     const int32_t* page_table, int max_pages, int* error_word, bn_stream_t stream) {
+    const char* what = "bn_gemm_qkv_rope_bf16";
+    if (!x || !wqkv_t || !q_out || !v_out || !prefill_workspace) return fail(BN_ERR_INVALID_ARG, "%s: null pointer", what);
+    if (B <= 0 || S <= 0 || Hq <= 0 || Hkv <= 0 || hidden <= 0 || position_offset < 0)
+        return fail(BN_ERR_INVALID_ARG, "%s: bad shape B=%d S=%d Hq=%d Hkv=%d hidden=%d", what, B, S, Hq, Hkv, hidden);
+    if (D != 64) return fail(BN_ERR_UNSUPPORTED, "%s: head_dim=%d (64 supported)", what, D);
+    if (pool && (!page_table || max_pages <= 0 || pool_pages <= 0))
+        return fail(BN_ERR_INVALID_ARG, "%s: a cache pool needs its page table", what);
+    if ((reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(v_out) | reinterpret_cast<uintptr_t>(pool)) & 15)
+        return fail(BN_ERR_INVALID_ARG, "%s: q/v/pool must be 16-byte aligned", what);
+    size_t off_table = 0, off_kmax2 = 0, off_krot = 0, total = 0;
+    prefill_bf16_workspace_layout(B, S, Hkv, &off_table, &off_kmax2, &off_krot, &total);
+    if (prefill_workspace_bytes < total)
+        return fail(BN_ERR_WORKSPACE, "%s: workspace of %zu bytes given, %zu needed (bn_attn_prefill_bf16_workspace_bytes)",
+                    what, prefill_workspace_bytes, total);
+    if (reinterpret_cast<uintptr_t>(prefill_workspace) & 255)
+        return fail(BN_ERR_INVALID_ARG, "%s: workspace must be 256-byte aligned", what);
+    uint8_t* ws = static_cast<uint8_t*>(prefill_workspace);
+    // the norm maxima are taken with atomics: clear them first (a few KB)
+    cudaError_t ce = cudaMemsetAsync(ws + off_kmax2, 0, off_krot - off_kmax2, as_stream(stream));
+    if (ce != cudaSuccess) return fail(BN_ERR_CUDA, "%s: cudaMemsetAsync: %s", what, cudaGetErrorString(ce));
+    QkvEpilogue e;
+    e.q = static_cast<__nv_bfloat16*>(q_out);
+    e.krot = reinterpret_cast<__nv_bfloat16*>(ws + off_krot);
+    e.v = static_cast<__nv_bfloat16*>(v_out);
+    e.table = reinterpret_cast<const float2*>(ws + off_table);
+    e.kmax2 = reinterpret_cast<int*>(ws + off_kmax2);
+    e.pool = static_cast<__nv_bfloat16*>(pool);
+    e.page_table = page_table;
+    e.pool_pages = pool_pages;
+    e.max_pages = max_pages;
+    e.S = S; e.NQ = Hq * D; e.NK = Hkv * D; e.Hkv = Hkv; e.n_ktiles = (S + 127) / 128; e.position_offset = position_offset;
+    const int N = (Hq + 2 * Hkv) * D;
+    return gemm_launch(x, wqkv_t, q_out, B * S, N, hidden, N, EPI_QKV, error_word, stream, what, nullptr, 1, 0, &e);
 }

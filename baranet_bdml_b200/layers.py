@@ -168,9 +168,10 @@ def _init_weight_t(in_features: int, out_features: int):
 
 
 class GroupedQueryAttentionBF16:
-    """The same layer on the bf16 tensor-core path, per-head grouped-query attention (BASELINE configs 2-4): the
-    four projections are `bn_gemm_bf16_nt` (weights held transposed, (out_features, in_features), bf16), the core is
-    `bn_attn_prefill_bf16` (RoPE, causal softmax, P V fused).  Same constructor arguments, attribute names and
+    """The same layer on the bf16 tensor-core path, per-head grouped-query attention (BASELINE configs 2-4): q, k and
+    v come from ONE tensor-core GEMM (`bn_gemm_qkv_rope_bf16`: weights held transposed, (out_features, in_features),
+    bf16; RoPE(K) in its epilogue), the core is `bn_attn_prefill_bf16` (RoPE(Q), causal softmax, P V fused), o_proj
+    is `bn_gemm_bf16_nt`: three kernel launches.  Same constructor arguments, attribute names and
     `__call__(hidden_states, position_offset, use_causal_mask)` as mygrad/llama/llama_layers.py:46-191;
     hidden_states is a torch bf16 tensor (B, S, hidden) or (S, hidden) on the GPU.  Inference only."""
 
@@ -188,10 +189,45 @@ class GroupedQueryAttentionBF16:
         init = _init_weight_t
         self.q_proj, self.k_proj = init(self.hidden_size, self.hidden_size), init(self.hidden_size, kv)
         self.v_proj, self.o_proj = init(self.hidden_size, kv), init(self.hidden_size, self.hidden_size)
+        self._qkv_t = None          # Wq^T, Wk^T, Wv^T stacked: built at the first fused call from the three above
+        self._ws_table = None       # (S, theta, position_offset) of the cos/sin table in the scratch buffer
         self.rotary_emb = RotaryEmbedding(self.head_dim, max_position_embeddings=config.max_position_embeddings,
                                           base=config.rope_theta)
         self.scale = 1.0 / np.sqrt(self.head_dim)
         self._ws = None
+
+    def packed_qkv(self):
+        """(Hq + 2 Hkv) * D rows: the three projection weights (held transposed) one after the other.  Rebuilt when
+        one of them has been replaced (they are plain attributes, as in the reference layer)."""
+        import torch
+        key = (self.q_proj.data_ptr(), self.k_proj.data_ptr(), self.v_proj.data_ptr())
+        if self._qkv_t is None or self._qkv_t[0] != key:
+            self._qkv_t = (key, torch.cat([self.q_proj, self.k_proj, self.v_proj], dim=0).contiguous())
+        return self._qkv_t[1]
+
+    def attend(self, x2, B: int, S: int, position_offset: int = 0, use_causal_mask: bool = True, cache=None,
+               workspace=None):
+        """x2 (B*S, hidden) bf16 -> attention output before o_proj, (B*S, hidden): ONE GEMM for q, k, v with the K
+        rotation (and, with `cache`, the append of K and V at positions position_offset ..) in its epilogue, then the
+        fused attention kernel on the rotated K it left in the scratch buffer.  head_dim 64.  A caller that passes
+        its own `workspace` keeps its cos/sin table current itself (ops.prefill_table)."""
+        from . import ops
+        if workspace is None:
+            key = (B, S)
+            if self._ws is None or self._ws[0] != key:
+                self._ws = (key, ops.prefill_workspace(B, S, self.num_heads, self.num_kv_heads, self.head_dim, x2.device))
+                self._ws_table = None
+            workspace = self._ws[1]
+            tkey = (S, float(self.rotary_emb.base), int(position_offset))
+            if self._ws_table != tkey:
+                ops.prefill_table(workspace, B, S, self.num_kv_heads, self.head_dim, self.rotary_emb.base, position_offset)
+                self._ws_table = tkey
+        q, v = ops.gemm_qkv_rope_bf16(x2, self.packed_qkv(), B, S, self.num_heads, self.num_kv_heads, self.head_dim,
+                                      workspace, position_offset=position_offset, cache=cache)
+        attn = ops.attn_prefill_bf16(q, None, v, scale=float(self.scale), theta=self.rotary_emb.base,
+                                     position_offset=position_offset, causal=use_causal_mask, workspace=workspace,
+                                     reuse_rotated_k=True)
+        return attn.view(B * S, self.num_heads * self.head_dim)
 
     def __call__(self, hidden_states, position_offset: int = 0, use_causal_mask: bool = True):
         from . import ops
@@ -199,16 +235,8 @@ class GroupedQueryAttentionBF16:
         B, S, H = x.shape
         if H != self.hidden_size:
             raise RuntimeError("Attention: hidden size mismatch")
-        x2 = x.reshape(B * S, H)
-        q = ops.gemm_bf16_nt(x2, self.q_proj).view(B, S, self.num_heads, self.head_dim)
-        k = ops.gemm_bf16_nt(x2, self.k_proj).view(B, S, self.num_kv_heads, self.head_dim)
-        v = ops.gemm_bf16_nt(x2, self.v_proj).view(B, S, self.num_kv_heads, self.head_dim)
-        key = (B, S)
-        if self._ws is None or self._ws[0] != key:
-            self._ws = (key, ops.prefill_workspace(B, S, self.num_heads, self.num_kv_heads, self.head_dim, x.device))
-        attn = ops.attn_prefill_bf16(q, k, v, scale=float(self.scale), theta=self.rotary_emb.base,
-                                     position_offset=position_offset, causal=use_causal_mask, workspace=self._ws[1])
-        out = ops.gemm_bf16_nt(attn.view(B * S, self.num_heads * self.head_dim), self.o_proj).view(B, S, H)
+        attn = self.attend(x.reshape(B * S, H), B, S, position_offset, use_causal_mask)
+        out = ops.gemm_bf16_nt(attn, self.o_proj).view(B, S, H)
         return out if hidden_states.dim() == 3 else out[0]
 
     def parameters(self):
@@ -247,9 +275,9 @@ class MLPBF16:
 
 class LLaMADecoderLayerBF16:
     """mygrad/llama/llama_layers.py:238-296 (pre-norm decoder block: input_layernorm -> self_attn -> residual add ->
-    post_attention_layernorm -> mlp -> residual add) on the bf16 tensor-core path, 10 launches per call:
-    norm, 3 projection GEMMs, K rotation, fused attention, o_proj GEMM, fused residual add + norm, fused gate/up GEMM,
-    down GEMM; the last residual add is returned un-added together with the MLP output by `forward_parts`, so that
+    post_attention_layernorm -> mlp -> residual add) on the bf16 tensor-core path, 7 kernel launches per call:
+    norm, fused q/k/v GEMM (K rotation in its epilogue), fused attention, o_proj GEMM, fused residual add + norm,
+    fused gate/up GEMM, down GEMM; the last residual add is returned un-added together with the MLP output by `forward_parts`, so that
     the NEXT layer's fused add + norm performs it (`__call__` adds it for a stand-alone layer).
     hidden_states: torch bf16 (B, S, hidden) on the GPU.  Inference only."""
 

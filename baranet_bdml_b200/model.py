@@ -86,24 +86,20 @@ class LLaMAModelBF16:
         B, S = input_ids.shape
         self._alloc_caches(B, max_len)
         h = self.embed(input_ids.reshape(-1)).view(B, S, -1)
-        seq_ids = torch.arange(B, dtype=torch.int32, device="cuda").repeat_interleave(S)
-        positions = torch.arange(S, dtype=torch.int32, device="cuda").repeat(B)
         pending = None
         H = cfg.hidden_size
+        # one scratch buffer for all blocks (they run one after the other): cos/sin table written once
+        ws = ops.prefill_workspace(B, S, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim)
+        ops.prefill_table(ws, B, S, cfg.num_key_value_heads, cfg.head_dim, cfg.rope_theta, 0)
         for layer, cache in zip(self.layers, self.caches):
             x2 = h.reshape(B * S, H)
             residual, normed = ops.add_rmsnorm_bf16(x2, None if pending is None else pending.reshape(B * S, H),
                                                     layer.input_layernorm_weight, layer.eps)
             at = layer.self_attn
-            q = ops.gemm_bf16_nt(normed, at.q_proj).view(B, S, at.num_heads, at.head_dim)
-            k = ops.gemm_bf16_nt(normed, at.k_proj)
-            v = ops.gemm_bf16_nt(normed, at.v_proj)
-            cache.append(seq_ids, positions, k, v)                # RoPE(K) + page write
+            # q/k/v in one GEMM whose epilogue rotates K and appends K and V to this block's cache
+            attn = at.attend(normed, B, S, 0, True, cache=cache, workspace=ws)
             cache.seq_lens.fill_(S)
-            attn = ops.attn_prefill_bf16(q, k.view(B, S, at.num_kv_heads, at.head_dim),
-                                         v.view(B, S, at.num_kv_heads, at.head_dim), scale=float(at.scale),
-                                         theta=at.rotary_emb.base, causal=True)
-            o = ops.gemm_bf16_nt(attn.view(B * S, H), at.o_proj)
+            o = ops.gemm_bf16_nt(attn, at.o_proj)
             residual, normed = ops.add_rmsnorm_bf16(residual, o, layer.post_attention_layernorm_weight, layer.eps)
             h, pending = residual.view(B, S, H), layer.mlp(normed).view(B, S, H)
         return self._logits(h[:, -1].contiguous(), pending[:, -1].contiguous())

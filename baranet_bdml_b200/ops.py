@@ -50,11 +50,14 @@ def attn_prefill_bf16(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scal
     `reuse_rotated_k`: the workspace still holds the rotated K of an earlier
     call on the same k and position_offset (skips the rotation launch).
     `single_tile_kernel` selects the simpler kernel variant kept for comparison."""
+    if k is None and not reuse_rotated_k:
+        raise RuntimeError("attn_prefill_bf16: k may only be omitted when the workspace already holds the rotated K")
     for t, n in ((q, "q"), (k, "k"), (v, "v")):
-        _need(t, torch.bfloat16, f"attn_prefill_bf16({n})")
+        if t is not None:
+            _need(t, torch.bfloat16, f"attn_prefill_bf16({n})")
     B, S, Hq, D = q.shape
-    Hkv = k.shape[2]
-    if k.shape != (B, S, Hkv, D) or v.shape != k.shape:
+    Hkv = v.shape[2]
+    if v.shape != (B, S, Hkv, D) or (k is not None and k.shape != v.shape):
         raise RuntimeError("Attention: hidden size mismatch")
     if out is None:
         out = torch.empty_like(q)
@@ -63,11 +66,46 @@ def attn_prefill_bf16(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scal
     if scale is None:
         scale = 1.0 / (D ** 0.5)
     _lib.check(_lib.load().bn_attn_prefill_bf16(
-        q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr() if lse is not None else None,
+        q.data_ptr(), k.data_ptr() if k is not None else None, v.data_ptr(), out.data_ptr(),
+        lse.data_ptr() if lse is not None else None,
         B, S, Hq, Hkv, D, float(scale), float(theta), int(position_offset), int(bool(causal)),
         (0x100 if reuse_rotated_k else 0) | (0x200 if single_tile_kernel else 0),
         workspace.ptr, workspace.nbytes, _stream()))
     return out
+
+
+def prefill_table(workspace: Workspace, B: int, S: int, Hkv: int, D: int = 64, theta: float = 10000.0,
+                  position_offset: int = 0) -> None:
+    """Writes the cos/sin table of positions position_offset .. position_offset + S - 1 into a prefill scratch buffer
+    (what the K-rotation launch of attn_prefill_bf16 does on the side), for use with gemm_qkv_rope_bf16."""
+    _lib.check(_lib.load().bn_attn_prefill_bf16_table(B, S, Hkv, D, float(theta), int(position_offset), workspace.ptr,
+                                                      workspace.nbytes, _stream()))
+
+
+def gemm_qkv_rope_bf16(x: torch.Tensor, wqkv_t: torch.Tensor, B: int, S: int, Hq: int, Hkv: int, D: int,
+                       workspace: Workspace, *, position_offset: int = 0, cache=None,
+                       error_word: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The layer's q, k and v projections as one GEMM: x (B*S, hidden) bf16, wqkv_t ((Hq + 2 Hkv) D, hidden) bf16
+    (rows of Wq^T, Wk^T, Wv^T).  Returns q (B, S, Hq, D) as projected and v (B, S, Hkv, D); the rotated K and its
+    norms are left in `workspace` (whose table must be current: prefill_table) for
+    attn_prefill_bf16(q, None, v, workspace=workspace, reuse_rotated_k=True); with `cache` (a PagedKVCache whose
+    sequences are the B rows) rotated K and V are also appended at positions position_offset .. + S - 1."""
+    _need(x, torch.bfloat16, "gemm_qkv_rope_bf16(x)")
+    _need(wqkv_t, torch.bfloat16, "gemm_qkv_rope_bf16(wqkv_t)")
+    hidden = x.shape[1]
+    if x.shape[0] != B * S or wqkv_t.shape != ((Hq + 2 * Hkv) * D, hidden):
+        raise RuntimeError(f"MatMul: inner dimensions mismatch {tuple(x.shape)} x {tuple(wqkv_t.shape)}^T")
+    q = torch.empty((B, S, Hq, D), dtype=torch.bfloat16, device=x.device)
+    v = torch.empty((B, S, Hkv, D), dtype=torch.bfloat16, device=x.device)
+    pool = pages = None
+    n_pages = max_pages = 0
+    if cache is not None:
+        pool, pages, n_pages, max_pages = cache.pool.data_ptr(), cache.page_table.data_ptr(), cache.num_pages, cache.max_pages
+    _lib.check(_lib.load().bn_gemm_qkv_rope_bf16(
+        x.data_ptr(), wqkv_t.data_ptr(), q.data_ptr(), v.data_ptr(), B, S, hidden, Hq, Hkv, D, int(position_offset),
+        workspace.ptr, workspace.nbytes, pool, n_pages, pages, max_pages,
+        error_word.data_ptr() if error_word is not None else None, _stream()))
+    return q, v
 
 
 def gemm_bf16_nt(a: torch.Tensor, bt: torch.Tensor, *, out: Optional[torch.Tensor] = None,

@@ -198,8 +198,8 @@ BN_API size_t bn_attn_prefill_bf16_workspace_bytes(int B, int S, int Hq, int Hkv
  * query head of its group and every query tile), then the attention kernel
  * (tcgen05 tensor cores, TMEM accumulators, TMA-staged K/V) runs.
  * flags: 0, or BN_PREFILL_REUSE_ROTATED_K when the scratch buffer still holds
- * the rotated K of an earlier call on the same k / position_offset (skips the
- * first launch).
+ * the rotated K of an earlier call on the same k / position_offset, or the one
+ * written by bn_gemm_qkv_rope_bf16 (skips the first launch; k may then be NULL).
  * BN_PREFILL_SINGLE_TILE_KERNEL selects the simpler kernel variant (one query
  * tile per CTA, two CTAs per SM) kept for comparison. */
 #define BN_PREFILL_REUSE_ROTATED_K 0x100
@@ -207,6 +207,25 @@ BN_API size_t bn_attn_prefill_bf16_workspace_bytes(int B, int S, int Hq, int Hkv
 BN_API int bn_attn_prefill_bf16(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S, int Hq,
                          int Hkv, int D, float scale, float theta, int position_offset, int causal, int flags,
                                 void* workspace, size_t workspace_bytes, bn_stream_t stream);
+
+/* The q, k and v projections of the layer as ONE tensor-core GEMM with RoPE(K), the cache append and the K operand
+ * of the attention kernel produced in its epilogue (mygrad/llama/llama_layers.py:157-163: three op_mm launches and
+ * the K rotation; plus what bn_kv_append does):
+ *   x (B*S, hidden) bf16; wqkv_t ((Hq + 2*Hkv) * D, hidden) bf16 = the rows of Wq^T, Wk^T, Wv^T one after the other;
+ *   q_out (B, S, Hq, D) bf16 as projected (bn_attn_prefill_bf16 rotates Q itself); v_out (B, S, Hkv, D) bf16;
+ *   rotated K (from the fp32 accumulators: one rounding) and the per-tile key norms go into `prefill_workspace`,
+ *   the scratch buffer of bn_attn_prefill_bf16 for the same B, S, Hkv, whose cos/sin table must have been written
+ *   by bn_attn_prefill_bf16_table (or by an earlier bn_attn_prefill_bf16) for the same S, theta, position_offset;
+ *   then call bn_attn_prefill_bf16(q_out, NULL, v_out, ..., flags = BN_PREFILL_REUSE_ROTATED_K).
+ *   pool / page_table (may be NULL): rotated K and V of token s of sequence b are also written to position
+ *   s + position_offset of that sequence's pages (row b of page_table).
+ * D must be 64; hidden a multiple of 8. */
+BN_API int bn_attn_prefill_bf16_table(int B, int S, int Hkv, int D, float theta, int position_offset, void* workspace,
+                                      size_t workspace_bytes, bn_stream_t stream);
+BN_API int bn_gemm_qkv_rope_bf16(const void* x, const void* wqkv_t, void* q_out, void* v_out, int B, int S, int hidden,
+                                 int Hq, int Hkv, int D, int position_offset, void* prefill_workspace,
+                                 size_t prefill_workspace_bytes, void* pool, int64_t pool_pages,
+                                 const int32_t* page_table, int max_pages, int* error_word, bn_stream_t stream);
 
 /* Paged KV cache.  One pool per layer:
  *   pool[page][kv_head][0=K,1=V][BN_PAGE_TOKENS][D]  bf16

@@ -206,3 +206,63 @@ def test_small_m_gemm(lib, M, N, K):
     scale = max(np.abs(ref).max(), 1e-30)
     assert np.abs(got.float().cpu().numpy() - ref).max() <= scale * 2.0 ** -8
     assert float((got.float() - big.float()).abs().max()) <= scale * 2.0 ** -7
+
+
+@pytest.mark.parametrize("B,S,off", [(2, 200, 0), (1, 128, 0), (3, 77, 5)])
+def test_fused_qkv_projection_with_rope_and_cache_append(lib, B, S, off):
+    """bn_gemm_qkv_rope_bf16 against the separate launches it replaces: q and v are the bits of the plain GEMM; the
+    rotated K (rotated from the fp32 accumulators, one rounding) is within one bf16 ulp of the fp64 rotation of the
+    fp64 product; the cache pages hold that same K and V at positions off .. off + S - 1; the per-tile norm maxima
+    bound the stored keys; and the attention that follows matches the unfused path within the bf16 gate."""
+    from baranet_bdml_b200 import ops
+    from baranet_bdml_b200.kv_cache import PagedKVCache, PAGE_TOKENS
+    Hq, Hkv, D, hidden = 8, 2, 64, 256
+    rng = np.random.default_rng(S + off)
+    x = R.round_bf16(rng.standard_normal((B * S, hidden), dtype=np.float32))
+    wq = R.round_bf16((rng.standard_normal((Hq * D, hidden)) * 0.06).astype(np.float32))
+    wk = R.round_bf16((rng.standard_normal((Hkv * D, hidden)) * 0.06).astype(np.float32))
+    wv = R.round_bf16((rng.standard_normal((Hkv * D, hidden)) * 0.06).astype(np.float32))
+    tx = torch.from_numpy(x).cuda().to(torch.bfloat16)
+    tq, tk, tv = (torch.from_numpy(w).cuda().to(torch.bfloat16) for w in (wq, wk, wv))
+    wqkv = torch.cat([tq, tk, tv], 0).contiguous()
+    max_pages = (S + off + PAGE_TOKENS - 1) // PAGE_TOKENS
+    cache = PagedKVCache(B * max_pages + 3, B, max_pages, Hkv, D)
+    perm = rng.permutation(B * max_pages + 3)[: B * max_pages].astype(np.int32).reshape(B, max_pages)
+    cache.page_table.copy_(torch.from_numpy(perm))
+    ws = ops.prefill_workspace(B, S, Hq, Hkv, D)
+    ops.prefill_table(ws, B, S, Hkv, D, 10000.0, off)
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    q, v = ops.gemm_qkv_rope_bf16(tx, wqkv, B, S, Hq, Hkv, D, ws, position_offset=off, cache=cache, error_word=err)
+    out = ops.attn_prefill_bf16(q, None, v, position_offset=off, workspace=ws, reuse_rotated_k=True)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    ws.status()
+    # q, v: the plain GEMM's bits
+    assert torch.equal(q.view(B * S, -1), ops.gemm_bf16_nt(tx, tq))
+    assert torch.equal(v.view(B * S, -1), ops.gemm_bf16_nt(tx, tv))
+    # rotated K in the cache pages against fp64
+    k64 = x.astype(np.float64) @ wk.astype(np.float64).T                       # (B*S, Hkv*D)
+    pool = cache.pool.float().cpu().numpy()
+    vq = v.float().cpu().numpy().reshape(B, S, Hkv, D)
+    worst = 0.0
+    for b in range(B):
+        pos = np.arange(S) + off
+        i = np.arange(D // 2)
+        freq = (1.0 / np.power(np.float32(10000.0), (2 * i).astype(np.float32) / np.float32(D))).astype(np.float32)
+        ang = (pos[:, None].astype(np.float32) * freq[None]).astype(np.float64)
+        kb = k64[b * S:(b + 1) * S].reshape(S, Hkv, D // 2, 2)
+        rot = np.empty_like(kb)
+        rot[..., 0] = kb[..., 0] * np.cos(ang)[:, None] - kb[..., 1] * np.sin(ang)[:, None]
+        rot[..., 1] = kb[..., 0] * np.sin(ang)[:, None] + kb[..., 1] * np.cos(ang)[:, None]
+        rot = rot.reshape(S, Hkv, D)
+        pages, slots = perm[b][pos // PAGE_TOKENS], pos % PAGE_TOKENS
+        got_k = pool[pages, :, 0, slots, :]                                    # (S, Hkv, D)
+        got_v = pool[pages, :, 1, slots, :]
+        worst = max(worst, np.abs(got_k - rot).max() / max(np.abs(rot).max(), 1e-30))
+        assert np.array_equal(got_v, vq[b])
+    assert worst <= 2.0 ** -8
+    # the attention that follows, against the unfused path (separate GEMMs, K rotated from its bf16 rounding)
+    k_plain = ops.gemm_bf16_nt(tx, tk).view(B, S, Hkv, D)
+    ref = ops.attn_prefill_bf16(q, k_plain, v, position_offset=off)
+    torch.cuda.synchronize()
+    assert float((out.float() - ref.float()).abs().max()) <= 2e-2
