@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libbn_attn.so")
-SOURCES = ["api.cu", "tma.cu", "attn_f32.cu", "rmsnorm.cu", "embed_argmax.cu", "kv_cache.cu", "attn_decode.cu", "attn_prefill_sm100.cu", "gemm_bf16_sm100.cu", "exchange.cu"]
+SOURCES = ["api.cu", "tma.cu", "attn_f32.cu", "rmsnorm.cu", "embed_argmax.cu", "kv_cache.cu", "attn_decode.cu", "attn_prefill_sm100.cu", "gemm_bf16_sm100.cu", "gemm_skinny.cu", "exchange.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared",
               "-I" + os.path.join(ROOT, "include"), "-I" + CSRC]

@@ -1,0 +1,172 @@
+// C (M,N) bf16 = A (M,K) bf16 @ Bt (N,K)^T bf16 for M <= 16 rows: the projections of a decode step, where every
+// sequence contributes ONE row (mygrad/llama/llama_layers.py:157-159,186 and the MLP, :217-232, applied to the new
+// token only; reference operator op_mm, src/ops/op_mm.cuh:39-57, whose naive kernel runs for such shapes).
+//
+// With so few rows the product is a stream of the weight matrix through the SMs: 2 FLOP per weight byte and row, far
+// below what the tensor cores need, so the bound is HBM bandwidth and what matters is that every SM has many loads in
+// flight.  The 128-row tcgen05 tiles of the large GEMM are the wrong tool here (an eighth of each instruction would do
+// useful work and a tile's ring holds few bytes in flight); this kernel uses warp-level mma.sync.m16n8k16, whose M = 16
+// is the whole batch:
+//   CTA = 8 warps = 8 output columns (8 rows of Bt); warp w takes the w-th eighth of K for all 8 columns.
+//   A lane loads 16 contiguous bytes (8 bf16 along K) of ONE weight row and of two activation rows per 32-wide K step
+//   (in batches of 4 or 8 steps, weight and activation loads of a batch all in flight before the first use).  The K order inside a step
+//   is whatever this lane assignment gives: a dot product does not care, as long as A and B use the same one, so no
+//   shuffles or shared-memory staging are needed to form the MMA fragments.
+//   The 8 warps' partial sums (16 x 8 fp32) are added through shared memory in warp order (deterministic).
+// Variants: up to three column ranges of one concatenated weight written to separate outputs (q, k, v of the layer in one
+// launch), and the SwiGLU pair (two weights, h = silu(x Wg) * (x Wu), op_silu.cuh:7-15).
+// K must be a multiple of 256 (a warp's eighth is a whole number of 32-wide steps) and at most 8192; N a multiple
+// of 8.  Anything else belongs to bn_gemm_bf16_nt_small_m.
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace bn {
+
+using namespace ptx;
+
+constexpr int SK_WARPS = 8;
+constexpr int SK_MAX_STEPS = 32;        // 32-wide K steps per warp: K <= 8 * 32 * 32 = 8192
+
+struct SkinnyParams {
+    const __nv_bfloat16* a;             // (M, K)
+    const __nv_bfloat16* bt;            // (N, K)
+    const __nv_bfloat16* bt2;           // SwiGLU: the up weight (N, K); bt is the gate weight
+    __nv_bfloat16* out[3];              // outputs of the column ranges
+    int n_end[3];                       // range r covers columns [n_end[r-1], n_end[r])
+    int ld[3];                          // row stride of out[r] in elements
+    int M, N, K, steps;                 // steps = K / (8 * 32)
+};
+
+template <bool SWIGLU>
+__global__ void __launch_bounds__(SK_WARPS * 32)
+gemm_skinny_kernel(const SkinnyParams p) {
+    __shared__ float s_part[SK_WARPS][2][16][8 + 1];
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int g = lane / 4, j = lane % 4;                 // weight row inside the CTA's 8 / which 8 of a step's 32 K positions
+    const int n0 = blockIdx.x * 8;
+    const size_t kbase = (size_t)warp * p.steps * 32 + j * 8;
+    const uint4* bw = reinterpret_cast<const uint4*>(p.bt + (size_t)(n0 + g) * p.K + kbase);
+    const uint4* bw2 = SWIGLU ? reinterpret_cast<const uint4*>(p.bt2 + (size_t)(n0 + g) * p.K + kbase) : nullptr;
+    const uint4* a_lo = reinterpret_cast<const uint4*>(p.a + (size_t)g * p.K + kbase);
+    const uint4* a_hi = reinterpret_cast<const uint4*>(p.a + (size_t)(g + 8) * p.K + kbase);
+    const bool lo_ok = g < p.M, hi_ok = g + 8 < p.M;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
+    // Loads first, arithmetic after: for a batch of K steps the lane requests its pieces of the weight rows (evict-first:
+    // each weight byte is read once per launch) AND of the two activation rows (read by every CTA, so they stay in L2)
+    // before it uses any of them - a launch of this kernel is one or two memory round trips long, and a load issued after
+    // a wait would add its whole latency to that.
+    constexpr int CH = SWIGLU ? 4 : 8;                     // steps per batch: 64 to 96 registers of loads in flight
+    const uint4 z = make_uint4(0, 0, 0, 0);
+    for (int s0 = 0; s0 < p.steps; s0 += CH) {
+        uint4 wv[CH], wv2[SWIGLU ? CH : 1], al[CH], ah[CH];
+#pragma unroll
+        for (int s = 0; s < CH; ++s)
+            if (s0 + s < p.steps) {
+                wv[s] = __ldcs(bw + (size_t)(s0 + s) * 4);          // 32 K positions = 64 B = 4 x 16 B per row and step
+                if (SWIGLU) wv2[s] = __ldcs(bw2 + (size_t)(s0 + s) * 4);
+            }
+#pragma unroll
+        for (int s = 0; s < CH; ++s)
+            if (s0 + s < p.steps) {
+                al[s] = lo_ok ? __ldg(a_lo + (size_t)(s0 + s) * 4) : z;
+                ah[s] = hi_ok ? __ldg(a_hi + (size_t)(s0 + s) * 4) : z;
+            }
+#pragma unroll
+        for (int s = 0; s < CH; ++s)
+            if (s0 + s < p.steps) {
+                // two k16 MMAs per step: the lane's first four K positions play (2j, 2j+1, 2j+8, 2j+9) of the first,
+                // its last four of the second, in A and B alike
+                mma_bf16_16816(acc, al[s].x, ah[s].x, al[s].y, ah[s].y, wv[s].x, wv[s].y);
+                mma_bf16_16816(acc, al[s].z, ah[s].z, al[s].w, ah[s].w, wv[s].z, wv[s].w);
+                if (SWIGLU) {
+                    mma_bf16_16816(acc2, al[s].x, ah[s].x, al[s].y, ah[s].y, wv2[s].x, wv2[s].y);
+                    mma_bf16_16816(acc2, al[s].z, ah[s].z, al[s].w, ah[s].w, wv2[s].z, wv2[s].w);
+                }
+            }
+    }
+    // C fragment: acc[0], acc[1] = row g, columns 2j, 2j+1; acc[2], acc[3] = row g + 8
+    s_part[warp][0][g][2 * j] = acc[0];
+    s_part[warp][0][g][2 * j + 1] = acc[1];
+    s_part[warp][0][g + 8][2 * j] = acc[2];
+    s_part[warp][0][g + 8][2 * j + 1] = acc[3];
+    if (SWIGLU) {
+        s_part[warp][1][g][2 * j] = acc2[0];
+        s_part[warp][1][g][2 * j + 1] = acc2[1];
+        s_part[warp][1][g + 8][2 * j] = acc2[2];
+        s_part[warp][1][g + 8][2 * j + 1] = acc2[3];
+    }
+    __syncthreads();
+    if (threadIdx.x < 128) {
+        const int row = threadIdx.x / 8, col = threadIdx.x % 8;
+        if (row < p.M) {
+            float v = 0.f, u = 0.f;
+#pragma unroll
+            for (int w = 0; w < SK_WARPS; ++w) {
+                v += s_part[w][0][row][col];
+                if (SWIGLU) u += s_part[w][1][row][col];
+            }
+            if (SWIGLU) v = __fdividef(v, 1.f + __expf(-v)) * u;          // silu(gate) * up
+            const int n = n0 + col;
+            // selects, not indexed parameter arrays (an index known only at run time would copy them to local memory)
+            __nv_bfloat16* o = p.out[0];
+            int ld = p.ld[0], first = 0;
+            if (n >= p.n_end[1]) { o = p.out[2]; ld = p.ld[2]; first = p.n_end[1]; }
+            else if (n >= p.n_end[0]) { o = p.out[1]; ld = p.ld[1]; first = p.n_end[0]; }
+            o[(size_t)row * ld + (n - first)] = __float2bfloat16(v);
+        }
+    }
+}
+
+static int skinny_check(const char* what, const void* a, const void* bt, int M, int N, int K) {
+    if (!a || !bt) return fail(BN_ERR_INVALID_ARG, "%s: null pointer", what);
+    if (M <= 0 || M > 16) return fail(BN_ERR_UNSUPPORTED, "%s: M=%d (1..16 rows)", what, M);
+    if (N <= 0 || N % 8) return fail(BN_ERR_UNSUPPORTED, "%s: N=%d must be a positive multiple of 8", what, N);
+    if (K <= 0 || K % 256 || K > SK_WARPS * 32 * SK_MAX_STEPS)
+        return fail(BN_ERR_UNSUPPORTED, "%s: K=%d must be a multiple of 256, at most %d", what, K, SK_WARPS * 32 * SK_MAX_STEPS);
+    if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(bt)) & 15)
+        return fail(BN_ERR_INVALID_ARG, "%s: a/bt must be 16-byte aligned", what);
+    return require_sm100();
+}
+
+}  // namespace bn
+
+using namespace bn;
+
+extern "C" int bn_gemm_bf16_nt_skinny(const void* a, const void* bt, int M, int N, int K, void* out0, int n0, void* out1,
+                                      int n1, void* out2, bn_stream_t stream) {
+    const char* what = "bn_gemm_bf16_nt_skinny";
+    if (int rc = skinny_check(what, a, bt, M, N, K)) return rc;
+    if (!out0 || n0 <= 0 || n0 > N || n0 % 8 || n1 < 0 || n1 % 8 || n0 + n1 > N || (n1 > 0 && !out1) ||
+        (n0 + n1 < N && !out2))
+        return fail(BN_ERR_INVALID_ARG, "%s: column ranges %d + %d of %d need their outputs (multiples of 8)", what, n0, n1, N);
+    SkinnyParams p{};
+    p.a = static_cast<const __nv_bfloat16*>(a);
+    p.bt = static_cast<const __nv_bfloat16*>(bt);
+    p.bt2 = nullptr;
+    p.out[0] = static_cast<__nv_bfloat16*>(out0);
+    p.out[1] = static_cast<__nv_bfloat16*>(out1);
+    p.out[2] = static_cast<__nv_bfloat16*>(out2);
+    p.n_end[0] = n0; p.n_end[1] = n0 + n1; p.n_end[2] = N;
+    p.ld[0] = n0; p.ld[1] = n1; p.ld[2] = N - n0 - n1;
+    p.M = M; p.N = N; p.K = K; p.steps = K / (SK_WARPS * 32);
+    gemm_skinny_kernel<false><<<N / 8, SK_WARPS * 32, 0, as_stream(stream)>>>(p);
+    return launch_status(what);
+}
+
+extern "C" int bn_gemm_swiglu_bf16_nt_skinny(const void* x, const void* gate_t, const void* up_t, void* h, int M, int inter,
+                                             int K, bn_stream_t stream) {
+    const char* what = "bn_gemm_swiglu_bf16_nt_skinny";
+    if (int rc = skinny_check(what, x, gate_t, M, inter, K)) return rc;
+    if (!up_t || !h || (reinterpret_cast<uintptr_t>(up_t) & 15)) return fail(BN_ERR_INVALID_ARG, "%s: null or misaligned pointer", what);
+    SkinnyParams p{};
+    p.a = static_cast<const __nv_bfloat16*>(x);
+    p.bt = static_cast<const __nv_bfloat16*>(gate_t);
+    p.bt2 = static_cast<const __nv_bfloat16*>(up_t);
+    p.out[0] = static_cast<__nv_bfloat16*>(h);
+    p.out[1] = p.out[2] = nullptr;
+    p.n_end[0] = p.n_end[1] = p.n_end[2] = inter;
+    p.ld[0] = inter; p.ld[1] = p.ld[2] = 0;
+    p.M = M; p.N = inter; p.K = K; p.steps = K / (SK_WARPS * 32);
+    gemm_skinny_kernel<true><<<inter / 8, SK_WARPS * 32, 0, as_stream(stream)>>>(p);
+    return launch_status(what);
+}

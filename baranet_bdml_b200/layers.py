@@ -264,6 +264,11 @@ class MLPBF16:
 
     def __call__(self, x, few_rows: bool = False):
         from . import ops
+        if few_rows and ops.skinny_ok(x.shape[0], self.intermediate_size, x.shape[1]) and \
+                ops.skinny_ok(x.shape[0], x.shape[1], self.intermediate_size):
+            # a decode step with at most 16 rows: both products are weight streams
+            h = ops.gemm_swiglu_bf16_nt_skinny(x, self.gate_proj, self.up_proj)
+            return ops.gemm_bf16_nt_skinny(h, self.down_proj)
         h = ops.gemm_swiglu_bf16_nt(x, self._gate_up, self.intermediate_size)
         # the down projection has few output tiles: with few rows (a decode step) the split-K form streams its weight
         # with all SMs

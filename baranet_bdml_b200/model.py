@@ -114,9 +114,15 @@ class LLaMAModelBF16:
             positions = cache.seq_lens.clone()                    # the new token's position = current length
             residual, normed = ops.add_rmsnorm_bf16(h, pending, layer.input_layernorm_weight, layer.eps)
             at = layer.self_attn
-            q = ops.linear_bf16(normed, at.q_proj).view(B, at.num_heads, at.head_dim)
-            k = ops.linear_bf16(normed, at.k_proj)
-            v = ops.linear_bf16(normed, at.v_proj)
+            kv = at.num_kv_heads * at.head_dim
+            if ops.skinny_ok(B, at.hidden_size + 2 * kv, normed.shape[1]):
+                # q, k, v as one stream of the concatenated weight
+                q, k, v = ops.gemm_bf16_nt_skinny(normed, at.packed_qkv(), (at.num_heads * at.head_dim, kv, kv))
+                q = q.view(B, at.num_heads, at.head_dim)
+            else:
+                q = ops.linear_bf16(normed, at.q_proj).view(B, at.num_heads, at.head_dim)
+                k = ops.linear_bf16(normed, at.k_proj)
+                v = ops.linear_bf16(normed, at.v_proj)
             cache.append(seq_ids, positions, k, v)
             cache.seq_lens.add_(1)
             attn = cache.decode(q, num_heads=at.num_heads, scale=float(at.scale))      # RoPE(q) at position len - 1

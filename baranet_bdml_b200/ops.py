@@ -153,11 +153,53 @@ def gemm_bf16_nt_small_m(a: torch.Tensor, bt: torch.Tensor, *, out: Optional[tor
     return out
 
 
+def skinny_ok(rows: int, n_out: int, k: int) -> bool:
+    """Shapes the weight-streaming kernel for at most 16 rows takes."""
+    return 0 < rows <= 16 and n_out % 8 == 0 and k % 256 == 0 and 0 < k <= 8192
+
+
+def gemm_bf16_nt_skinny(x: torch.Tensor, weight_t: torch.Tensor, splits: Optional[Tuple[int, ...]] = None):
+    """x (rows <= 16, in) @ weight_t (out, in)^T by streaming the weight through all SMs (warp-level MMAs whose M = 16
+    is the whole batch).  `splits` = sizes of up to three column ranges that go to separate output tensors (the q, k, v
+    projections over the concatenated weight); returns one tensor, or a tuple with `splits`."""
+    _need(x, torch.bfloat16, "gemm_bf16_nt_skinny(x)")
+    _need(weight_t, torch.bfloat16, "gemm_bf16_nt_skinny(weight_t)")
+    M, K = x.shape
+    N = weight_t.shape[0]
+    if weight_t.shape[1] != K:
+        raise RuntimeError(f"MatMul: inner dimensions mismatch {tuple(x.shape)} x {tuple(weight_t.shape)}^T")
+    sizes = list(splits) if splits else [N]
+    if sum(sizes) != N or not 1 <= len(sizes) <= 3:
+        raise RuntimeError("gemm_bf16_nt_skinny: the column ranges must add up to the weight's rows (at most three)")
+    outs = [torch.empty((M, n), dtype=torch.bfloat16, device=x.device) for n in sizes]
+    ptrs = [o.data_ptr() for o in outs] + [None] * (3 - len(outs))
+    n0, n1 = sizes[0], (sizes[1] if len(sizes) > 1 else 0)
+    _lib.check(_lib.load().bn_gemm_bf16_nt_skinny(x.data_ptr(), weight_t.data_ptr(), M, N, K, ptrs[0], n0, ptrs[1], n1,
+                                                  ptrs[2], _stream()))
+    return tuple(outs) if splits else outs[0]
+
+
+def gemm_swiglu_bf16_nt_skinny(x: torch.Tensor, gate_t: torch.Tensor, up_t: torch.Tensor) -> torch.Tensor:
+    """silu(x @ Wgate) * (x @ Wup) for at most 16 rows, the two weights (inter, K) given separately."""
+    for t, n in ((x, "x"), (gate_t, "gate_t"), (up_t, "up_t")):
+        _need(t, torch.bfloat16, f"gemm_swiglu_bf16_nt_skinny({n})")
+    M, K = x.shape
+    inter = gate_t.shape[0]
+    if gate_t.shape != (inter, K) or up_t.shape != gate_t.shape:
+        raise RuntimeError("gemm_swiglu_bf16_nt_skinny: gate and up weights must both be (inter, K)")
+    out = torch.empty((M, inter), dtype=torch.bfloat16, device=x.device)
+    _lib.check(_lib.load().bn_gemm_swiglu_bf16_nt_skinny(x.data_ptr(), gate_t.data_ptr(), up_t.data_ptr(), out.data_ptr(),
+                                                         M, inter, K, _stream()))
+    return out
+
+
 def linear_bf16(x: torch.Tensor, weight_t: torch.Tensor) -> torch.Tensor:
-    """x (rows, in) @ weight_t (out, in)^T, choosing the kernel by shape: with few rows and too few 256-wide output
-    tiles to occupy the GPU (measured cross-over: fewer than half as many tiles as SMs) the split-K small-M form,
-    otherwise the large-tile kernel."""
+    """x (rows, in) @ weight_t (out, in)^T, choosing the kernel by shape: at most 16 rows -> the weight-streaming
+    kernel; few rows and too few 256-wide output tiles to occupy the GPU (measured cross-over: fewer than half as many
+    tiles as SMs) -> the split-K small-M form; otherwise the large-tile kernel."""
     rows, n_out = x.shape[0], weight_t.shape[0]
+    if skinny_ok(rows, n_out, x.shape[1]):
+        return gemm_bf16_nt_skinny(x, weight_t)
     if rows <= 128 and (n_out + 255) // 256 < 74:
         return gemm_bf16_nt_small_m(x, weight_t)
     return gemm_bf16_nt(x, weight_t)

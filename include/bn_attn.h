@@ -132,6 +132,18 @@ BN_API size_t bn_gemm_bf16_nt_small_m_workspace_bytes(int M, int N, int K);
 BN_API int bn_gemm_bf16_nt_small_m(const void* a, const void* bt, void* c, int M, int N, int K, void* workspace,
                                    size_t workspace_bytes, int* error_word, bn_stream_t stream);
 
+/* The same product for M <= 16 rows (a decode step with up to 16 sequences on the GPU): the weight matrix streamed
+ * through all SMs with warp-level MMAs (mma.sync m16n8k16, whose M is the whole batch) - no scratch, one launch.
+ * The N columns may go to up to three outputs: columns [0, n0) to out0 (M, n0), [n0, n0 + n1) to out1 (M, n1), the
+ * rest to out2 - the q, k and v projections of the layer as one launch over the concatenated weight.  For a plain
+ * product pass n0 = N, n1 = 0, out1 = out2 = NULL.  K a multiple of 256 (<= 8192), N, n0, n1 multiples of 8.
+ * bn_gemm_swiglu_bf16_nt_skinny: h (M, inter) = silu(x @ gate) * (x @ up) with the two weights given separately,
+ * (inter, K) each (not the packed form of bn_gemm_swiglu_bf16_nt). */
+BN_API int bn_gemm_bf16_nt_skinny(const void* a, const void* bt, int M, int N, int K, void* out0, int n0, void* out1,
+                                  int n1, void* out2, bn_stream_t stream);
+BN_API int bn_gemm_swiglu_bf16_nt_skinny(const void* x, const void* gate_t, const void* up_t, void* h, int M, int inter,
+                                         int K, bn_stream_t stream);
+
 /* h (M, inter) bf16 = silu(x @ Wgate) * (x @ Wup): both GEMMs of the SwiGLU MLP, the activation and the product in
  * one launch of the tensor-core GEMM.  x (M,K) bf16; gate_up_t is the PACKED weight, ceil(inter/128)*256 rows of K
  * bf16: for every block of 128 intermediate indices, the 128 rows of Wgate^T followed by the 128 rows of Wup^T for

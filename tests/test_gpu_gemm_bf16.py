@@ -266,3 +266,43 @@ def test_fused_qkv_projection_with_rope_and_cache_append(lib, B, S, off):
     ref = ops.attn_prefill_bf16(q, k_plain, v, position_offset=off)
     torch.cuda.synchronize()
     assert float((out.float() - ref.float()).abs().max()) <= 2e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 8, 256), (16, 2048, 2048), (2, 2560, 2048), (16, 2048, 5632), (5, 32000, 2048),
+                                   (13, 264, 512)])
+def test_skinny_gemm(lib, M, N, K):
+    """The weight-streaming product for at most 16 rows against fp64 on the same operands (one bf16 ulp at the largest
+    magnitude), equal run to run, and split into three column ranges equal to the unsplit result."""
+    from baranet_bdml_b200 import ops
+    rng = np.random.default_rng(M + N + K)
+    a = R.round_bf16(rng.standard_normal((M, K), dtype=np.float32))
+    bt = R.round_bf16((rng.standard_normal((N, K)) * 0.05).astype(np.float32))
+    ta, tb = torch.from_numpy(a).cuda().to(torch.bfloat16), torch.from_numpy(bt).cuda().to(torch.bfloat16)
+    got = ops.gemm_bf16_nt_skinny(ta, tb)
+    again = ops.gemm_bf16_nt_skinny(ta, tb)
+    torch.cuda.synchronize()
+    assert torch.equal(got, again)
+    ref = a.astype(np.float64) @ bt.astype(np.float64).T
+    assert np.abs(got.float().cpu().numpy() - ref).max() <= max(np.abs(ref).max(), 1e-30) * 2.0 ** -8
+    if N >= 24:
+        n0 = (N // 3) // 8 * 8
+        n1 = 8
+        parts = ops.gemm_bf16_nt_skinny(ta, tb, (n0, n1, N - n0 - n1))
+        torch.cuda.synchronize()
+        assert torch.equal(torch.cat(parts, dim=1), got)
+
+
+def test_skinny_swiglu(lib):
+    from baranet_bdml_b200 import ops
+    rng = np.random.default_rng(77)
+    M, K, inter = 16, 2048, 5632
+    x = R.round_bf16(rng.standard_normal((M, K), dtype=np.float32))
+    wg = R.round_bf16((rng.standard_normal((inter, K)) * 0.03).astype(np.float32))
+    wu = R.round_bf16((rng.standard_normal((inter, K)) * 0.03).astype(np.float32))
+    tx, tg, tu = (torch.from_numpy(t).cuda().to(torch.bfloat16) for t in (x, wg, wu))
+    got = ops.gemm_swiglu_bf16_nt_skinny(tx, tg, tu).float().cpu().numpy()
+    g = x.astype(np.float64) @ wg.astype(np.float64).T
+    u = x.astype(np.float64) @ wu.astype(np.float64).T
+    ref = g / (1.0 + np.exp(-g)) * u
+    assert np.abs(got - ref).max() <= max(np.abs(ref).max(), 1e-30) * 2.0 ** -8
+    assert lib.bn_gemm_bf16_nt_skinny(tx.data_ptr(), tg.data_ptr(), 17, inter, K, tx.data_ptr(), inter, None, 0, None, None) != 0
