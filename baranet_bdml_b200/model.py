@@ -78,7 +78,10 @@ class LLaMAModelBF16:
         for _ in self.layers:
             c = PagedKVCache(B * pages_per_seq, B, pages_per_seq, cfg.num_key_value_heads, cfg.head_dim, cfg.rope_theta)
             c.page_table.copy_(torch.arange(B * pages_per_seq, dtype=torch.int32, device="cuda").view(B, pages_per_seq))
+            if self.caches:
+                c.seq_lens = self.caches[0].seq_lens      # every block holds the same tokens: ONE length vector, advanced once per step
             self.caches.append(c)
+        self.seq_lens = self.caches[0].seq_lens
 
     def prefill(self, input_ids: torch.Tensor, max_len: int) -> torch.Tensor:
         """Prompt pass: (B, S) ids -> logits of the last position (B, vocab); fills the KV caches."""
@@ -98,10 +101,10 @@ class LLaMAModelBF16:
             at = layer.self_attn
             # q/k/v in one GEMM whose epilogue rotates K and appends K and V to this block's cache
             attn = at.attend(normed, B, S, 0, True, cache=cache, workspace=ws)
-            cache.seq_lens.fill_(S)
             o = ops.gemm_bf16_nt(attn, at.o_proj)
             residual, normed = ops.add_rmsnorm_bf16(residual, o, layer.post_attention_layernorm_weight, layer.eps)
             h, pending = residual.view(B, S, H), layer.mlp(normed).view(B, S, H)
+        self.seq_lens.fill_(S)
         return self._logits(h[:, -1].contiguous(), pending[:, -1].contiguous())
 
     def decode_step(self, token_ids: torch.Tensor, check: bool = True) -> torch.Tensor:
@@ -110,8 +113,9 @@ class LLaMAModelBF16:
         h = self.embed(token_ids, check)
         seq_ids = torch.arange(B, dtype=torch.int32, device="cuda")
         pending = None
+        positions = self.seq_lens.clone()                         # the new token's position = current length
+        self.seq_lens.add_(1)
         for layer, cache in zip(self.layers, self.caches):
-            positions = cache.seq_lens.clone()                    # the new token's position = current length
             residual, normed = ops.add_rmsnorm_bf16(h, pending, layer.input_layernorm_weight, layer.eps)
             at = layer.self_attn
             kv = at.num_kv_heads * at.head_dim
@@ -124,7 +128,6 @@ class LLaMAModelBF16:
                 k = ops.linear_bf16(normed, at.k_proj)
                 v = ops.linear_bf16(normed, at.v_proj)
             cache.append(seq_ids, positions, k, v)
-            cache.seq_lens.add_(1)
             attn = cache.decode(q, num_heads=at.num_heads, scale=float(at.scale))      # RoPE(q) at position len - 1
             o = ops.linear_bf16(attn.view(B, -1), at.o_proj)
             residual, normed = ops.add_rmsnorm_bf16(residual, o, layer.post_attention_layernorm_weight, layer.eps)
@@ -138,7 +141,7 @@ class LLaMAModelBF16:
         lengths advance inside the graph, so every replay is the next position."""
         B = self.caches[0].num_seqs
         static_tok = torch.zeros((B,), dtype=torch.int32, device="cuda")
-        saved = [c.seq_lens.clone() for c in self.caches]
+        saved = self.seq_lens.clone()
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):                      # warm-up outside the capture (workspaces, attributes)
@@ -149,8 +152,7 @@ class LLaMAModelBF16:
             logits = self.decode_step(static_tok, check=False)
             nxt = self.argmax(logits)
         torch.cuda.synchronize()
-        for c, s0 in zip(self.caches, saved):              # warm-up and capture must not count as positions
-            c.seq_lens.copy_(s0)
+        self.seq_lens.copy_(saved)                         # warm-up and capture must not count as positions
 
         def step(token_ids: torch.Tensor):
             static_tok.copy_(token_ids)
