@@ -37,7 +37,10 @@ struct SkinnyParams {
     int M, N, K, steps;                 // steps = K / (8 * 32)
 };
 
-template <bool SWIGLU>
+// CH = K steps whose loads a lane keeps in flight at once.  More of them cover more latency per warp; fewer leave
+// registers for more CTAs per SM (8: two, 2: four), which matters when the grid would otherwise need a second, nearly
+// empty wave.
+template <bool SWIGLU, int CH>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_kernel(const SkinnyParams p) {
     __shared__ float s_part[SK_WARPS][2][16][8 + 1];
@@ -55,16 +58,29 @@ gemm_skinny_kernel(const SkinnyParams p) {
     // each weight byte is read once per launch) AND of the two activation rows (read by every CTA, so they stay in L2)
     // before it uses any of them - a launch of this kernel is one or two memory round trips long, and a load issued after
     // a wait would add its whole latency to that.
-    constexpr int CH = SWIGLU ? 4 : 8;                     // steps per batch: 64 to 96 registers of loads in flight
     const uint4 z = make_uint4(0, 0, 0, 0);
-    for (int s0 = 0; s0 < p.steps; s0 += CH) {
-        uint4 wv[CH], wv2[SWIGLU ? CH : 1], al[CH], ah[CH];
+    uint4 wv[CH], wv2[SWIGLU ? CH : 1], al[CH], ah[CH];
+    auto load_weights = [&](int s0) {
 #pragma unroll
         for (int s = 0; s < CH; ++s)
             if (s0 + s < p.steps) {
-                wv[s] = __ldcs(bw + (size_t)(s0 + s) * 4);          // 32 K positions = 64 B = 4 x 16 B per row and step
+                wv[s] = __ldcs(bw + (size_t)(s0 + s) * 4);              // 32 K positions = 64 B = 4 x 16 B per row and step
                 if (SWIGLU) wv2[s] = __ldcs(bw2 + (size_t)(s0 + s) * 4);
             }
+    };
+    // The warp's whole slice of the 8 weight rows is requested into L2 at once (a 128-byte line is two steps of a
+    // row; the four lanes of a row name the same line and are merged): the batches below then find their weights
+    // in L2 instead of each paying a round trip to HBM.  Under a programmatic dependent launch this happens while the
+    // kernel before this one in the stream is still running - the weights do not depend on it, the activations do,
+    // and nothing is READ before the wait (L2 is the point of coherence, so a line prefetched early cannot go stale).
+    for (int s = 0; s < p.steps; s += 2) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(bw + (size_t)s * 4));
+        if (SWIGLU) asm volatile("prefetch.global.L2 [%0];" ::"l"(bw2 + (size_t)s * 4));
+    }
+    grid_dependency_wait();
+    grid_launch_dependents();
+    for (int s0 = 0; s0 < p.steps; s0 += CH) {
+        load_weights(s0);
 #pragma unroll
         for (int s = 0; s < CH; ++s)
             if (s0 + s < p.steps) {
@@ -117,6 +133,25 @@ gemm_skinny_kernel(const SkinnyParams p) {
     }
 }
 
+// Launched as a programmatic dependent of the stream's previous kernel (an ordinary launch if that is refused).
+template <bool SWIGLU, int CH>
+static void skinny_launch(const SkinnyParams& p, int grid, bn_stream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(SK_WARPS * 32);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = as_stream(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<SWIGLU, CH>, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        gemm_skinny_kernel<SWIGLU, CH><<<grid, SK_WARPS * 32, 0, as_stream(stream)>>>(p);
+    }
+}
+
 static int skinny_check(const char* what, const void* a, const void* bt, int M, int N, int K) {
     if (!a || !bt) return fail(BN_ERR_INVALID_ARG, "%s: null pointer", what);
     if (M <= 0 || M > 16) return fail(BN_ERR_UNSUPPORTED, "%s: M=%d (1..16 rows)", what, M);
@@ -149,7 +184,13 @@ extern "C" int bn_gemm_bf16_nt_skinny(const void* a, const void* bt, int M, int 
     p.n_end[0] = n0; p.n_end[1] = n0 + n1; p.n_end[2] = N;
     p.ld[0] = n0; p.ld[1] = n1; p.ld[2] = N - n0 - n1;
     p.M = M; p.N = N; p.K = K; p.steps = K / (SK_WARPS * 32);
-    gemm_skinny_kernel<false><<<N / 8, SK_WARPS * 32, 0, as_stream(stream)>>>(p);
+    // measured on the decode step's shapes: 256 CTAs (o, down) run fastest two per SM with 8 steps in flight, 320 (q/k/v
+    // in one launch) four per SM with 2
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (N / 8 <= 2 * sms) skinny_launch<false, 8>(p, N / 8, stream);
+    else skinny_launch<false, 2>(p, N / 8, stream);
     return launch_status(what);
 }
 
@@ -167,6 +208,6 @@ extern "C" int bn_gemm_swiglu_bf16_nt_skinny(const void* x, const void* gate_t, 
     p.n_end[0] = p.n_end[1] = p.n_end[2] = inter;
     p.ld[0] = inter; p.ld[1] = p.ld[2] = 0;
     p.M = M; p.N = inter; p.K = K; p.steps = K / (SK_WARPS * 32);
-    gemm_skinny_kernel<true><<<inter / 8, SK_WARPS * 32, 0, as_stream(stream)>>>(p);
+    skinny_launch<true, 2>(p, inter / 8, stream);
     return launch_status(what);
 }

@@ -28,6 +28,7 @@ __global__ void kv_append_kernel(__nv_bfloat16* __restrict__ pool, int64_t pool_
                                  int D, float theta) {
     const int half = D / 2;
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    ptx::grid_launch_dependents();      // a programmatic dependent (the decode kernel) may begin its set-up; it waits for this grid before it reads
     if (idx >= (int64_t)T_ * Hkv * half) return;
     const int i = (int)(idx % half);
     const int g = (int)((idx / half) % Hkv);

@@ -206,6 +206,9 @@ rmsnorm_bf16_kernel(const RmsBf16Params p) {
     __shared__ float s_part[8];
     const int tid = threadIdx.x, lane = tid % 32, warp = tid / 32;
     const int pieces = p.hidden / 8;
+    // a kernel launched as a programmatic dependent of this one (a projection that first streams its weights) may
+    // start now; it waits for this grid's completion before it reads anything written here
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     for (int row = blockIdx.x; row < p.rows; row += gridDim.x) {
         const uint4* ar = reinterpret_cast<const uint4*>(p.a + (size_t)row * p.hidden);
         const uint4* br = p.b ? reinterpret_cast<const uint4*>(p.b + (size_t)row * p.hidden) : nullptr;
