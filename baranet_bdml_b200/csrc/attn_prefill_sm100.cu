@@ -494,12 +494,16 @@ prefill_kernel_v1(const __grid_constant__ CUtensorMap tmap_k, const __grid_const
 // gives up (a bounded mbarrier wait ran out, or the CTA-wide abort flag was seen)
 // arrives once on every named barrier it belongs to before it leaves, and every
 // warp checks the abort flag after each named barrier.
-// Measured and dropped on this structure: a quarter of the exponentials as a cubic
-// on the FMA pipe (the softmax warps' issue slots are as scarce as the exponential
-// unit: 248 vs 225 us); two extra warps that only rotate Q (a single warp per tile
-// is too slow for the short units); rotating the next unit's Q after a unit's
-// first step; a rolled 16-column loop with out-of-line helpers (smaller code,
-// slower: 260 us).
+// What bounds the kernel is the softmax warps' own instruction streams (96 registers per thread, four warps per
+// scheduler: dependency waits are not covered), not the exponential unit: every change that adds instructions to a
+// step makes it slower, even when it takes work off that unit.
+// Measured and dropped on this structure (config 2; this kernel 222 - 225 us): an eighth / a quarter / half of the
+// exponentials as a cubic on the FMA pipe (246 / 262 / 279 us); the softmax scale folded into the Q rotation (no gain
+// at config 2, and Q * scale rounds differently from the rotated Q that the parity oracle rounds); rotating the next
+// unit's Q before a unit's last step (240 us) or after its first (238 us); the common step as straight-line code and
+// the diagonal step as a rolled loop (244 us, spills); two extra warps that only rotate Q (227 us); a rolled
+// 16-column loop with out-of-line helpers (260 us); the two tiles as independent streams with dynamically assigned
+// score buffers (277 - 288 us).
 // Optional event log for performance work (compiled out unless built with -DBN_TIMELINE): the warps of CTA 0
 // append (clock64, code) pairs to the caller's lse buffer, 2048 entries per warp, INSTEAD of the log-sum-exp.
 #ifdef BN_TIMELINE
@@ -518,7 +522,18 @@ prefill_kernel_v1(const __grid_constant__ CUtensorMap tmap_k, const __grid_const
 #ifndef BN_MMA_LEADER
 #define BN_MMA_LEADER elect_one()
 #endif
-constexpr int P2_THREADS = 576;
+// Threads per query row in a softmax group: 2 (eight warps per tile, 64 keys of a step each, 96 registers per thread)
+// or 1 (four warps per tile, a whole row per thread, 165 registers: -DBN_P2_TPR=1 passes the same tests and takes
+// 384 us at config 2 against 222 - 225 us; 290 us with the four 16-column chunks of a half as straight-line code, which
+// lets the compiler overlap them - with two threads per row that form spills at 96 registers and is no faster).
+#ifndef BN_P2_TPR
+#define BN_P2_TPR 2
+#endif
+constexpr int P2_TPR = BN_P2_TPR;
+constexpr int P2_WPT = 4 * P2_TPR;             // softmax warps per query tile
+constexpr int P2_SOFT = 2 * P2_WPT;            // softmax warps; then one MMA warp and one producer warp
+constexpr int P2_NH = 2 / P2_TPR;              // 64-key halves of a step that one thread handles
+constexpr int P2_THREADS = 32 * (P2_SOFT + 2);
 constexpr int P2_NSTAGE = 4;
 constexpr int P2_NSBUF = 3;                  // score / probability buffers in tensor memory
 constexpr int P2_SMEM_BYTES = 1024 + PF_TILE_BYTES * (4 + 2 * P2_NSTAGE);
@@ -645,17 +660,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         for (int i = 0; i < 2; ++i) {
             for (int u = 0; u < 2; ++u) {
                 mbar_init(smem_u32(&bar_qfull[i][u]), 1);
-                mbar_init(smem_u32(&bar_qrot[i][u]), 8);
+                mbar_init(smem_u32(&bar_qrot[i][u]), P2_WPT);
                 mbar_init(smem_u32(&bar_qfree[i][u]), 1);
             }
             mbar_init(smem_u32(&bar_o[i]), 1);
             mbar_init(smem_u32(&bar_rs[i]), 1);
-            mbar_init(smem_u32(&bar_rp[i]), 8);
+            mbar_init(smem_u32(&bar_rp[i]), P2_WPT);
             s_redo[i] = 0;
         }
         for (int s = 0; s < P2_NSBUF; ++s) {
             mbar_init(smem_u32(&bar_s[s]), 1);
-            mbar_init(smem_u32(&bar_p[s]), 8);
+            mbar_init(smem_u32(&bar_p[s]), P2_WPT);
         }
         for (int s = 0; s < P2_NSTAGE; ++s) {
             mbar_init(smem_u32(&bar_kvfull[s]), 1);
@@ -664,7 +679,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         s_abort = 0;
         fence_mbar_init();
     }
-    if (warp == 16) {
+    if (warp == P2_SOFT) {
         tc::tmem_alloc(smem_u32(&s_tmem_base), P2_TMEM_COLS);
         tc::tmem_relinquish();
     }
@@ -673,7 +688,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     tc::fence_after_sync();
     const uint32_t tmem = s_tmem_base;
 
-    if (warp == 17) {
+    if (warp == P2_SOFT + 1) {
         // ---------------------------------------------------------- TMA producer
         // K/V tiles stream through a four-stage ring.  The Q tiles of a unit are requested a whole unit ahead: as
         // soon as the unit before last has released their buffer, so that the rotation warp has the whole current
@@ -725,7 +740,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 }
             }
         }
-    } else if (warp == 16) {
+    } else if (warp == P2_SOFT) {
         // ------------------------------------------------------------ MMA issuer
         // ONE thread runs this loop, and its own instruction stream is the critical resource: it shares a scheduler
         // with four busy softmax warps.  So the steady-state path is kept short and straight: one generator (for
@@ -872,11 +887,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         // ------------------------------------------ softmax groups (warps 0..15)
         // Eight warps per query tile: TWO threads per query row, each owning 64 of a step's 128 keys (and 32 of the
         // 64 output columns).  The two threads of a row share the exponent reference.
-        const int u = warp / 8;                     // which query tile of the pair
-        const int hf = (warp / 4) % 2;              // which half of the keys of a step (and of the O columns)
+        const int u = warp / P2_WPT;                // which query tile of the pair
+        const int hf = (warp / 4) % P2_TPR;         // which half of the keys of a step (and of the O columns); 0 when a thread has both
         const int row = (warp % 4) * 32 + lane;     // TMEM lane = query row inside the tile
         const int pair_bar = 1 + u * 4 + (warp % 4);   // named barrier of the two warps that share these 32 rows
-        const int tile_bar = 9 + u;                    // named barrier of the tile's eight warps
+        const int tile_bar = 9 + u;                    // named barrier of the tile's warps
         const uint32_t lane_base = ((uint32_t)((warp % 4) * 32)) << 16;
         const uint32_t tO = tmem + lane_base + P2_COL_O + u * 64 + hf * 32;
         int q_use = 0;
@@ -894,46 +909,50 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 sbase += w.n_t[0] + w.n_t[1];
             }
         };
-        // RoPE on the TMA-loaded Q tile, in place (128-byte-swizzled, K-major).  Each of the tile's eight warps
-        // rotates 16 rows, a row at a time with lane = rotation pair: the row of the cos/sin table is one
+        // RoPE on the TMA-loaded Q tile, in place (128-byte-swizzled, K-major).  Each of the tile's warps rotates
+        // its 16 or 32 rows, a row at a time with lane = rotation pair: the row of the cos/sin table is one
         // coalesced 256-byte load and the lanes touch the 32 banks of the row's 128 bytes.  Also leaves the largest
         // squared norm of the warp's rotated rows for the bound on the scores.
         auto rotate_q = [&](const UnitInfo& w) -> bool {
             const int buf = q_use & 1;
             const uint32_t par = (q_use >> 1) & 1;
             ++q_use;
-            const int r_first = (warp % 8) * 16;
-            const int gi_first = (2 * w.qp + u) * PF_BM + r_first;
-            float2 cs[16];
-#pragma unroll
-            for (int r = 0; r < 16; ++r) cs[r] = __ldg(p.table + (size_t)min(gi_first + r, p.S - 1) * (PF_D / 2) + lane);
-            if (!mbar_wait(smem_u32(&bar_qfull[buf][u]), par, &s_abort)) return false;
-            const uint32_t tile = sQ + (buf * 2 + u) * PF_TILE_BYTES + r_first * 128 + (lane & 3) * 4;
-            const uint32_t chunk = (uint32_t)lane >> 2;
+            constexpr int ROWS = PF_BM / P2_WPT;        // rows per warp: 16 or 32, sixteen at a time
             unsigned row_max = 0;
+            const uint32_t chunk = (uint32_t)lane >> 2;
+#pragma unroll 1
+            for (int rb = 0; rb < ROWS; rb += 16) {
+                const int r_first = (warp % P2_WPT) * ROWS + rb;
+                const int gi_first = (2 * w.qp + u) * PF_BM + r_first;
+                float2 cs[16];
 #pragma unroll
-            for (int r0 = 0; r0 < 16; r0 += 8) {
-                uint32_t x[8];
+                for (int r = 0; r < 16; ++r) cs[r] = __ldg(p.table + (size_t)min(gi_first + r, p.S - 1) * (PF_D / 2) + lane);
+                if (rb == 0 && !mbar_wait(smem_u32(&bar_qfull[buf][u]), par, &s_abort)) return false;
+                const uint32_t tile = sQ + (buf * 2 + u) * PF_TILE_BYTES + r_first * 128 + (lane & 3) * 4;
 #pragma unroll
-                for (int r = 0; r < 8; ++r)       // row r_first + r0 + r: its low three bits are r
-                    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(x[r]) : "r"(tile + (r0 + r) * 128 + ((chunk ^ r) << 4)));
+                for (int r0 = 0; r0 < 16; r0 += 8) {
+                    uint32_t x[8];
 #pragma unroll
-                for (int r = 0; r < 8; ++r) {
-                    const float2 t2 = cs[r0 + r];
-                    const float x0 = bf16_lo(x[r]), x1 = bf16_hi(x[r]);
-                    const uint32_t y = pack_bf16(x0 * t2.x - x1 * t2.y, x0 * t2.y + x1 * t2.x);
-                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(tile + (r0 + r) * 128 + ((chunk ^ r) << 4)), "r"(y) : "memory");
-                    // squared norm of the rotated row, summed over the 32 lanes in fixed point (units of 2^-10,
-                    // rounded up); a lane value at the cap makes the sum reach it, which reads as "unbounded"
-                    const float y0 = bf16_lo(y), y1 = bf16_hi(y);
-                    const float n2 = fmaf(y0, y0, y1 * y1) * 1024.f + 1.f;
-                    row_max = max(row_max, __reduce_add_sync(0xffffffffu, (unsigned)(n2 <= 1.3e8f ? n2 : 1.3e8f)));   // a NaN takes the cap
+                    for (int r = 0; r < 8; ++r)       // row r_first + r0 + r: its low three bits are r
+                        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(x[r]) : "r"(tile + (r0 + r) * 128 + ((chunk ^ r) << 4)));
+#pragma unroll
+                    for (int r = 0; r < 8; ++r) {
+                        const float2 t2 = cs[r0 + r];
+                        const float x0 = bf16_lo(x[r]), x1 = bf16_hi(x[r]);
+                        const uint32_t y = pack_bf16(x0 * t2.x - x1 * t2.y, x0 * t2.y + x1 * t2.x);
+                        asm volatile("st.shared.b32 [%0], %1;" ::"r"(tile + (r0 + r) * 128 + ((chunk ^ r) << 4)), "r"(y) : "memory");
+                        // squared norm of the rotated row, summed over the 32 lanes in fixed point (units of 2^-10,
+                        // rounded up); a lane value at the cap makes the sum reach it, which reads as "unbounded"
+                        const float y0 = bf16_lo(y), y1 = bf16_hi(y);
+                        const float n2 = fmaf(y0, y0, y1 * y1) * 1024.f + 1.f;
+                        row_max = max(row_max, __reduce_add_sync(0xffffffffu, (unsigned)(n2 <= 1.3e8f ? n2 : 1.3e8f)));   // a NaN takes the cap
+                    }
                 }
             }
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-                s_qmax2[buf][u][warp % 8] = row_max >= 130000000u ? INFINITY : (float)row_max * (1.f / 1024.f);
+                s_qmax2[buf][u][warp % P2_WPT] = row_max >= 130000000u ? INFINITY : (float)row_max * (1.f / 1024.f);
                 mbar_arrive(smem_u32(&bar_qrot[buf][u]));
             }
             return true;
@@ -980,12 +999,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                     const volatile float* qm = s_qmax2[(q_use - 1) & 1][u];
                     float m2 = qm[0];
 #pragma unroll
-                    for (int i = 1; i < 8; ++i) m2 = fmaxf(m2, qm[i]);
+                    for (int i = 1; i < P2_WPT; ++i) m2 = fmaxf(m2, qm[i]);
                     q_bound = m2 * p.bound_scale;
                 }
                 const bool bounded = !moved && (q_bound * k_max2 <= 1.0f);
                 const int j0 = j * PF_BN + hf * 64;             // first key of this thread's 64 columns
-                const bool need_mask = (j0 + 63) > tile_free_last;
+                const bool need_mask = (j0 + 64 * P2_NH - 1) > tile_free_last;    // some key of the thread's columns is masked for some row of the tile
 
                 // One pass over this thread's 64 columns: P = exp2(S * scale_log2 - m_ref * scale_log2), each 8 packed
                 // columns written over scores that have already been read.  A 16-column chunk is decided for the
@@ -1002,38 +1021,44 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                         const float mneg = -m_ref * p.scale_log2;
                         const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2), mneg2 = pack_f32x2(mneg, mneg);
                         uint32_t r0[16], r1[16], pk[8];
-                        auto chunk = [&](uint32_t (&r)[16], int c) {
-                            const int kc = j0 + c * 16;
-                            if (!need_mask || kc + 15 <= warp_first_last) softmax_chunk16<false>(r, pk, scale2, mneg2, kc, row_last, sum2);
-                            else if (kc > warp_last_last) {
 #pragma unroll
-                                for (int i = 0; i < 8; ++i) pk[i] = 0u;
-                            } else softmax_chunk16<true>(r, pk, scale2, mneg2, kc, row_last, sum2);
-                        };
-                        // the load of the next 16 columns is in flight while the current 16 are processed
-                        tc::ld16(tS + 0, r0);
-                        tc::wait_ld(r0);
-                        tc::ld16(tS + 16, r1);
-                        chunk(r0, 0);
-                        tc::st8(tS + 0, pk);
-                        tc::wait_ld(r1);
-                        tc::ld16(tS + 32, r0);
-                        chunk(r1, 1);
-                        tc::st8(tS + 8, pk);
-                        tc::wait_ld(r0);
-                        tc::ld16(tS + 48, r1);
-                        chunk(r0, 2);
-                        tc::st8(tS + 16, pk);
-                        tc::wait_ld(r1);
-                        chunk(r1, 3);
-                        tc::st8(tS + 24, pk);
+                        for (int hh = 0; hh < P2_NH; ++hh) {       // the thread's 64-key halves of the step: one or two
+                            const uint32_t tSh = tS + hh * 64;
+                            const int j0h = j0 + hh * 64;
+                            const bool need_mask_h = (j0h + 63) > tile_free_last;
+                            auto chunk = [&](uint32_t (&r)[16], int c) {
+                                const int kc = j0h + c * 16;
+                                if (!need_mask_h || kc + 15 <= warp_first_last) softmax_chunk16<false>(r, pk, scale2, mneg2, kc, row_last, sum2);
+                                else if (kc > warp_last_last) {
+#pragma unroll
+                                    for (int i = 0; i < 8; ++i) pk[i] = 0u;
+                                } else softmax_chunk16<true>(r, pk, scale2, mneg2, kc, row_last, sum2);
+                            };
+                            // the load of the next 16 columns is in flight while the current 16 are processed
+                            tc::ld16(tSh + 0, r0);
+                            tc::wait_ld(r0);
+                            tc::ld16(tSh + 16, r1);
+                            chunk(r0, 0);
+                            tc::st8(tSh + 0, pk);
+                            tc::wait_ld(r1);
+                            tc::ld16(tSh + 32, r0);
+                            chunk(r1, 1);
+                            tc::st8(tSh + 8, pk);
+                            tc::wait_ld(r0);
+                            tc::ld16(tSh + 48, r1);
+                            chunk(r0, 2);
+                            tc::st8(tSh + 16, pk);
+                            tc::wait_ld(r1);
+                            chunk(r1, 3);
+                            tc::st8(tSh + 24, pk);
+                        }
                         float s0, s1;
                         unpack_f32x2(sum2, s0, s1);
                         lsum = s0 + s1;
                     }
                     if (bounded || second) break;
                     const bool over = !(lsum <= 0x1p64f) || (j == 0 && hf == 0 && lsum < 0x1p-64f);
-                    const bool redo = named_bar_or(tile_bar, 256, over);
+                    const bool redo = named_bar_or(tile_bar, 32 * P2_WPT, over);
                     if (s_abort) { ok = false; break; }
                     if (!redo) break;
                     // Rare, and taken by the whole tile together.  The first pass has overwritten scores, so the
@@ -1044,7 +1069,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                     tc::wait_st();
                     tc::fence_before_sync();
                     ++redo_n;
-                    if ((warp & 7) == 0 && lane == 0) *reinterpret_cast<volatile int*>(&s_redo[u]) = redo_n;
+                    if ((warp % P2_WPT) == 0 && lane == 0) *reinterpret_cast<volatile int*>(&s_redo[u]) = redo_n;
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&bar_p[sb]));
                     ok = mbar_wait(smem_u32(&bar_rs[u]), (redo_n - 1) & 1, &s_abort);
@@ -1052,25 +1077,29 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                     tc::fence_after_sync();
                     float hmax = -INFINITY;
 #pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {
+                    for (int c = 0; c < 4 * P2_NH; ++c) {
                         uint32_t r[16];
-                        tc::ld16(tS + c * 16, r);
+                        const int col = (c >> 2) * 64 + (c & 3) * 16;
+                        tc::ld16(tS + col, r);
                         tc::wait_ld(r);
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
-                            if (!need_mask || j0 + c * 16 + i <= row_last) hmax = fmaxf(hmax, __uint_as_float(r[i]));
+                            if (!need_mask || j0 + col + i <= row_last) hmax = fmaxf(hmax, __uint_as_float(r[i]));
                     }
-                    s_xchg[u][hf][row] = hmax;
-                    named_bar_sync(pair_bar, 64);
-                    if (s_abort) { ok = false; break; }
-                    const float tmax = fmaxf(hmax, s_xchg[u][hf ^ 1][row]);
+                    float tmax = hmax;
+                    if (P2_TPR == 2) {
+                        s_xchg[u][hf][row] = hmax;
+                        named_bar_sync(pair_bar, 64);
+                        if (s_abort) { ok = false; break; }
+                        tmax = fmaxf(hmax, s_xchg[u][hf ^ 1][row]);
+                    }
                     const float m_new = j == 0 ? tmax : fmaxf(m_ref, tmax);   // the first step may also move it down
                     const float m_upd = m_new == -INFINITY ? m_ref : m_new;
                     if (j > 0) {
                         const float alpha = ex2((m_ref - m_upd) * p.scale_log2);
                         l_run *= alpha;
 #pragma unroll 1
-                        for (int c = 0; c < 2; ++c) {       // this thread's 32 of the 64 O columns
+                        for (int c = 0; c < 2 * P2_NH; ++c) {       // this thread's 32 (or all 64) O columns
                             uint32_t ro[16];
                             tc::ld16(tO + c * 16, ro);
                             tc::wait_ld(ro);
@@ -1082,7 +1111,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                     m_ref = m_upd;
                 }
                 if (!ok) break;
-                if (second) {
+                if (second && P2_TPR == 2) {
                     named_bar_sync(pair_bar, 64);      // the exchange slots may be written again
                     if (s_abort) { ok = false; break; }
                 }
@@ -1112,31 +1141,37 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             ++units_done;
             if (!ok) break;
             tc::fence_after_sync();
-            s_xchg[u][hf][row] = l_run;
-            named_bar_sync(pair_bar, 64);
-            const float l_row = l_run + s_xchg[u][hf ^ 1][row];
+            float l_row = l_run;
+            if (P2_TPR == 2) {
+                s_xchg[u][hf][row] = l_run;
+                named_bar_sync(pair_bar, 64);
+                l_row = l_run + s_xchg[u][hf ^ 1][row];
+            }
             const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
             __nv_bfloat16* dst = p.out + (((size_t)b * p.S + gi) * p.Hq + h) * PF_D + hf * 32;
-            uint32_t ro[32];
-            tc::ld32(tO, ro);
-            tc::wait_ld(ro);
             // the next unit's first P V overwrites O only after this group's next P arrive, which follows these loads
-            if (gi < p.S) {
+#pragma unroll 1
+            for (int oh = 0; oh < P2_NH; ++oh) {
+                uint32_t ro[32];
+                tc::ld32(tO + oh * 32, ro);
+                tc::wait_ld(ro);
+                if (gi < p.S) {
 #pragma unroll
-                for (int v = 0; v < 4; ++v) {
-                    uint4 o4;
-                    o4.x = pack_bf16(__uint_as_float(ro[v * 8 + 0]) * inv, __uint_as_float(ro[v * 8 + 1]) * inv);
-                    o4.y = pack_bf16(__uint_as_float(ro[v * 8 + 2]) * inv, __uint_as_float(ro[v * 8 + 3]) * inv);
-                    o4.z = pack_bf16(__uint_as_float(ro[v * 8 + 4]) * inv, __uint_as_float(ro[v * 8 + 5]) * inv);
-                    o4.w = pack_bf16(__uint_as_float(ro[v * 8 + 6]) * inv, __uint_as_float(ro[v * 8 + 7]) * inv);
-                    *reinterpret_cast<uint4*>(dst + v * 8) = o4;
+                    for (int v = 0; v < 4; ++v) {
+                        uint4 o4;
+                        o4.x = pack_bf16(__uint_as_float(ro[v * 8 + 0]) * inv, __uint_as_float(ro[v * 8 + 1]) * inv);
+                        o4.y = pack_bf16(__uint_as_float(ro[v * 8 + 2]) * inv, __uint_as_float(ro[v * 8 + 3]) * inv);
+                        o4.z = pack_bf16(__uint_as_float(ro[v * 8 + 4]) * inv, __uint_as_float(ro[v * 8 + 5]) * inv);
+                        o4.w = pack_bf16(__uint_as_float(ro[v * 8 + 6]) * inv, __uint_as_float(ro[v * 8 + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + oh * 32 + v * 8) = o4;
+                    }
                 }
-#ifndef BN_TIMELINE
-                if (p.lse && hf == 0)
-                    p.lse[((size_t)b * p.Hq + h) * p.S + gi] =
-                        l_row > 0.f ? (m_ref * p.scale_log2 + log2f(l_row)) * PF_LN2 : -INFINITY;
-#endif
             }
+#ifndef BN_TIMELINE
+            if (gi < p.S && p.lse && hf == 0)
+                p.lse[((size_t)b * p.Hq + h) * p.S + gi] =
+                    l_row > 0.f ? (m_ref * p.scale_log2 + log2f(l_row)) * PF_LN2 : -INFINITY;
+#endif
             // the partner reads this thread's exchange slot before either of them can write it again: the next
             // write is behind the tile barrier of the next step, or behind the partner's own arrival at the next
             // epilogue's pair barrier
@@ -1145,8 +1180,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         }
         // a warp that gives up (a bounded wait ran out) releases whoever may be waiting for it at a named barrier
         if (!ok) {
-            named_bar_arrive(pair_bar, 64);
-            named_bar_arrive(tile_bar, 256);
+            if (P2_TPR == 2) named_bar_arrive(pair_bar, 64);
+            named_bar_arrive(tile_bar, 32 * P2_WPT);
         }
     }
 
@@ -1154,7 +1189,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     tc::fence_before_sync();
     __syncthreads();
     if (tid == 0 && s_abort) atomicExch(p.error_word, BN_ERR_TIMEOUT);
-    if (warp == 16) {
+    if (warp == P2_SOFT) {
         tc::fence_after_sync();
         tc::tmem_dealloc(tmem, P2_TMEM_COLS);
     }

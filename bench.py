@@ -896,7 +896,7 @@ def measure_generate(torch, args, rank, world, dist, reduce_max, pk):
     from baranet_bdml_b200 import layers as L
     from baranet_bdml_b200.model import LLaMAModelBF16
     import numpy as np
-    n_prompts, S, new_tokens = 16, 512, 128
+    n_prompts, S, new_tokens = 16, 512, int(getattr(args, "generate_steps", 128) or 128)
     if n_prompts % world:
         return {"error": f"16 prompts do not divide over {world} ranks"}
     B = n_prompts // world
@@ -928,7 +928,10 @@ def measure_generate(torch, args, rank, world, dist, reduce_max, pk):
     run_once()                                   # warm-up: workspaces, kernel attributes, graph capture paths
     if dist is not None:
         dist.barrier()
-    ms_prefill, ms_decode, last = run_once()
+    # three whole generations, the median of each part (the eager prompt pass follows the host's load)
+    runs = [run_once()[:2] for _ in range(1 if args.generate_only else 3)]
+    ms_prefill = sorted(r[0] for r in runs)[len(runs) // 2]
+    ms_decode = sorted(r[1] for r in runs)[len(runs) // 2]
     ms_prefill, ms_decode = reduce_max(ms_prefill), reduce_max(ms_decode)
     for c in model.caches:
         c.status()
@@ -946,8 +949,9 @@ def measure_generate(torch, args, rank, world, dist, reduce_max, pk):
                    "prompts_per_gpu": B, "parameters": n_params, "rms_norm_eps": 1e-5,
                    "rms_norm_eps_note": "BASELINE config 5 says 1e-5; the reference's LLaMAConfig default is 1e-6",
                    "parallelism": f"prompts dealt to {world} rank(s), weights replicated, no collective",
-                   "decode": "one CUDA-graph replay per token (about 290 kernels); prompt pass eager"},
-        "gpu_launches": None,
+                   "decode": "one CUDA-graph replay per token (8 launches per block + 4 of this library, and 6 small "
+                             f"torch kernels: casts, the length vector); prompt pass eager; median of {len(runs)} generation(s)"},
+        "gpu_launches": len(runs) * (new_tokens * (8 * cfg.num_hidden_layers + 4) + 7 * cfg.num_hidden_layers + 5),
     }
     del model
     torch.cuda.empty_cache()
@@ -1027,6 +1031,8 @@ def run_ours(args):
         sampler.start()
     if args.decode_only:
         result = measure_decode(torch, args, rank, world, dist, reduce_max, pk)
+    elif args.generate_only:
+        result = measure_generate(torch, args, rank, world, dist, reduce_max, pk)
     else:
         result = measure_prefill(torch, ops, args, rank, world, dist, reduce_max, pk)
         if not args.no_decode:
@@ -1070,7 +1076,7 @@ def run_ours(args):
                     result["layer_f32"] = {"error": repr(e)}
     if rank == 0:
         result["clocks"] = sampler.stop()
-        if world == 1 and not args.no_cpu_baseline and not args.decode_only:
+        if world == 1 and not args.no_cpu_baseline and not args.decode_only and not args.generate_only:
             r = cpu_prefill_sample(n_batches=2)
             result["cpu_baseline"] = {"value": r["value"], "unit": "TFLOP/s", "cores": r["cores"], "kind": "port",
                                       "sample": r["sample"], "seconds": r["seconds"]}
@@ -1085,6 +1091,11 @@ def run_ours(args):
                     return None
                 obj = obj[k]
             return obj
+        if args.decode_only or args.generate_only:       # a profiling run of one object: nothing to summarise
+            _emit(json.dumps(result))
+            if dist is not None:
+                dist.destroy_process_group()
+            return
         result["summary"] = {
             "prefill_tflops": result.get("value"), "prefill_frac": pick(result, "roofline", "frac"),
             "prefill_sharded_tflops": pick(result, "sharded", "value"),
@@ -1129,6 +1140,9 @@ def main():
     ap.add_argument("--no-generate", action="store_true", help="skip the config-5 generation measurement")
     ap.add_argument("--decode-only", action="store_true",
                     help="run only the decode measurement (for profiling); prints its object alone")
+    ap.add_argument("--generate-only", action="store_true",
+                    help="run only the config-5 generation (for profiling), one timed generation; prints its object alone")
+    ap.add_argument("--generate-steps", type=int, default=128, help="decode steps of the config-5 generation")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
