@@ -133,25 +133,6 @@ gemm_skinny_kernel(const SkinnyParams p) {
     }
 }
 
-// Launched as a programmatic dependent of the stream's previous kernel (an ordinary launch if that is refused).
-template <bool SWIGLU, int CH>
-static void skinny_launch(const SkinnyParams& p, int grid, bn_stream_t stream) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(SK_WARPS * 32);
-    cfg.dynamicSmemBytes = 0;
-    cfg.stream = as_stream(stream);
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<SWIGLU, CH>, p) != cudaSuccess) {
-        (void)cudaGetLastError();
-        gemm_skinny_kernel<SWIGLU, CH><<<grid, SK_WARPS * 32, 0, as_stream(stream)>>>(p);
-    }
-}
-
 static int skinny_check(const char* what, const void* a, const void* bt, int M, int N, int K) {
     if (!a || !bt) return fail(BN_ERR_INVALID_ARG, "%s: null pointer", what);
     if (M <= 0 || M > 16) return fail(BN_ERR_UNSUPPORTED, "%s: M=%d (1..16 rows)", what, M);
@@ -189,8 +170,8 @@ extern "C" int bn_gemm_bf16_nt_skinny(const void* a, const void* bt, int M, int 
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (N / 8 <= 2 * sms) skinny_launch<false, 8>(p, N / 8, stream);
-    else skinny_launch<false, 2>(p, N / 8, stream);
+    if (N / 8 <= 2 * sms) launch_dependent(gemm_skinny_kernel<false, 8>, N / 8, SK_WARPS * 32, 0, as_stream(stream), p);
+    else launch_dependent(gemm_skinny_kernel<false, 2>, N / 8, SK_WARPS * 32, 0, as_stream(stream), p);
     return launch_status(what);
 }
 
@@ -208,6 +189,6 @@ extern "C" int bn_gemm_swiglu_bf16_nt_skinny(const void* x, const void* gate_t, 
     p.n_end[0] = p.n_end[1] = p.n_end[2] = inter;
     p.ld[0] = inter; p.ld[1] = p.ld[2] = 0;
     p.M = M; p.N = inter; p.K = K; p.steps = K / (SK_WARPS * 32);
-    skinny_launch<true, 2>(p, inter / 8, stream);
+    launch_dependent(gemm_skinny_kernel<true, 2>, inter / 8, SK_WARPS * 32, 0, as_stream(stream), p);
     return launch_status(what);
 }

@@ -28,7 +28,10 @@ __global__ void kv_append_kernel(__nv_bfloat16* __restrict__ pool, int64_t pool_
                                  int D, float theta) {
     const int half = D / 2;
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    ptx::grid_launch_dependents();      // a programmatic dependent (the decode kernel) may begin its set-up; it waits for this grid before it reads
+    // launched as a programmatic dependent: the projections that produce k_new / v_new have completed after the wait;
+    // the decode kernel behind this one may begin its set-up and waits for this grid before it reads the pool
+    ptx::grid_dependency_wait();
+    ptx::grid_launch_dependents();
     if (idx >= (int64_t)T_ * Hkv * half) return;
     const int i = (int)(idx % half);
     const int g = (int)((idx / half) % Hkv);
@@ -72,12 +75,12 @@ extern "C" int bn_kv_append(void* pool, int64_t pool_pages, const int32_t* page_
     const unsigned blocks = (unsigned)((n + 255) / 256);
     __nv_bfloat16* pl = static_cast<__nv_bfloat16*>(pool);
     if (dtype == 0)
-        kv_append_kernel<float><<<blocks, 256, 0, as_stream(stream)>>>(
-            pl, pool_pages, page_table, max_pages, seq_ids, positions, T, static_cast<const float*>(k_new),
-            static_cast<const float*>(v_new), kv_row_stride, Hkv, D, theta);
+        launch_dependent(kv_append_kernel<float>, blocks, 256, 0, as_stream(stream), pl, pool_pages, page_table,
+                         max_pages, seq_ids, positions, T, static_cast<const float*>(k_new),
+                         static_cast<const float*>(v_new), kv_row_stride, Hkv, D, theta);
     else
-        kv_append_kernel<__nv_bfloat16><<<blocks, 256, 0, as_stream(stream)>>>(
-            pl, pool_pages, page_table, max_pages, seq_ids, positions, T, static_cast<const __nv_bfloat16*>(k_new),
-            static_cast<const __nv_bfloat16*>(v_new), kv_row_stride, Hkv, D, theta);
+        launch_dependent(kv_append_kernel<__nv_bfloat16>, blocks, 256, 0, as_stream(stream), pl, pool_pages, page_table,
+                         max_pages, seq_ids, positions, T, static_cast<const __nv_bfloat16*>(k_new),
+                         static_cast<const __nv_bfloat16*>(v_new), kv_row_stride, Hkv, D, theta);
     return launch_status("bn_kv_append");
 }

@@ -206,8 +206,10 @@ rmsnorm_bf16_kernel(const RmsBf16Params p) {
     __shared__ float s_part[8];
     const int tid = threadIdx.x, lane = tid % 32, warp = tid / 32;
     const int pieces = p.hidden / 8;
-    // a kernel launched as a programmatic dependent of this one (a projection that first streams its weights) may
-    // start now; it waits for this grid's completion before it reads anything written here
+    // Launched as a programmatic dependent: nothing is read before the kernel ahead of this one has completed.  The
+    // kernel behind this one (a projection that first requests its weights into L2) may start now; it in turn waits
+    // for this grid's completion before it reads anything written here.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     for (int row = blockIdx.x; row < p.rows; row += gridDim.x) {
         const uint4* ar = reinterpret_cast<const uint4*>(p.a + (size_t)row * p.hidden);
@@ -292,6 +294,6 @@ extern "C" int bn_add_rmsnorm_bf16(const void* a, const void* b, const void* w, 
     RmsBf16Params p{static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b),
                     static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(sum),
                     static_cast<__nv_bfloat16*>(y), rows, hidden, eps};
-    rmsnorm_bf16_kernel<<<(unsigned)(rows < cap ? rows : cap), 256, 0, as_stream(stream)>>>(p);
+    launch_dependent(rmsnorm_bf16_kernel, (unsigned)(rows < cap ? rows : cap), 256, 0, as_stream(stream), p);
     return launch_status("bn_add_rmsnorm_bf16");
 }

@@ -185,6 +185,13 @@ class LLaMAModelBF16:
             logits = self.decode_step(nxt)
         return out
 
+    def status(self) -> None:
+        """Raises if any kernel of the model gave up a bounded wait since the last check (attention scratch of every
+        block's cache, and the per-device error word of the projection GEMMs).  Synchronises."""
+        for c in self.caches or []:
+            c.status()
+        ops.gemm_status()
+
     def parameters(self):
         p = [self.embed_tokens]
         for layer in self.layers:

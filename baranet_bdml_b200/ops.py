@@ -104,8 +104,38 @@ def gemm_qkv_rope_bf16(x: torch.Tensor, wqkv_t: torch.Tensor, B: int, S: int, Hq
     _lib.check(_lib.load().bn_gemm_qkv_rope_bf16(
         x.data_ptr(), wqkv_t.data_ptr(), q.data_ptr(), v.data_ptr(), B, S, hidden, Hq, Hkv, D, int(position_offset),
         workspace.ptr, workspace.nbytes, pool, n_pages, pages, max_pages,
-        error_word.data_ptr() if error_word is not None else None, _stream()))
+        _gemm_error_ptr(x.device, error_word), _stream()))
     return q, v
+
+
+_gemm_err = {}
+
+
+def _gemm_error_ptr(device, given: Optional[torch.Tensor]):
+    """The error word a tcgen05 GEMM launch reports a bounded wait that ran out into: the caller's, else one int32 per
+    device that lives as long as the process (`gemm_status` reads it).  None only while a stream capture is the first
+    thing that asks for it (no allocation inside a capture)."""
+    if given is not None:
+        return given.data_ptr()
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    word = _gemm_err.get(key)
+    if word is None:
+        if torch.cuda.is_current_stream_capturing():
+            return None
+        word = _gemm_err[key] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{key}")
+    return word.data_ptr()
+
+
+def gemm_status(device=None) -> None:
+    """Raises if any GEMM launched without an error word of its own gave up a bounded wait on this device since the
+    last call (its output is then garbage); clears the word.  Synchronises."""
+    key = torch.cuda.current_device() if device is None else torch.device(device).index
+    word = _gemm_err.get(key)
+    if word is not None:
+        code = int(word.item())
+        if code != 0:
+            word.zero_()
+            raise RuntimeError(f"a projection GEMM reported error {code} (a bounded wait ran out)")
 
 
 def gemm_bf16_nt(a: torch.Tensor, bt: torch.Tensor, *, out: Optional[torch.Tensor] = None,
@@ -122,7 +152,7 @@ def gemm_bf16_nt(a: torch.Tensor, bt: torch.Tensor, *, out: Optional[torch.Tenso
         out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
     _need(out, torch.bfloat16, "gemm_bf16_nt(out)")
     _lib.check(_lib.load().bn_gemm_bf16_nt(a.data_ptr(), bt.data_ptr(), out.data_ptr(), M, N, K,
-                                           error_word.data_ptr() if error_word is not None else None, _stream()))
+                                           _gemm_error_ptr(a.device, error_word), _stream()))
     return out
 
 
@@ -148,8 +178,8 @@ def gemm_bf16_nt_small_m(a: torch.Tensor, bt: torch.Tensor, *, out: Optional[tor
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
     _need(out, torch.bfloat16, "gemm_bf16_nt_small_m(out)")
-    _lib.check(lib.bn_gemm_bf16_nt_small_m(a.data_ptr(), bt.data_ptr(), out.data_ptr(), M, N, K, ws.data_ptr(), n, None,
-                                           _stream()))
+    _lib.check(lib.bn_gemm_bf16_nt_small_m(a.data_ptr(), bt.data_ptr(), out.data_ptr(), M, N, K, ws.data_ptr(), n,
+                                           _gemm_error_ptr(a.device, None), _stream()))
     return out
 
 
@@ -253,7 +283,7 @@ def gemm_swiglu_bf16_nt(x: torch.Tensor, gate_up_t: torch.Tensor, inter: int, *,
         out = torch.empty((M, inter), dtype=torch.bfloat16, device=x.device)
     _need(out, torch.bfloat16, "gemm_swiglu_bf16_nt(out)")
     _lib.check(_lib.load().bn_gemm_swiglu_bf16_nt(x.data_ptr(), gate_up_t.data_ptr(), out.data_ptr(), M, int(inter), K,
-                                                  error_word.data_ptr() if error_word is not None else None, _stream()))
+                                                  _gemm_error_ptr(x.device, error_word), _stream()))
     return out
 
 

@@ -933,8 +933,7 @@ def measure_generate(torch, args, rank, world, dist, reduce_max, pk):
     ms_prefill = sorted(r[0] for r in runs)[len(runs) // 2]
     ms_decode = sorted(r[1] for r in runs)[len(runs) // 2]
     ms_prefill, ms_decode = reduce_max(ms_prefill), reduce_max(ms_decode)
-    for c in model.caches:
-        c.status()
+    model.status()
     n_params = sum(int(t.numel()) for t in model.parameters())
     total_ms = ms_prefill + ms_decode
     out = {

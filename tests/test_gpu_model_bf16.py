@@ -123,3 +123,20 @@ def test_model_logits_against_staged_fp64(lib):
         # two blocks of the decoder-layer gate (2e-2 + two bf16 ulps each) carried through a norm and one more GEMM
         assert err <= 3e-2 * scale, (b, err, scale)
         assert np.abs(got_last[b] - ref[-1]).max() <= 3e-2 * scale
+
+
+def test_model_status_reads_the_gemm_error_word(lib):
+    """Every projection GEMM of the model reports into one error word per device; `status()` is quiet after an ordinary
+    generation, raises once when the word is set (here by hand: nothing is made to hang) and clears it."""
+    from baranet_bdml_b200 import ops
+    model = tiny_model(9)
+    ids = torch.from_numpy(np.random.default_rng(2).integers(3, 1000, (2, 40)).astype(np.int32)).cuda()
+    model.prefill(ids, 48)
+    model.decode_step(ids[:, 0].contiguous())
+    model.status()
+    word = ops._gemm_err[torch.cuda.current_device()]
+    word.fill_(-6)
+    with pytest.raises(RuntimeError):
+        model.status()
+    model.status()
+    assert int(word.item()) == 0
