@@ -56,6 +56,7 @@ constexpr int DEC_THREADS = (DEC_CWARPS + 2) * 32;                      // + pro
 constexpr int DEC_SMEM_BYTES = DEC_NSTAGES * DEC_STAGE_BYTES + 1024;
 constexpr int DEC_MAX_SEQS = 1024;          // sequences per launch (prefix table in shared memory)
 constexpr int DEC_DEFAULT_MIN_TOKENS = 1024;   // a CTA's range is never shorter than this
+constexpr int DEC_WHOLE_MAX_STAGES = 8;        // sequences up to this many stages are never split (if there are enough of them)
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 
@@ -115,11 +116,19 @@ struct Schedule {
     int Hkv, B;
     int T;                 // all stages of the launch (< 2^31)
     int G;                 // CTAs that take part
+    bool whole;            // short sequences: a CTA takes whole (sequence, KV head) segments, nothing is split
     __device__ __forceinline__ int nst(int b) const { return prefix[b + 1] - prefix[b]; }
     // 32-bit division whenever the products fit (G <= 2^9 CTAs, T < 2^22 stages): the 64-bit form is an emulated
     // sequence several times longer, and these sit on the path to the first TMA load
     __device__ __forceinline__ bool small() const { return T < (1 << 22) && G <= (1 << 9); }
     __device__ __forceinline__ int range_begin(int cta) const {
+        if (whole) {
+            // segments [cta * n / G, (cta + 1) * n / G) of the n = B * Hkv segments, in (sequence, head) order
+            const int n = B * Hkv, k = (int)((unsigned)cta * (unsigned)n / (unsigned)G);
+            if (k >= n) return T;
+            const int b = k / Hkv;
+            return Hkv * prefix[b] + (k - b * Hkv) * nst(b);
+        }
         return small() ? (int)((unsigned)cta * (unsigned)T / (unsigned)G) : (int)((long long)cta * T / G);
     }
     // the CTA whose range holds global stage x
@@ -192,6 +201,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
     __shared__ __align__(8) uint64_t merge_bar, part_bar;
     __shared__ int s_prefix[DEC_MAX_SEQS + 1];
     __shared__ int s_len[DEC_MAX_SEQS];
+    __shared__ int s_nmax;                      // stages of the longest sequence
     __shared__ float mrg_m[DEC_CWARPS][DEC_G], mrg_l[DEC_CWARPS][DEC_G];
     __shared__ __align__(16) float mrg_o[DEC_CWARPS][DEC_G][DEC_D + 2];   // read back as float2
     __shared__ __align__(16) __nv_bfloat16 s_q[DEC_G][DEC_D];   // rotated query heads of the current segment
@@ -224,10 +234,11 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
     }
     __syncthreads();
     if (warp == 0) {
-        int carry = 0;
+        int carry = 0, nmax = 0;
         for (int b0 = 0; b0 < p.B; b0 += 32) {
             const int b = b0 + lane;
             int v = b < p.B ? s_prefix[b + 1] : 0;
+            nmax = max(nmax, v);
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
                 const int t = __shfl_up_sync(0xffffffffu, v, o);
@@ -236,7 +247,8 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
             if (b < p.B) s_prefix[b + 1] = carry + v;
             carry += __shfl_sync(0xffffffffu, v, 31);
         }
-        if (lane == 0) s_prefix[0] = 0;
+        nmax = __reduce_max_sync(0xffffffffu, nmax);
+        if (lane == 0) { s_prefix[0] = 0; s_nmax = nmax; }
     }
     __syncthreads();
 
@@ -246,7 +258,12 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmap, const DecodeParams
     sc.Hkv = p.Hkv;
     sc.B = p.B;
     sc.T = p.Hkv * s_prefix[p.B];
-    sc.G = max(1, min((int)gridDim.x, sc.T / p.min_stages));
+    // Equal shares of the stage stream cut segments wherever a share ends, and every cut costs a partial result, a
+    // ticket and a merge.  That is the right trade for long sequences; when no sequence is longer than 8 stages (2048
+    // tokens) and there are at least 16 segments, a cut costs more than the imbalance it removes (16 sequences of 576
+    // tokens: 7.1 us with whole segments against 9.3 - 10.9 us with equal shares), so CTAs take whole segments.
+    sc.whole = s_nmax <= DEC_WHOLE_MAX_STAGES && p.B * p.Hkv >= 16;
+    sc.G = sc.whole ? min((int)gridDim.x, p.B * p.Hkv) : max(1, min((int)gridDim.x, sc.T / p.min_stages));
     const bool active = sc.T > 0 && (int)blockIdx.x < sc.G;
     const int range_lo = active ? sc.range_begin(blockIdx.x) : 0;
     const int range_hi = active ? sc.range_begin(blockIdx.x + 1) : 0;

@@ -53,7 +53,11 @@ def run_decode(cache, q, **kw):
 
 
 @pytest.mark.parametrize("lens", [[1], [16], [17], [1024], [4096], [5, 130, 16, 511, 512, 513, 2049],
-                                  [0, 3, 0, 700]])
+                                  [0, 3, 0, 700],
+                                  # no sequence above 2048 tokens and at least 16 (sequence, KV head) segments: CTAs take
+                                  # whole segments (ragged, with empty sequences; more segments than CTAs in the last one)
+                                  [5, 130, 16, 511, 512, 513, 2048, 1, 0, 257],
+                                  [(37 * i) % 600 for i in range(50)]])
 def test_decode_vs_oracle(lib, lens):
     cache, pool, pt, q = build_cache(lens, sum(lens) + len(lens), poison=True)
     got, got32, lse = run_decode(cache, q, max_seq_len=max(max(lens), 1))
