@@ -81,40 +81,45 @@ rope_table_kernel(float2* __restrict__ table, int S, float theta, int position_o
 // ---------------------------------------------------------------------------
 // launch 1: K rotation + cos/sin table
 // ---------------------------------------------------------------------------
-constexpr int RK_POS = 8;   // positions per block
+// One block per (batch element, 128-key tile), all KV heads: the block owns the tile's norm maxima, so they are plain
+// stores (no global atomics, nothing to clear first), and a cos/sin pair is computed once per position and block.
+constexpr int RK_THREADS = 512;
+constexpr int RK_UNROLL = 4;    // 16-byte pieces a thread has in flight
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(RK_THREADS)
 rope_k_kernel(const __nv_bfloat16* __restrict__ k, __nv_bfloat16* __restrict__ krot, float2* __restrict__ table,
               int* __restrict__ kmax2, int B, int S, int Hkv, float theta, int position_offset,
               int* __restrict__ error_word) {
-    __shared__ float2 cs[RK_POS][PF_D / 2];
-    __shared__ int s_kmax[64];          // per KV head (up to 64): largest |k|^2 of this block's keys, as float bits
-    const int s0 = blockIdx.x * RK_POS, b = blockIdx.y;
-    if (blockIdx.x == 0 && b == 0 && threadIdx.x == 0) *error_word = 0;
-    // 16-byte pieces (4 rotation pairs) of this block's positions: issue the loads before the cos/sin work
+    __shared__ float2 cs[PF_BN][PF_D / 2];      // 32 KB
+    __shared__ int s_kmax[64];                  // per KV head (up to 64): largest |k|^2 of the tile's keys, as float bits
+    const int tile = blockIdx.x, b = blockIdx.y;
+    const int s0 = tile * PF_BN, npos = min(PF_BN, S - s0);
+    if (tile == 0 && b == 0 && threadIdx.x == 0) *error_word = 0;
+    // 16-byte pieces (4 rotation pairs) of the tile's keys: the first loads are issued before the cos/sin work
     const int chunks_per_pos = Hkv * (PF_D / 8);
-    const int n_chunks = min(RK_POS, S - s0) * chunks_per_pos;
+    const int n_chunks = npos * chunks_per_pos;
     const uint4* src = reinterpret_cast<const uint4*>(k + ((size_t)b * S + s0) * Hkv * PF_D);
     uint4* dst = reinterpret_cast<uint4*>(krot + ((size_t)b * S + s0) * Hkv * PF_D);
-    constexpr int RK_UNROLL = 2;
     uint4 raw[RK_UNROLL];
 #pragma unroll
     for (int i = 0; i < RK_UNROLL; ++i) {
-        const int e = threadIdx.x + i * 256;
+        const int e = threadIdx.x + i * RK_THREADS;
         raw[i] = e < n_chunks ? __ldg(src + e) : make_uint4(0, 0, 0, 0);
     }
     if (threadIdx.x < 64) s_kmax[threadIdx.x] = 0;
     {
-        const int ds = threadIdx.x / (PF_D / 2), i = threadIdx.x % (PF_D / 2);
+        const int i = threadIdx.x % (PF_D / 2);                      // the thread's rotation pair: one frequency
         const float freq = rope_inv_freq(i, PF_D, theta);
-        const float angle = (s0 + ds + position_offset) * freq;
-        const float2 v = make_float2(cosf(angle), sinf(angle));
-        cs[ds][i] = v;
-        if (b == 0 && s0 + ds < S) table[(size_t)(s0 + ds) * (PF_D / 2) + i] = v;
+        for (int ds = threadIdx.x / (PF_D / 2); ds < npos; ds += RK_THREADS / (PF_D / 2)) {
+            const float angle = (s0 + ds + position_offset) * freq;
+            const float2 v = make_float2(cosf(angle), sinf(angle));
+            cs[ds][i] = v;
+            if (b == 0) table[(size_t)(s0 + ds) * (PF_D / 2) + i] = v;
+        }
     }
     __syncthreads();
     // Rotates one 16-byte piece (4 pairs); the squared norm of the key it belongs to is summed over the 8 threads
-    // that hold the key's 8 pieces (neighbouring lanes) and the block's maximum per KV head kept in shared memory.
+    // that hold the key's 8 pieces (neighbouring lanes) and the tile's maximum per KV head kept in shared memory.
     // A non-negative float orders like its bit pattern, so the maxima are integer atomics.
     auto rotate = [&](uint4 x, int e, bool valid) {
         const int ds = e / chunks_per_pos, c = e % (PF_D / 8);     // position, and which 4 pairs of the head
@@ -138,22 +143,27 @@ rope_k_kernel(const __nv_bfloat16* __restrict__ k, __nv_bfloat16* __restrict__ k
         }
         return make_uint4(w[0], w[1], w[2], w[3]);
     };
+    // whole warps take part in the shuffles, so the loops run to a multiple of the block size
+    for (int e0 = 0; e0 < n_chunks; e0 += RK_UNROLL * RK_THREADS) {
+        uint4 nxt[RK_UNROLL];
 #pragma unroll
-    for (int i = 0; i < RK_UNROLL; ++i) {
-        const int e = threadIdx.x + i * 256;
-        const uint4 y = rotate(raw[i], e, e < n_chunks);
-        if (e < n_chunks) dst[e] = y;
-    }
-    for (int e0 = RK_UNROLL * 256; e0 < n_chunks; e0 += 256) {     // whole warps take part in the shuffles
-        const int e = e0 + threadIdx.x;
-        const uint4 y = rotate(e < n_chunks ? __ldg(src + e) : make_uint4(0, 0, 0, 0), e, e < n_chunks);
-        if (e < n_chunks) dst[e] = y;
+        for (int i = 0; i < RK_UNROLL; ++i) {                        // the next round's loads before this round's work
+            const int e = e0 + RK_UNROLL * RK_THREADS + threadIdx.x + i * RK_THREADS;
+            nxt[i] = e < n_chunks ? __ldg(src + e) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int i = 0; i < RK_UNROLL; ++i) {
+            const int e = e0 + threadIdx.x + i * RK_THREADS;
+            const uint4 y = rotate(raw[i], e, e < n_chunks);
+            if (e < n_chunks) dst[e] = y;
+        }
+#pragma unroll
+        for (int i = 0; i < RK_UNROLL; ++i) raw[i] = nxt[i];
     }
     __syncthreads();
-    // the 8 positions of a block lie inside one 128-key tile
     // (more than 64 KV heads share slots: a head then reads the maximum over the heads of its slot, still a bound)
-    for (int hh = threadIdx.x; hh < Hkv; hh += 256)
-        atomicMax(kmax2 + ((size_t)b * Hkv + hh) * ((S + PF_BN - 1) / PF_BN) + s0 / PF_BN, s_kmax[hh & 63]);
+    for (int hh = threadIdx.x; hh < Hkv; hh += RK_THREADS)
+        kmax2[((size_t)b * Hkv + hh) * ((S + PF_BN - 1) / PF_BN) + tile] = s_kmax[hh & 63];
 }
 
 // ---------------------------------------------------------------------------
@@ -1259,9 +1269,7 @@ extern "C" int bn_attn_prefill_bf16(const void* q, const void* k, const void* v,
 
     int* kmax2 = reinterpret_cast<int*>(ws + L.kmax2);
     if (!(flags & BN_PREFILL_REUSE_ROTATED_K)) {
-        cudaError_t e = cudaMemsetAsync(kmax2, 0, L.krot - L.kmax2, st);      // the rotation takes maxima into it
-        if (e != cudaSuccess) return fail(BN_ERR_CUDA, "bn_attn_prefill_bf16: cudaMemsetAsync: %s", cudaGetErrorString(e));
-        rope_k_kernel<<<dim3((S + RK_POS - 1) / RK_POS, B), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(k), krot, table,
+        rope_k_kernel<<<dim3((S + PF_BN - 1) / PF_BN, B), RK_THREADS, 0, st>>>(static_cast<const __nv_bfloat16*>(k), krot, table,
                                                                           kmax2, B, S, Hkv, theta, position_offset, error_word);
         if (int rc = launch_status("bn_attn_prefill_bf16 (rope_k)")) return rc;
     }
