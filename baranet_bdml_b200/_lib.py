@@ -34,6 +34,7 @@ SIGNATURES = {
     "bn_gemm_bf16_nt_small_m": (_i, [_p, _p, _p, _i, _i, _i, _p, _sz, _p, _p]),
     "bn_gemm_bf16_nt_skinny": (_i, [_p, _p, _i, _i, _i, _p, _i, _p, _i, _p, _p]),
     "bn_gemm_swiglu_bf16_nt_skinny": (_i, [_p, _p, _p, _p, _i, _i, _i, _p]),
+    "bn_gemm_qkv_append_bf16_skinny": (_i, [_p, _p, _i, _i, _i, _i, _i, _p, _p, _i64, _p, _i, _p, _p, _f, _p]),
     "bn_gemm_swiglu_bf16_nt": (_i, [_p, _p, _p, _i, _i, _i, _p, _p]),
     "bn_rmsnorm_f32": (_i, [_p, _i64, _i64, _p, _i64, _p, _i64, _i64, _i, _i, _f, _p]),
     "bn_add_rmsnorm_f32": (_i, [_p, _i64, _i64, _p, _i64, _i64, _p, _i64, _p, _i64, _i64, _p, _i64, _i64, _i, _i, _f,

@@ -35,12 +35,21 @@ struct SkinnyParams {
     int n_end[3];                       // range r covers columns [n_end[r-1], n_end[r])
     int ld[3];                          // row stride of out[r] in elements
     int M, N, K, steps;                 // steps = K / (8 * 32)
+    // APPEND: columns from n_end[0] on are the K and V projections of one new token per row and go to the paged cache
+    // instead of out[1] / out[2] (arguments as bn_kv_append)
+    __nv_bfloat16* pool;
+    const int32_t* page_table;
+    const int32_t* seq_ids;
+    const int32_t* positions;
+    int64_t pool_pages;
+    int max_pages, Hkv, D;
+    float theta;
 };
 
 // CH = K steps whose loads a lane keeps in flight at once.  More of them cover more latency per warp; fewer leave
 // registers for more CTAs per SM (8: two, 2: four), which matters when the grid would otherwise need a second, nearly
 // empty wave.
-template <bool SWIGLU, int CH>
+template <bool SWIGLU, int CH, bool APPEND = false>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_kernel(const SkinnyParams p) {
     __shared__ float s_part[SK_WARPS][2][16][8 + 1];
@@ -114,15 +123,43 @@ gemm_skinny_kernel(const SkinnyParams p) {
     __syncthreads();
     if (threadIdx.x < 128) {
         const int row = threadIdx.x / 8, col = threadIdx.x % 8;
+        float v = 0.f, u = 0.f;
         if (row < p.M) {
-            float v = 0.f, u = 0.f;
 #pragma unroll
             for (int w = 0; w < SK_WARPS; ++w) {
                 v += s_part[w][0][row][col];
                 if (SWIGLU) u += s_part[w][1][row][col];
             }
             if (SWIGLU) v = __fdividef(v, 1.f + __expf(-v)) * u;          // silu(gate) * up
-            const int n = n0 + col;
+        }
+        const int n = n0 + col;
+        if (APPEND && n >= p.n_end[0]) {       // the same for the CTA's 8 columns: the ranges are multiples of 8
+            // What bn_kv_append does with the bf16 row the plain kernel would have written: the value is rounded to
+            // bf16 first, a K pair (2i, 2i+1) = (this column, its neighbour) is rotated at the row's position in fp32
+            // and rounded again, V is stored as it is - the cache ends up with the bits of the two-launch path.
+            const float vb = __bfloat162float(__float2bfloat16(v));
+            const float other = __shfl_xor_sync(0xffffffffu, vb, 1);
+            if (row < p.M) {
+                const bool is_k = n < p.n_end[1];
+                const int local = n - (is_k ? p.n_end[0] : p.n_end[1]);
+                const int g = local / p.D, d = local - g * p.D;
+                const int pos = p.positions[row];
+                const int lp = pos / BN_PAGE_TOKENS;
+                if (pos >= 0 && lp < p.max_pages) {
+                    const int page = p.page_table[(int64_t)p.seq_ids[row] * p.max_pages + lp];
+                    if (page >= 0 && page < p.pool_pages) {
+                        float y = vb;
+                        if (is_k) {
+                            const float angle = pos * rope_inv_freq(d / 2, p.D, p.theta);
+                            const float c = cosf(angle), sn = sinf(angle);
+                            y = (d & 1) ? other * sn + vb * c : vb * c - other * sn;
+                        }
+                        p.pool[((((int64_t)page * p.Hkv + g) * 2 + (is_k ? 0 : 1)) * BN_PAGE_TOKENS + pos % BN_PAGE_TOKENS) * p.D + d] =
+                            __float2bfloat16(y);
+                    }
+                }
+            }
+        } else if (row < p.M) {
             // selects, not indexed parameter arrays (an index known only at run time would copy them to local memory)
             __nv_bfloat16* o = p.out[0];
             int ld = p.ld[0], first = 0;
@@ -190,5 +227,34 @@ extern "C" int bn_gemm_swiglu_bf16_nt_skinny(const void* x, const void* gate_t, 
     p.ld[0] = inter; p.ld[1] = p.ld[2] = 0;
     p.M = M; p.N = inter; p.K = K; p.steps = K / (SK_WARPS * 32);
     launch_dependent(gemm_skinny_kernel<true, 2>, inter / 8, SK_WARPS * 32, 0, as_stream(stream), p);
+    return launch_status(what);
+}
+
+extern "C" int bn_gemm_qkv_append_bf16_skinny(const void* x, const void* wqkv_t, int M, int hidden, int Hq, int Hkv, int D,
+                                              void* q_out, void* pool, int64_t pool_pages, const int32_t* page_table,
+                                              int max_pages, const int32_t* seq_ids, const int32_t* positions, float theta,
+                                              bn_stream_t stream) {
+    const char* what = "bn_gemm_qkv_append_bf16_skinny";
+    if (Hq <= 0 || Hkv <= 0 || D <= 0 || D % 8)
+        return fail(BN_ERR_INVALID_ARG, "%s: bad head shape Hq=%d Hkv=%d D=%d (D a multiple of 8)", what, Hq, Hkv, D);
+    const int N = (Hq + 2 * Hkv) * D;
+    if (int rc = skinny_check(what, x, wqkv_t, M, N, hidden)) return rc;
+    if (!q_out || !pool || !page_table || !seq_ids || !positions || max_pages <= 0 || pool_pages <= 0)
+        return fail(BN_ERR_INVALID_ARG, "%s: null pointer or empty cache", what);
+    SkinnyParams p{};
+    p.a = static_cast<const __nv_bfloat16*>(x);
+    p.bt = static_cast<const __nv_bfloat16*>(wqkv_t);
+    p.out[0] = static_cast<__nv_bfloat16*>(q_out);
+    p.n_end[0] = Hq * D; p.n_end[1] = (Hq + Hkv) * D; p.n_end[2] = N;
+    p.ld[0] = Hq * D;
+    p.M = M; p.N = N; p.K = hidden; p.steps = hidden / (SK_WARPS * 32);
+    p.pool = static_cast<__nv_bfloat16*>(pool);
+    p.page_table = page_table; p.seq_ids = seq_ids; p.positions = positions;
+    p.pool_pages = pool_pages; p.max_pages = max_pages; p.Hkv = Hkv; p.D = D; p.theta = theta;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (N / 8 <= 2 * sms) launch_dependent(gemm_skinny_kernel<false, 8, true>, N / 8, SK_WARPS * 32, 0, as_stream(stream), p);
+    else launch_dependent(gemm_skinny_kernel<false, 2, true>, N / 8, SK_WARPS * 32, 0, as_stream(stream), p);
     return launch_status(what);
 }

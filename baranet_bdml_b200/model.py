@@ -120,14 +120,14 @@ class LLaMAModelBF16:
             at = layer.self_attn
             kv = at.num_kv_heads * at.head_dim
             if ops.skinny_ok(B, at.hidden_size + 2 * kv, normed.shape[1]):
-                # q, k, v as one stream of the concatenated weight
-                q, k, v = ops.gemm_bf16_nt_skinny(normed, at.packed_qkv(), (at.num_heads * at.head_dim, kv, kv))
+                # q, k, v as one stream of the concatenated weight; K rotated and K, V appended by the same launch
+                q = ops.gemm_qkv_append_bf16_skinny(normed, at.packed_qkv(), cache, seq_ids, positions, at.num_heads)
                 q = q.view(B, at.num_heads, at.head_dim)
             else:
                 q = ops.linear_bf16(normed, at.q_proj).view(B, at.num_heads, at.head_dim)
                 k = ops.linear_bf16(normed, at.k_proj)
                 v = ops.linear_bf16(normed, at.v_proj)
-            cache.append(seq_ids, positions, k, v)
+                cache.append(seq_ids, positions, k, v)
             attn = cache.decode(q, num_heads=at.num_heads, scale=float(at.scale))      # RoPE(q) at position len - 1
             o = ops.linear_bf16(attn.view(B, -1), at.o_proj)
             residual, normed = ops.add_rmsnorm_bf16(residual, o, layer.post_attention_layernorm_weight, layer.eps)

@@ -209,6 +209,27 @@ def gemm_bf16_nt_skinny(x: torch.Tensor, weight_t: torch.Tensor, splits: Optiona
     return tuple(outs) if splits else outs[0]
 
 
+def gemm_qkv_append_bf16_skinny(x: torch.Tensor, wqkv_t: torch.Tensor, cache, seq_ids: torch.Tensor,
+                                positions: torch.Tensor, num_heads: int) -> torch.Tensor:
+    """The q, k and v projections of one new token per row (rows <= 16) over the concatenated weight, with RoPE(K) and
+    the append to `cache` (a PagedKVCache) in the same launch; returns q (rows, num_heads * D).  Leaves in the cache
+    the bits of `gemm_bf16_nt_skinny` + `cache.append`."""
+    _need(x, torch.bfloat16, "gemm_qkv_append_bf16_skinny(x)")
+    _need(wqkv_t, torch.bfloat16, "gemm_qkv_append_bf16_skinny(wqkv_t)")
+    _need(seq_ids, torch.int32, "gemm_qkv_append_bf16_skinny(seq_ids)")
+    _need(positions, torch.int32, "gemm_qkv_append_bf16_skinny(positions)")
+    M, K = x.shape
+    D, Hkv = cache.head_dim, cache.num_kv_heads
+    if wqkv_t.shape != ((num_heads + 2 * Hkv) * D, K):
+        raise RuntimeError(f"MatMul: inner dimensions mismatch {tuple(x.shape)} x {tuple(wqkv_t.shape)}^T")
+    q = torch.empty((M, num_heads * D), dtype=torch.bfloat16, device=x.device)
+    _lib.check(_lib.load().bn_gemm_qkv_append_bf16_skinny(
+        x.data_ptr(), wqkv_t.data_ptr(), M, K, num_heads, Hkv, D, q.data_ptr(), cache.pool.data_ptr(), cache.num_pages,
+        cache.page_table.data_ptr(), cache.max_pages, seq_ids.data_ptr(), positions.data_ptr(), float(cache.theta),
+        _stream()))
+    return q
+
+
 def gemm_swiglu_bf16_nt_skinny(x: torch.Tensor, gate_t: torch.Tensor, up_t: torch.Tensor) -> torch.Tensor:
     """silu(x @ Wgate) * (x @ Wup) for at most 16 rows, the two weights (inter, K) given separately."""
     for t, n in ((x, "x"), (gate_t, "gate_t"), (up_t, "up_t")):

@@ -948,9 +948,9 @@ def measure_generate(torch, args, rank, world, dist, reduce_max, pk):
                    "prompts_per_gpu": B, "parameters": n_params, "rms_norm_eps": 1e-5,
                    "rms_norm_eps_note": "BASELINE config 5 says 1e-5; the reference's LLaMAConfig default is 1e-6",
                    "parallelism": f"prompts dealt to {world} rank(s), weights replicated, no collective",
-                   "decode": "one CUDA-graph replay per token (8 launches per block + 4 of this library, and 6 small "
+                   "decode": "one CUDA-graph replay per token (7 launches per block + 4 of this library, and 6 small "
                              f"torch kernels: casts, the length vector); prompt pass eager; median of {len(runs)} generation(s)"},
-        "gpu_launches": len(runs) * (new_tokens * (8 * cfg.num_hidden_layers + 4) + 7 * cfg.num_hidden_layers + 5),
+        "gpu_launches": len(runs) * (new_tokens * (7 * cfg.num_hidden_layers + 4) + 7 * cfg.num_hidden_layers + 5),
     }
     del model
     torch.cuda.empty_cache()

@@ -144,6 +144,17 @@ BN_API int bn_gemm_bf16_nt_skinny(const void* a, const void* bt, int M, int N, i
 BN_API int bn_gemm_swiglu_bf16_nt_skinny(const void* x, const void* gate_t, const void* up_t, void* h, int M, int inter,
                                          int K, bn_stream_t stream);
 
+/* The q, k and v projections of a decode step (one new token per row, M <= 16) with the cache append in the same launch:
+ * x (M, hidden) @ wqkv_t ((Hq + 2 Hkv) D, hidden)^T; the q columns go to q_out (M, Hq D), the k columns are rotated at
+ * positions[row] and written with the v columns into the page of (seq_ids[row], positions[row]) - the bits that
+ * bn_gemm_bf16_nt_skinny followed by bn_kv_append (bf16 rows) leave in the cache, in one launch instead of two
+ * (mygrad/llama/llama_layers.py:157-171 for the new token only).  Cache arguments as bn_kv_append; rows whose position
+ * or page is out of range are skipped as there.  hidden a multiple of 256 (<= 8192), D a multiple of 8. */
+BN_API int bn_gemm_qkv_append_bf16_skinny(const void* x, const void* wqkv_t, int M, int hidden, int Hq, int Hkv, int D,
+                                          void* q_out, void* pool, int64_t pool_pages, const int32_t* page_table,
+                                          int max_pages, const int32_t* seq_ids, const int32_t* positions, float theta,
+                                          bn_stream_t stream);
+
 /* h (M, inter) bf16 = silu(x @ Wgate) * (x @ Wup): both GEMMs of the SwiGLU MLP, the activation and the product in
  * one launch of the tensor-core GEMM.  x (M,K) bf16; gate_up_t is the PACKED weight, ceil(inter/128)*256 rows of K
  * bf16: for every block of 128 intermediate indices, the 128 rows of Wgate^T followed by the 128 rows of Wup^T for

@@ -306,3 +306,38 @@ def test_skinny_swiglu(lib):
     ref = g / (1.0 + np.exp(-g)) * u
     assert np.abs(got - ref).max() <= max(np.abs(ref).max(), 1e-30) * 2.0 ** -8
     assert lib.bn_gemm_bf16_nt_skinny(tx.data_ptr(), tg.data_ptr(), 17, inter, K, tx.data_ptr(), inter, None, 0, None, None) != 0
+
+
+@pytest.mark.parametrize("M,Hq,Hkv,D,hidden", [(16, 32, 4, 64, 2048), (3, 4, 2, 64, 256), (7, 6, 3, 32, 512)])
+def test_skinny_qkv_with_cache_append(lib, M, Hq, Hkv, D, hidden):
+    """One launch for the q, k and v projections of a decode step with RoPE(K) and the cache append against the
+    two-launch path (three-output skinny GEMM, then bn_kv_append): q equal, and every page of the cache equal bit for
+    bit - including rows whose position is out of the page table's range, which both paths skip."""
+    from baranet_bdml_b200 import ops
+    from baranet_bdml_b200.kv_cache import PagedKVCache
+    rng = np.random.default_rng(M * 1000 + hidden)
+    x = torch.from_numpy(R.round_bf16(rng.standard_normal((M, hidden), dtype=np.float32))).cuda().to(torch.bfloat16)
+    w = torch.from_numpy(R.round_bf16((rng.standard_normal(((Hq + 2 * Hkv) * D, hidden)) * 0.05).astype(np.float32)))
+    w = w.cuda().to(torch.bfloat16)
+    pages_per = 6                                                      # 96 positions per sequence
+    pos = rng.integers(0, pages_per * 16, (M,)).astype(np.int32)
+    if M > 4:
+        pos[1] = pages_per * 16 + 5                                    # past the last page: skipped
+        pos[2] = -1
+    seq = rng.permutation(M).astype(np.int32)
+    caches = []
+    for _ in range(2):
+        c = PagedKVCache(M * pages_per + 2, M, pages_per, Hkv, D)
+        c.page_table.copy_(torch.from_numpy(rng.permutation(M * pages_per + 2)[: M * pages_per].astype(np.int32)
+                                            .reshape(M, pages_per)))
+        c.pool.zero_()
+        caches.append(c)
+    caches[1].page_table.copy_(caches[0].page_table)
+    seq_t, pos_t = torch.from_numpy(seq).cuda(), torch.from_numpy(pos).cuda()
+    q1, k1, v1 = ops.gemm_bf16_nt_skinny(x, w, (Hq * D, Hkv * D, Hkv * D))
+    caches[0].append(seq_t, pos_t, k1, v1)
+    q2 = ops.gemm_qkv_append_bf16_skinny(x, w, caches[1], seq_t, pos_t, Hq)
+    torch.cuda.synchronize()
+    assert torch.equal(q1, q2)
+    assert torch.equal(caches[0].pool, caches[1].pool)
+    assert float(caches[1].pool.float().abs().max()) > 0
