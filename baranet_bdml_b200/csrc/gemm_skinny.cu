@@ -14,7 +14,8 @@
 //   shuffles or shared-memory staging are needed to form the MMA fragments.
 //   The 8 warps' partial sums (16 x 8 fp32) are added through shared memory in warp order (deterministic).
 // Variants: up to three column ranges of one concatenated weight written to separate outputs (q, k, v of the layer in one
-// launch), and the SwiGLU pair (two weights, h = silu(x Wg) * (x Wu), op_silu.cuh:7-15).
+// launch); the same with the K and V ranges rotated / appended to the paged cache by the epilogue instead (what
+// bn_kv_append would do with them, mygrad/llama/llama_layers.py:161-171 for the new token); and the SwiGLU pair (two weights, h = silu(x Wg) * (x Wu), op_silu.cuh:7-15).
 // K must be a multiple of 256 (a warp's eighth is a whole number of 32-wide steps) and at most 8192; N a multiple
 // of 8.  Anything else belongs to bn_gemm_bf16_nt_small_m.
 #include "common.cuh"
