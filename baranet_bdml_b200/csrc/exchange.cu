@@ -39,7 +39,7 @@ struct ExchangeParams {
     float* out;
     float* lse;
     int world, rank, n, D;
-    int expect;                            // counter value that means "delivered": step * EX_CTAS
+    int expect;                            // counter value that means "delivered": the step number
     int parity;
     unsigned long long wait_ns;
 };
@@ -48,18 +48,22 @@ __global__ void __launch_bounds__(EX_THREADS) exchange_merge_kernel(const Exchan
     __shared__ int s_abort;
     const int per_rank = p.n * (p.D + 1);                  // floats; a multiple of 4 (checked on the host)
     const int n_vec = per_rank / 4;
-    const int v0 = (int)((long long)n_vec * blockIdx.x / gridDim.x), v1 = (int)((long long)n_vec * (blockIdx.x + 1) / gridDim.x);
     if (threadIdx.x == 0) s_abort = 0;
-    // ---- phase 1: deliver this CTA's slice to every rank
-    const float4* src = reinterpret_cast<const float4*>(p.send);
-    for (int t = 0; t < p.n_targets; ++t) {
-        const int r = (p.rank + 1 + t) % p.n_targets;      // start with the neighbour, end with ourselves
+    // ---- phase 1: CTA t delivers this rank's whole partial to ONE rank (the t-th after ourselves, ourselves last), so
+    // a step costs every rank one system-scope fence and one counter update per target, whatever the number of CTAs
+    if ((int)blockIdx.x < p.n_targets) {
+        const int r = (p.rank + 1 + (int)blockIdx.x) % p.n_targets;
+        const float4* src = reinterpret_cast<const float4*>(p.send);
         float4* dst = reinterpret_cast<float4*>(p.peer_slots[r] + ((size_t)p.parity * p.world + p.rank) * per_rank);
-        for (int v = v0 + threadIdx.x; v < v1; v += EX_THREADS) dst[v] = src[v];
+        for (int v = threadIdx.x; v < n_vec; v += EX_THREADS) dst[v] = src[v];
+        // the CTA barrier orders every thread's stores before the one thread that publishes them: only it executes the
+        // system-scope fence (cumulative over what the barrier made visible to it)
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence_system();
+            atomicAdd_system(p.peer_flags[r] + p.rank, 1);
+        }
     }
-    __threadfence_system();
-    __syncthreads();
-    if ((int)threadIdx.x < p.n_targets) atomicAdd_system(p.peer_flags[threadIdx.x] + p.rank, 1);
     // ---- phase 2: everybody's step has arrived in OUR buffer?
     if ((int)threadIdx.x < p.world) {
         const uint64_t t0 = ptx::globaltimer_ns();
@@ -69,8 +73,8 @@ __global__ void __launch_bounds__(EX_THREADS) exchange_merge_kernel(const Exchan
                 if (s_abort || ptx::globaltimer_ns() - t0 > p.wait_ns) { s_abort = 1; break; }
             }
         }
+        __threadfence_system();      // acquire side, by the threads that saw the counters; the barrier hands it on
     }
-    __threadfence_system();
     __syncthreads();
     if (s_abort) {
         if (threadIdx.x == 0) atomicExch(p.error_word, BN_ERR_TIMEOUT);
@@ -80,18 +84,32 @@ __global__ void __launch_bounds__(EX_THREADS) exchange_merge_kernel(const Exchan
     const float* base = p.slots + (size_t)p.parity * p.world * per_rank;
     const int sub = threadIdx.x / 64, lane = threadIdx.x % 64;      // four rows at a time, 64 threads each
     for (int row = blockIdx.x * 4 + sub; row < p.n; row += gridDim.x * 4) {
+        // every rank's log-sum-exp of the row first (independent loads: one round trip to L2, not one per rank), then
+        // the weights e^(l_r - m*) once, then the rank's O values, again all requested before the first use
+        float l[EX_MAX_WORLD], wgt[EX_MAX_WORLD];
+#pragma unroll
+        for (int r = 0; r < EX_MAX_WORLD; ++r)
+            l[r] = r < p.world ? __ldcg(base + (size_t)r * per_rank + (size_t)p.n * p.D + row) : -INFINITY;
         float mstar = -INFINITY;
-        for (int r = 0; r < p.world; ++r) mstar = fmaxf(mstar, __ldcg(base + (size_t)r * per_rank + (size_t)p.n * p.D + row));
+#pragma unroll
+        for (int r = 0; r < EX_MAX_WORLD; ++r) mstar = fmaxf(mstar, l[r]);
         const float ms = mstar == -INFINITY ? 0.f : mstar;
         float tot = 0.f;
-        for (int r = 0; r < p.world; ++r) tot += expf(__ldcg(base + (size_t)r * per_rank + (size_t)p.n * p.D + row) - ms);
+#pragma unroll
+        for (int r = 0; r < EX_MAX_WORLD; ++r) {
+            wgt[r] = expf(l[r] - ms);               // 0 for a rank that holds no token of the row
+            if (r < p.world) tot += wgt[r];         // in rank order: every rank computes the same bits
+        }
         const float inv = tot > 0.f ? 1.f / tot : 0.f;
         for (int d = lane; d < p.D; d += 64) {
+            float o[EX_MAX_WORLD];
+#pragma unroll
+            for (int r = 0; r < EX_MAX_WORLD; ++r)
+                o[r] = (r < p.world && l[r] > -INFINITY) ? __ldcg(base + (size_t)r * per_rank + (size_t)row * p.D + d) : 0.f;
             float acc = 0.f;
-            for (int r = 0; r < p.world; ++r) {
-                const float l = __ldcg(base + (size_t)r * per_rank + (size_t)p.n * p.D + row);
-                if (l > -INFINITY) acc += __ldcg(base + (size_t)r * per_rank + (size_t)row * p.D + d) * expf(l - ms);
-            }
+#pragma unroll
+            for (int r = 0; r < EX_MAX_WORLD; ++r)
+                if (r < p.world && l[r] > -INFINITY) acc += o[r] * wgt[r];
             p.out[(size_t)row * p.D + d] = acc * inv;
         }
         if (p.lse && lane == 0) p.lse[row] = tot > 0.f ? ms + logf(tot) : -INFINITY;
@@ -195,10 +213,10 @@ extern "C" int bn_exchange_combine(bn_exchange_t* x, const float* partial, float
     p.lse = lse;
     p.world = x->world; p.rank = x->rank; p.n = x->n; p.D = x->D;
     x->step += 1;
-    p.expect = x->step * EX_CTAS;
+    p.expect = x->step;                       // one delivery per source rank and step
     p.parity = x->step & 1;
     p.wait_ns = (unsigned long long)(wait_us ? wait_us : 1000000u) * 1000ull;
-    exchange_merge_kernel<<<EX_CTAS, EX_THREADS, 0, as_stream(stream)>>>(p);
+    exchange_merge_kernel<<<x->n_targets > EX_CTAS ? x->n_targets : EX_CTAS, EX_THREADS, 0, as_stream(stream)>>>(p);
     return launch_status("bn_exchange_combine");
 }
 

@@ -1032,6 +1032,8 @@ def run_ours(args):
         result = measure_decode(torch, args, rank, world, dist, reduce_max, pk)
     elif args.generate_only:
         result = measure_generate(torch, args, rank, world, dist, reduce_max, pk)
+    elif args.longctx_only:
+        result = measure_longctx(torch, args, rank, world, dist, reduce_max, pk)
     else:
         result = measure_prefill(torch, ops, args, rank, world, dist, reduce_max, pk)
         if not args.no_decode:
@@ -1075,7 +1077,7 @@ def run_ours(args):
                     result["layer_f32"] = {"error": repr(e)}
     if rank == 0:
         result["clocks"] = sampler.stop()
-        if world == 1 and not args.no_cpu_baseline and not args.decode_only and not args.generate_only:
+        if world == 1 and not args.no_cpu_baseline and not (args.decode_only or args.generate_only or args.longctx_only):
             r = cpu_prefill_sample(n_batches=2)
             result["cpu_baseline"] = {"value": r["value"], "unit": "TFLOP/s", "cores": r["cores"], "kind": "port",
                                       "sample": r["sample"], "seconds": r["seconds"]}
@@ -1090,7 +1092,7 @@ def run_ours(args):
                     return None
                 obj = obj[k]
             return obj
-        if args.decode_only or args.generate_only:       # a profiling run of one object: nothing to summarise
+        if args.decode_only or args.generate_only or args.longctx_only:       # a run of one object: nothing to summarise
             _emit(json.dumps(result))
             if dist is not None:
                 dist.destroy_process_group()
@@ -1142,6 +1144,8 @@ def main():
     ap.add_argument("--generate-only", action="store_true",
                     help="run only the config-5 generation (for profiling), one timed generation; prints its object alone")
     ap.add_argument("--generate-steps", type=int, default=128, help="decode steps of the config-5 generation")
+    ap.add_argument("--longctx-only", action="store_true",
+                    help="run only the config-4 sequence-split decode (decode kernel + exchange); prints its object alone")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
