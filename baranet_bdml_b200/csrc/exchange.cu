@@ -44,8 +44,14 @@ struct ExchangeParams {
     unsigned long long wait_ns;
 };
 
-__global__ void __launch_bounds__(EX_THREADS) exchange_merge_kernel(const ExchangeParams p) {
+// 96 registers: a CTA of this kernel then fits beside a CTA of the decode kernel (124 registers x 320 threads), so
+// as a programmatic dependent of it the kernel is resident, and waiting, when the decode kernel ends.
+__global__ void __maxnreg__(96) exchange_merge_kernel(const ExchangeParams p) {
     __shared__ int s_abort;
+    // nothing is read before the kernel that produced `send` has completed; the next kernel of the stream (the next
+    // step's decode kernel) may begin its set-up while this one waits for the other ranks
+    ptx::grid_dependency_wait();
+    ptx::grid_launch_dependents();
     const int per_rank = p.n * (p.D + 1);                  // floats; a multiple of 4 (checked on the host)
     const int n_vec = per_rank / 4;
     if (threadIdx.x == 0) s_abort = 0;
@@ -216,7 +222,8 @@ extern "C" int bn_exchange_combine(bn_exchange_t* x, const float* partial, float
     p.expect = x->step;                       // one delivery per source rank and step
     p.parity = x->step & 1;
     p.wait_ns = (unsigned long long)(wait_us ? wait_us : 1000000u) * 1000ull;
-    exchange_merge_kernel<<<x->n_targets > EX_CTAS ? x->n_targets : EX_CTAS, EX_THREADS, 0, as_stream(stream)>>>(p);
+    launch_dependent(exchange_merge_kernel, (unsigned)(x->n_targets > EX_CTAS ? x->n_targets : EX_CTAS), EX_THREADS, 0,
+                     as_stream(stream), p);
     return launch_status("bn_exchange_combine");
 }
 
