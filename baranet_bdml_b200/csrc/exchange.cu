@@ -4,17 +4,20 @@
 //
 // Message: n rows of (D + 1) floats per rank (33.8 KB at batch 4 x 32 heads x (64 + 1)), i.e. latency-bound.  A
 // collective library needs a launch for the all-gather and another for the merge; here ONE kernel per GPU does
-// both over peer-mapped memory:
-//   phase 1  every CTA copies its slice of this rank's partial into the slot [parity][rank] of EVERY rank's
-//            exchange buffer with plain 16-byte stores (NVLink peer stores; no multicast, no TMA), fences at system
-//            scope and adds 1 to the counter [rank] in each of those buffers;
-//   phase 2  it waits, with a time limit, until the counters of its own buffer show that every CTA of every rank
-//            has delivered this step, then merges the rows it owns in rank order (so every rank computes the same
-//            bits) and writes them out.
+// both over peer-mapped memory, and the data carries its own arrival flag:
+//   phase 1  CTA t copies this rank's whole partial into the slot [parity][rank] of ONE rank's exchange buffer (the
+//            t-th after its own, its own last) with plain 16-byte stores (NVLink peer stores; no multicast, no TMA),
+//            each store = two floats and, beside each, the step number.  No fence and no counter: an 8-byte pair is
+//            written as one piece, so a reader that sees the step number beside a value sees the value.
+//   phase 2  every CTA merges the rows it owns in rank order (so every rank computes the same bits): it reads a row's
+//            log-sum-exps and then its outputs from every rank's slot, again and again - with a time limit - until
+//            the step number stands beside them.
+// (The first two versions published with a system-scope fence and per-rank counters, every CTA storing a slice to
+// every rank: 31 us at 8 GPUs; one CTA per target: 18 us; this form has no fence and no counter round trip at all.)
 // Steps alternate between two slot sets: a rank can be at most one step ahead of another (it cannot finish step
 // t + 1 before every rank has delivered step t + 1, which a rank does only after its own merge of step t), so the
-// slots of step t are not overwritten before they have been read.  The counters only grow (step e expects
-// e * CTAs per rank), so nothing is ever reset between steps.
+// slots of step t are not overwritten before they have been read.  The step number only grows and a fresh buffer holds
+// zeros, so a stale pair can never pass for the current step.
 // A wait that runs out (a rank that never arrives) stores BN_ERR_TIMEOUT in the buffer's error word and the kernel
 // returns; bn_exchange_status reports it.  After a timeout the exchange is out of step and must be destroyed.
 #include "common.cuh"
@@ -26,100 +29,122 @@ constexpr int EX_MAX_WORLD = 16;
 constexpr int EX_CTAS = 8;
 constexpr int EX_THREADS = 256;
 constexpr size_t EX_HEADER = 256;      // error word
-constexpr size_t EX_FLAGS = 256;       // EX_MAX_WORLD counters
+constexpr size_t EX_FLAGS = 256;       // reserved
 
 struct ExchangeParams {
-    float* peer_slots[EX_MAX_WORLD];       // slot area of every rank's buffer (this rank's own: local pointer)
-    int* peer_flags[EX_MAX_WORLD];
+    uint2* peer_slots[EX_MAX_WORLD];       // slot area of every rank's buffer (this rank's own: local pointer)
     int n_targets;                         // distinct buffers to deliver to (world, or 1 in single-process loop-back)
     const float* send;                     // this rank's partial: n * D outputs, then n log-sum-exps
-    float* slots;                          // own slot area: [2][world][n * (D + 1)]
-    volatile int* flags;                   // own counters
+    const uint2* slots;                    // own slot area: [2][world][n * (D + 1)] (value bits, step number)
     int* error_word;
     float* out;
     float* lse;
     int world, rank, n, D;
-    int expect;                            // counter value that means "delivered": the step number
+    uint32_t step;                         // 1, 2, ...: stands beside every value of this step
     int parity;
     unsigned long long wait_ns;
 };
 
+__device__ __forceinline__ uint2 ld_pair(const uint2* p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+
+// Values [idx] of every rank's slot, each read again until this step's number stands beside it (or the time limit runs
+// out: false).  All first reads are issued before any is looked at.
+template <int W>
+__device__ __forceinline__ bool gather_pairs(const ExchangeParams& p, const uint2* base, size_t per_rank, size_t idx,
+                                             unsigned active, float (&val)[W], uint64_t t0, int* s_abort) {
+    uint2 v[W];
+#pragma unroll
+    for (int r = 0; r < W; ++r)
+        if ((active >> r) & 1u) v[r] = ld_pair(base + (size_t)r * per_rank + idx);
+    for (uint32_t it = 0;; ++it) {
+        bool all = true;
+#pragma unroll
+        for (int r = 0; r < W; ++r)
+            if (((active >> r) & 1u) && v[r].y != p.step) {
+                v[r] = ld_pair(base + (size_t)r * per_rank + idx);
+                all = false;
+            }
+        if (all) break;
+        if ((it & 63) == 63 && (*reinterpret_cast<volatile int*>(s_abort) || ptx::globaltimer_ns() - t0 > p.wait_ns)) {
+            *reinterpret_cast<volatile int*>(s_abort) = 1;
+            return false;
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < W; ++r) val[r] = ((active >> r) & 1u) ? __uint_as_float(v[r].x) : 0.f;
+    return true;
+}
+
 // 96 registers: a CTA of this kernel then fits beside a CTA of the decode kernel (124 registers x 320 threads), so
 // as a programmatic dependent of it the kernel is resident, and waiting, when the decode kernel ends.
+// W = the most ranks the instance handles (its per-rank values live in registers): 8 or EX_MAX_WORLD.
+template <int W>
 __global__ void __maxnreg__(96) exchange_merge_kernel(const ExchangeParams p) {
     __shared__ int s_abort;
     // nothing is read before the kernel that produced `send` has completed; the next kernel of the stream (the next
     // step's decode kernel) may begin its set-up while this one waits for the other ranks
     ptx::grid_dependency_wait();
     ptx::grid_launch_dependents();
-    const int per_rank = p.n * (p.D + 1);                  // floats; a multiple of 4 (checked on the host)
-    const int n_vec = per_rank / 4;
+    const size_t per_rank = (size_t)p.n * (p.D + 1);       // floats; a multiple of 4 (checked on the host)
     if (threadIdx.x == 0) s_abort = 0;
-    // ---- phase 1: CTA t delivers this rank's whole partial to ONE rank (the t-th after ourselves, ourselves last), so
-    // a step costs every rank one system-scope fence and one counter update per target, whatever the number of CTAs
+    __syncthreads();
+    // ---- phase 1: CTA t delivers this rank's whole partial to ONE rank
     if ((int)blockIdx.x < p.n_targets) {
         const int r = (p.rank + 1 + (int)blockIdx.x) % p.n_targets;
-        const float4* src = reinterpret_cast<const float4*>(p.send);
-        float4* dst = reinterpret_cast<float4*>(p.peer_slots[r] + ((size_t)p.parity * p.world + p.rank) * per_rank);
-        for (int v = threadIdx.x; v < n_vec; v += EX_THREADS) dst[v] = src[v];
-        // the CTA barrier orders every thread's stores before the one thread that publishes them: only it executes the
-        // system-scope fence (cumulative over what the barrier made visible to it)
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            __threadfence_system();
-            atomicAdd_system(p.peer_flags[r] + p.rank, 1);
+        const float2* src = reinterpret_cast<const float2*>(p.send);
+        uint4* dst = reinterpret_cast<uint4*>(p.peer_slots[r] + ((size_t)p.parity * p.world + p.rank) * per_rank);
+        for (int v = threadIdx.x; v < (int)(per_rank / 2); v += EX_THREADS) {
+            const float2 x = src[v];
+            asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst + v), "r"(__float_as_uint(x.x)),
+                         "r"(p.step), "r"(__float_as_uint(x.y)), "r"(p.step)
+                         : "memory");
         }
     }
-    // ---- phase 2: everybody's step has arrived in OUR buffer?
-    if ((int)threadIdx.x < p.world) {
-        const uint64_t t0 = ptx::globaltimer_ns();
-        for (uint32_t it = 0;; ++it) {
-            if (p.flags[threadIdx.x] - p.expect >= 0) break;       // counters only grow
-            if ((it & 63) == 63) {
-                if (s_abort || ptx::globaltimer_ns() - t0 > p.wait_ns) { s_abort = 1; break; }
-            }
-        }
-        __threadfence_system();      // acquire side, by the threads that saw the counters; the barrier hands it on
-    }
-    __syncthreads();
-    if (s_abort) {
-        if (threadIdx.x == 0) atomicExch(p.error_word, BN_ERR_TIMEOUT);
-        return;
-    }
-    // ---- merge the rows this CTA owns, parts in rank order
-    const float* base = p.slots + (size_t)p.parity * p.world * per_rank;
+    // ---- phase 2: merge the rows this CTA owns, parts in rank order
+    const uint64_t t0 = ptx::globaltimer_ns();
+    const uint2* base = p.slots + (size_t)p.parity * p.world * per_rank;
+    const unsigned all_ranks = p.world >= 32 ? 0xffffffffu : ((1u << p.world) - 1u);
     const int sub = threadIdx.x / 64, lane = threadIdx.x % 64;      // four rows at a time, 64 threads each
-    for (int row = blockIdx.x * 4 + sub; row < p.n; row += gridDim.x * 4) {
-        // every rank's log-sum-exp of the row first (independent loads: one round trip to L2, not one per rank), then
-        // the weights e^(l_r - m*) once, then the rank's O values, again all requested before the first use
-        float l[EX_MAX_WORLD], wgt[EX_MAX_WORLD];
-#pragma unroll
-        for (int r = 0; r < EX_MAX_WORLD; ++r)
-            l[r] = r < p.world ? __ldcg(base + (size_t)r * per_rank + (size_t)p.n * p.D + row) : -INFINITY;
+    bool ok = true;
+    for (int row = blockIdx.x * 4 + sub; ok && row < p.n; row += gridDim.x * 4) {
+        float l[W], wgt[W];
+        ok = gather_pairs<W>(p, base, per_rank, (size_t)p.n * p.D + row, all_ranks, l, t0, &s_abort);
+        if (!ok) break;
         float mstar = -INFINITY;
+        unsigned holds = 0;                         // ranks that hold a token of the row
 #pragma unroll
-        for (int r = 0; r < EX_MAX_WORLD; ++r) mstar = fmaxf(mstar, l[r]);
+        for (int r = 0; r < W; ++r)
+            if (r < p.world) {
+                mstar = fmaxf(mstar, l[r]);
+                if (l[r] > -INFINITY) holds |= 1u << r;
+            }
         const float ms = mstar == -INFINITY ? 0.f : mstar;
         float tot = 0.f;
 #pragma unroll
-        for (int r = 0; r < EX_MAX_WORLD; ++r) {
-            wgt[r] = expf(l[r] - ms);               // 0 for a rank that holds no token of the row
-            if (r < p.world) tot += wgt[r];         // in rank order: every rank computes the same bits
+        for (int r = 0; r < W; ++r) {
+            wgt[r] = r < p.world ? expf(l[r] - ms) : 0.f;       // 0 for a rank that holds no token of the row
+            if (r < p.world) tot += wgt[r];                     // in rank order: every rank computes the same bits
         }
         const float inv = tot > 0.f ? 1.f / tot : 0.f;
         for (int d = lane; d < p.D; d += 64) {
-            float o[EX_MAX_WORLD];
-#pragma unroll
-            for (int r = 0; r < EX_MAX_WORLD; ++r)
-                o[r] = (r < p.world && l[r] > -INFINITY) ? __ldcg(base + (size_t)r * per_rank + (size_t)row * p.D + d) : 0.f;
+            float o[W];
+            // every rank's value is waited for, also where its weight is 0: the slot must be complete before the step ends
+            ok = gather_pairs<W>(p, base, per_rank, (size_t)row * p.D + d, all_ranks, o, t0, &s_abort);
+            if (!ok) break;
             float acc = 0.f;
 #pragma unroll
-            for (int r = 0; r < EX_MAX_WORLD; ++r)
-                if (r < p.world && l[r] > -INFINITY) acc += o[r] * wgt[r];
+            for (int r = 0; r < W; ++r)
+                if ((holds >> r) & 1u) acc += o[r] * wgt[r];
             p.out[(size_t)row * p.D + d] = acc * inv;
         }
-        if (p.lse && lane == 0) p.lse[row] = tot > 0.f ? ms + logf(tot) : -INFINITY;
+        if (ok && p.lse && lane == 0) p.lse[row] = tot > 0.f ? ms + logf(tot) : -INFINITY;
     }
+    __syncthreads();
+    if (s_abort && threadIdx.x == 0) atomicExch(p.error_word, BN_ERR_TIMEOUT);
 }
 
 }  // namespace bn
@@ -137,7 +162,7 @@ struct bn_exchange {
 };
 
 static size_t exchange_bytes(int n, int D, int world) {
-    return EX_HEADER + EX_FLAGS + (size_t)2 * world * n * (D + 1) * sizeof(float);
+    return EX_HEADER + EX_FLAGS + (size_t)2 * world * n * (D + 1) * sizeof(uint2);
 }
 
 extern "C" int bn_exchange_create(int n, int D, int world, int rank, bn_exchange_t** out) {
@@ -204,26 +229,25 @@ extern "C" int bn_exchange_combine(bn_exchange_t* x, const float* partial, float
     if (reinterpret_cast<uintptr_t>(partial) & 15) return fail(BN_ERR_INVALID_ARG, "bn_exchange_combine: partial must be 16-byte aligned");
     ExchangeParams p;
     char* own = static_cast<char*>(x->buffer);
-    for (int r = 0; r < EX_MAX_WORLD; ++r) { p.peer_slots[r] = nullptr; p.peer_flags[r] = nullptr; }
+    for (int r = 0; r < EX_MAX_WORLD; ++r) p.peer_slots[r] = nullptr;
     for (int r = 0; r < x->n_targets; ++r) {
         char* base = (r == x->rank || x->n_targets == 1) ? own : static_cast<char*>(x->peer_base[r]);
-        p.peer_flags[r] = reinterpret_cast<int*>(base + EX_HEADER);
-        p.peer_slots[r] = reinterpret_cast<float*>(base + EX_HEADER + EX_FLAGS);
+        p.peer_slots[r] = reinterpret_cast<uint2*>(base + EX_HEADER + EX_FLAGS);
     }
     p.n_targets = x->n_targets;
     p.send = partial;
-    p.slots = reinterpret_cast<float*>(own + EX_HEADER + EX_FLAGS);
-    p.flags = reinterpret_cast<volatile int*>(own + EX_HEADER);
+    p.slots = reinterpret_cast<const uint2*>(own + EX_HEADER + EX_FLAGS);
     p.error_word = reinterpret_cast<int*>(own);
     p.out = out;
     p.lse = lse;
     p.world = x->world; p.rank = x->rank; p.n = x->n; p.D = x->D;
     x->step += 1;
-    p.expect = x->step;                       // one delivery per source rank and step
+    p.step = (uint32_t)x->step;
     p.parity = x->step & 1;
     p.wait_ns = (unsigned long long)(wait_us ? wait_us : 1000000u) * 1000ull;
-    launch_dependent(exchange_merge_kernel, (unsigned)(x->n_targets > EX_CTAS ? x->n_targets : EX_CTAS), EX_THREADS, 0,
-                     as_stream(stream), p);
+    const unsigned grid = (unsigned)(x->n_targets > EX_CTAS ? x->n_targets : EX_CTAS);
+    if (x->world <= 8) launch_dependent(exchange_merge_kernel<8>, grid, EX_THREADS, 0, as_stream(stream), p);
+    else launch_dependent(exchange_merge_kernel<EX_MAX_WORLD>, grid, EX_THREADS, 0, as_stream(stream), p);
     return launch_status("bn_exchange_combine");
 }
 
