@@ -36,12 +36,10 @@ struct ExchangeParams {
     int n_targets;                         // distinct buffers to deliver to (world, or 1 in single-process loop-back)
     const float* send;                     // this rank's partial: n * D outputs, then n log-sum-exps
     const uint2* slots;                    // own slot area: [2][world][n * (D + 1)] (value bits, step number)
-    int* error_word;
+    int* error_word;                       // header word 0; word 1 = steps completed, word 2 = CTAs done with this step
     float* out;
     float* lse;
     int world, rank, n, D;
-    uint32_t step;                         // 1, 2, ...: stands beside every value of this step
-    int parity;
     unsigned long long wait_ns;
 };
 
@@ -55,7 +53,7 @@ __device__ __forceinline__ uint2 ld_pair(const uint2* p) {
 // out: false).  All first reads are issued before any is looked at.
 template <int W>
 __device__ __forceinline__ bool gather_pairs(const ExchangeParams& p, const uint2* base, size_t per_rank, size_t idx,
-                                             unsigned active, float (&val)[W], uint64_t t0, int* s_abort) {
+                                             unsigned active, uint32_t step, float (&val)[W], uint64_t t0, int* s_abort) {
     uint2 v[W];
 #pragma unroll
     for (int r = 0; r < W; ++r)
@@ -64,7 +62,7 @@ __device__ __forceinline__ bool gather_pairs(const ExchangeParams& p, const uint
         bool all = true;
 #pragma unroll
         for (int r = 0; r < W; ++r)
-            if (((active >> r) & 1u) && v[r].y != p.step) {
+            if (((active >> r) & 1u) && v[r].y != step) {
                 v[r] = ld_pair(base + (size_t)r * per_rank + idx);
                 all = false;
             }
@@ -90,29 +88,34 @@ __global__ void __maxnreg__(96) exchange_merge_kernel(const ExchangeParams p) {
     ptx::grid_dependency_wait();
     ptx::grid_launch_dependents();
     const size_t per_rank = (size_t)p.n * (p.D + 1);       // floats; a multiple of 4 (checked on the host)
+    // The step number lives in the buffer, not in the launch: every CTA reads "steps completed" (the last CTA of the
+    // previous launch wrote it; the wait above, or stream order, puts that before this read) - so the same launch can
+    // be replayed from a CUDA graph.  It is advanced below by the last CTA to finish, when every CTA has read it.
+    const uint32_t step = *reinterpret_cast<volatile uint32_t*>(p.error_word + 1) + 1u;     // 1, 2, ...
+    const int parity = (int)(step & 1u);
     if (threadIdx.x == 0) s_abort = 0;
     __syncthreads();
     // ---- phase 1: CTA t delivers this rank's whole partial to ONE rank
     if ((int)blockIdx.x < p.n_targets) {
         const int r = (p.rank + 1 + (int)blockIdx.x) % p.n_targets;
         const float2* src = reinterpret_cast<const float2*>(p.send);
-        uint4* dst = reinterpret_cast<uint4*>(p.peer_slots[r] + ((size_t)p.parity * p.world + p.rank) * per_rank);
+        uint4* dst = reinterpret_cast<uint4*>(p.peer_slots[r] + ((size_t)parity * p.world + p.rank) * per_rank);
         for (int v = threadIdx.x; v < (int)(per_rank / 2); v += EX_THREADS) {
             const float2 x = src[v];
             asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst + v), "r"(__float_as_uint(x.x)),
-                         "r"(p.step), "r"(__float_as_uint(x.y)), "r"(p.step)
+                         "r"(step), "r"(__float_as_uint(x.y)), "r"(step)
                          : "memory");
         }
     }
     // ---- phase 2: merge the rows this CTA owns, parts in rank order
     const uint64_t t0 = ptx::globaltimer_ns();
-    const uint2* base = p.slots + (size_t)p.parity * p.world * per_rank;
+    const uint2* base = p.slots + (size_t)parity * p.world * per_rank;
     const unsigned all_ranks = p.world >= 32 ? 0xffffffffu : ((1u << p.world) - 1u);
     const int sub = threadIdx.x / 64, lane = threadIdx.x % 64;      // four rows at a time, 64 threads each
     bool ok = true;
     for (int row = blockIdx.x * 4 + sub; ok && row < p.n; row += gridDim.x * 4) {
         float l[W], wgt[W];
-        ok = gather_pairs<W>(p, base, per_rank, (size_t)p.n * p.D + row, all_ranks, l, t0, &s_abort);
+        ok = gather_pairs<W>(p, base, per_rank, (size_t)p.n * p.D + row, all_ranks, step, l, t0, &s_abort);
         if (!ok) break;
         float mstar = -INFINITY;
         unsigned holds = 0;                         // ranks that hold a token of the row
@@ -133,7 +136,7 @@ __global__ void __maxnreg__(96) exchange_merge_kernel(const ExchangeParams p) {
         for (int d = lane; d < p.D; d += 64) {
             float o[W];
             // every rank's value is waited for, also where its weight is 0: the slot must be complete before the step ends
-            ok = gather_pairs<W>(p, base, per_rank, (size_t)row * p.D + d, all_ranks, o, t0, &s_abort);
+            ok = gather_pairs<W>(p, base, per_rank, (size_t)row * p.D + d, all_ranks, step, o, t0, &s_abort);
             if (!ok) break;
             float acc = 0.f;
 #pragma unroll
@@ -144,7 +147,14 @@ __global__ void __maxnreg__(96) exchange_merge_kernel(const ExchangeParams p) {
         if (ok && p.lse && lane == 0) p.lse[row] = tot > 0.f ? ms + logf(tot) : -INFINITY;
     }
     __syncthreads();
-    if (s_abort && threadIdx.x == 0) atomicExch(p.error_word, BN_ERR_TIMEOUT);
+    if (threadIdx.x == 0) {
+        if (s_abort) atomicExch(p.error_word, BN_ERR_TIMEOUT);
+        __threadfence();
+        if (atomicAdd(p.error_word + 2, 1) == (int)gridDim.x - 1) {      // the last CTA of the launch
+            p.error_word[2] = 0;
+            *reinterpret_cast<volatile uint32_t*>(p.error_word + 1) = step;
+        }
+    }
 }
 
 }  // namespace bn
@@ -241,9 +251,6 @@ extern "C" int bn_exchange_combine(bn_exchange_t* x, const float* partial, float
     p.out = out;
     p.lse = lse;
     p.world = x->world; p.rank = x->rank; p.n = x->n; p.D = x->D;
-    x->step += 1;
-    p.step = (uint32_t)x->step;
-    p.parity = x->step & 1;
     p.wait_ns = (unsigned long long)(wait_us ? wait_us : 1000000u) * 1000ull;
     const unsigned grid = (unsigned)(x->n_targets > EX_CTAS ? x->n_targets : EX_CTAS);
     if (x->world <= 8) launch_dependent(exchange_merge_kernel<8>, grid, EX_THREADS, 0, as_stream(stream), p);

@@ -340,10 +340,12 @@ BN_API int bn_attn_lse_combine_strided(const float* outs, int64_t outs_part_stri
  * ------------------------------------------------------------------------
  * The merge of bn_attn_lse_combine with the exchange in the same launch: every rank stores its partial (n rows of D
  * outputs, then n log-sum-exps: the layout the decode kernel writes when out_f32 and lse point into one buffer)
- * into every rank's exchange buffer with plain peer stores, waits (bounded) for the others' and merges in rank
- * order, so all ranks end with identical results.  No counterpart in the reference, which is single-GPU.
+ * into every rank's exchange buffer with plain peer stores - every value with the step number beside it, so no fence
+ * and no separate flag is needed - and merges in rank order, reading each rank's values again (bounded) until this
+ * step's number stands beside them, so all ranks end with identical results.  No counterpart in the reference,
+ * which is single-GPU.
  *
- *   bn_exchange_create       one per rank (allocates the buffer: 2 * world * n * (D + 1) floats + 512 bytes);
+ *   bn_exchange_create       one per rank (allocates the buffer: 2 * world * n * (D + 1) * 8 bytes + 512 bytes);
  *   bn_exchange_ipc_handle   64 bytes that name the buffer to the other processes of the node; the caller gathers
  *                            the handles of all ranks (rank order) with whatever transport it has;
  *   bn_exchange_open_peers   maps the other ranks' buffers (handles = world * 64 bytes); loopback != 0 instead keeps

@@ -1,8 +1,8 @@
 """The peer-memory exchange + merge kernel (bn_exchange_*), through the C ABI.
 
 One GPU is enough for two of its properties: a single-rank exchange must reproduce the plain merge over many steps
-(counters, the two alternating slot sets), and a wait for a rank that never delivers must END with BN_ERR_TIMEOUT and
-leave the context usable (the failure is made by a counter that nothing advances - no fault, trap or endless loop).
+(step numbers, the two alternating slot sets), and a wait for a rank that never delivers must END with BN_ERR_TIMEOUT
+and leave the context usable (the failure is made by a slot that nothing ever writes - no fault, trap or endless loop).
 The two-rank run over real peer memory needs two GPUs and is skipped without them."""
 import ctypes as C
 import os
@@ -45,7 +45,7 @@ def test_single_rank_exchange_reproduces_its_partial_over_many_steps(lib):
 def test_a_rank_that_never_delivers_ends_in_a_timeout_status(lib):
     from baranet_bdml_b200 import _lib
     n, D = 128, 64
-    h = _make(lib, n, D, 2, 0, 1)        # world 2 inside one process: the counter of rank 1 is never advanced
+    h = _make(lib, n, D, 2, 0, 1)        # world 2 inside one process: the slot of rank 1 is never written
     out = torch.zeros((n, D), device="cuda")
     part = torch.randn(n * (D + 1), device="cuda")
     _lib.check(lib.bn_exchange_combine(h, part.data_ptr(), out.data_ptr(), None, 2000, None))     # 2 ms
