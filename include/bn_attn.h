@@ -351,7 +351,8 @@ BN_API int bn_attn_lse_combine_strided(const float* outs, int64_t outs_part_stri
  *   bn_exchange_open_peers   maps the other ranks' buffers (handles = world * 64 bytes); loopback != 0 instead keeps
  *                            everything in this process (world 1, or a test that lets a wait run out);
  *   bn_exchange_combine      one launch per step on every rank, in the same order on all of them; wait_us bounds the
- *                            wait for the slowest rank (0 = one second);
+ *                            wait for the slowest rank (0 = one second); the step count is kept in the buffer, so
+ *                            the launch may be captured into a CUDA graph and replayed;
  *   bn_exchange_status       synchronises `stream`; BN_ERR_TIMEOUT if a wait ran out (the exchange must then be
  *                            destroyed: the ranks are out of step);
  *   bn_exchange_destroy      unmaps and frees.
