@@ -42,6 +42,36 @@ def test_single_rank_exchange_reproduces_its_partial_over_many_steps(lib):
     lib.bn_exchange_destroy(h)
 
 
+def test_exchange_replayed_from_a_cuda_graph(lib):
+    """The step number lives in the exchange buffer, not in the launch: a captured launch replayed many times (with
+    eager launches in between) keeps merging what is in its send buffer at that moment."""
+    from baranet_bdml_b200 import _lib
+    n, D = 128, 64
+    h = _make(lib, n, D, 1, 0, 1)
+    part = torch.randn(n * (D + 1), device="cuda")
+    out = torch.empty((n, D), device="cuda")
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(3):       # an odd number of steps per replay: both slot sets meet both ends of a replay
+                _lib.check(lib.bn_exchange_combine(h, part.data_ptr(), out.data_ptr(), None, 0, side.cuda_stream))
+    torch.cuda.current_stream().wait_stream(side)
+    for it in range(6):
+        part.normal_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert lib.bn_exchange_status(h, None) == _lib.BN_OK
+        assert torch.equal(out, part[: n * D].view(n, D))
+        if it % 2:                    # an eager step between replays
+            part.normal_()
+            _lib.check(lib.bn_exchange_combine(h, part.data_ptr(), out.data_ptr(), None, 0, None))
+            torch.cuda.synchronize()
+            assert torch.equal(out, part[: n * D].view(n, D))
+    lib.bn_exchange_destroy(h)
+
+
 def test_a_rank_that_never_delivers_ends_in_a_timeout_status(lib):
     from baranet_bdml_b200 import _lib
     n, D = 128, 64
