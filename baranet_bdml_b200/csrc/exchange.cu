@@ -26,7 +26,7 @@
 namespace bn {
 
 constexpr int EX_MAX_WORLD = 16;
-constexpr int EX_CTAS = 8;
+constexpr int EX_CTAS = 8;         // fewest CTAs of a launch
 constexpr int EX_THREADS = 256;
 constexpr size_t EX_HEADER = 256;      // error word
 constexpr size_t EX_FLAGS = 256;       // reserved
@@ -252,7 +252,12 @@ extern "C" int bn_exchange_combine(bn_exchange_t* x, const float* partial, float
     p.lse = lse;
     p.world = x->world; p.rank = x->rank; p.n = x->n; p.D = x->D;
     p.wait_ns = (unsigned long long)(wait_us ? wait_us : 1000000u) * 1000ull;
-    const unsigned grid = (unsigned)(x->n_targets > EX_CTAS ? x->n_targets : EX_CTAS);
+    // one CTA merges four rows at a time; enough CTAs that every row group is merged in the first pass (a pass is two
+    // round trips to L2), and at least one CTA per target rank for the delivery
+    int want = (x->n + 3) / 4;
+    if (want > 128) want = 128;
+    if (want < EX_CTAS) want = EX_CTAS;
+    const unsigned grid = (unsigned)(x->n_targets > want ? x->n_targets : want);
     if (x->world <= 8) launch_dependent(exchange_merge_kernel<8>, grid, EX_THREADS, 0, as_stream(stream), p);
     else launch_dependent(exchange_merge_kernel<EX_MAX_WORLD>, grid, EX_THREADS, 0, as_stream(stream), p);
     return launch_status("bn_exchange_combine");
