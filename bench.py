@@ -59,6 +59,11 @@ class _Traffic(dict):
 NCU_TRAFFIC = _Traffic(_ncu_traffic())
 
 
+# nominal figures, beside the measured ones the fractions are taken against: dense bf16 2250 TFLOP/s, HBM3e 8000 GB/s
+NOMINAL_TENSOR_TFLOPS = 2250.0
+NOMINAL_HBM_GBS = 8000.0
+
+
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -430,6 +435,7 @@ def measure_prefill(torch, ops, args, rank, world, dist, reduce_max, pk):
                      "frac": ach / pk["tensor"], "traffic": NCU_TRAFFIC["prefill_kernel"],
                      "traffic_unit": "bytes of DRAM traffic per launch (ncu capture, profiles/prefill_kernel_config2.md)",
                      "peak_source": pk["source"] + " (bf16 burst)",
+                     "frac_of_nominal": ach / NOMINAL_TENSOR_TFLOPS, "nominal_peak": NOMINAL_TENSOR_TFLOPS,
                      "kernel": "prefill_kernel", "kernel_ms": ms_kernel},
         "e2e": None if ms_e2e is None else {
             "value": flops * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
@@ -529,7 +535,8 @@ def measure_decode(torch, args, rank, world, dist, reduce_max, pk):
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s", "frac": gbs / pk["hbm"],
                      "traffic": NCU_TRAFFIC["decode_paged_kernel"],
                      "traffic_unit": "bytes of DRAM traffic per launch (ncu capture, profiles/decode_paged_kernel_config3.md)",
-                     "peak_source": pk["source"], "kernel": "decode_paged_kernel"},
+                     "peak_source": pk["source"], "frac_of_nominal": gbs / NOMINAL_HBM_GBS,
+                     "nominal_peak": NOMINAL_HBM_GBS, "kernel": "decode_paged_kernel"},
         "ms_per_step_eager_by_rank": per_rank,
         "gpu_launches": dsteps,
     }
@@ -903,6 +910,7 @@ def measure_longctx(torch, args, rank, world, dist, reduce_max, pk):
                    "l2": "cache per GPU is %d MiB" % (B * Lloc * Hkv * D * 4 >> 20)},
         "roofline": {"bound": "hbm", "achieved": gbs / world, "peak": pk["hbm"], "unit": "GB/s",
                      "frac": gbs / world / pk["hbm"], "traffic": None, "peak_source": pk["source"],
+                     "frac_of_nominal": gbs / world / NOMINAL_HBM_GBS, "nominal_peak": NOMINAL_HBM_GBS,
                      "kernel": "decode_paged_kernel", "note": "per GPU; includes the exchange when n_gpus > 1"},
         "step_split_ms": {"decode_kernel": ms_dec, "decode_kernel_by_rank": _all_ranks(torch, dist, ms_dec_own),
                           "exchange_and_merge": ms_ex, "exchange_and_merge_nccl_all_gather": ms_ex_nccl,
